@@ -1,0 +1,95 @@
+// Shared device helpers for the sm_100a kernels: element conversion, warp and block
+// reductions, vector access, and the error convention of the C entry points.
+//
+// Every entry point is `extern "C" int asb_<name>(..., cudaStream_t stream)`. It returns 0 on
+// success; on a refused size or a failed launch it stores a message (asb_last_error) and
+// returns non-zero. Nothing here allocates device memory: buffers come from the caller.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include <cstdarg>
+#include <cstdio>
+
+namespace asb {
+
+enum DType : int { kFloat32 = 0, kBFloat16 = 1 };
+
+char* error_buffer();
+int fail(const char* fmt, ...);
+int check_launch(const char* what);
+
+template <typename T>
+__device__ __forceinline__ float to_float(T v);
+template <>
+__device__ __forceinline__ float to_float<float>(float v) {
+  return v;
+}
+template <>
+__device__ __forceinline__ float to_float<__nv_bfloat16>(__nv_bfloat16 v) {
+  return __bfloat162float(v);
+}
+
+template <typename T>
+__device__ __forceinline__ T from_float(float v);
+template <>
+__device__ __forceinline__ float from_float<float>(float v) {
+  return v;
+}
+template <>
+__device__ __forceinline__ __nv_bfloat16 from_float<__nv_bfloat16>(float v) {
+  return __float2bfloat16_rn(v);
+}
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+
+// Sum over a block of up to 1024 threads; `scratch` holds 32 floats of shared memory. Every
+// thread gets the total. The order of the additions depends only on the block size.
+__device__ __forceinline__ float block_sum(float v, float* scratch) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  v = warp_sum(v);
+  __syncthreads();
+  if (lane == 0) scratch[warp] = v;
+  __syncthreads();
+  const int nwarps = (blockDim.x + 31) >> 5;
+  float t = lane < nwarps ? scratch[lane] : 0.f;
+  return warp_sum(t);
+}
+
+__device__ __forceinline__ float block_max(float v, float* scratch) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  v = warp_max(v);
+  __syncthreads();
+  if (lane == 0) scratch[warp] = v;
+  __syncthreads();
+  const int nwarps = (blockDim.x + 31) >> 5;
+  float t = lane < nwarps ? scratch[lane] : -INFINITY;
+  return warp_max(t);
+}
+
+}  // namespace asb
+
+#define ASB_DISPATCH_DTYPE(dtype, T, ...)                         \
+  do {                                                            \
+    if ((dtype) == asb::kFloat32) {                               \
+      using T = float;                                            \
+      __VA_ARGS__;                                                \
+    } else if ((dtype) == asb::kBFloat16) {                       \
+      using T = __nv_bfloat16;                                    \
+      __VA_ARGS__;                                                \
+    } else {                                                      \
+      return asb::fail("unknown dtype code %d", (int)(dtype));    \
+    }                                                             \
+  } while (0)

@@ -1,0 +1,30 @@
+// Error text of the last refused call on this thread, and the library's identity.
+#include "common.cuh"
+
+namespace asb {
+
+char* error_buffer() {
+  static thread_local char buffer[512];
+  return buffer;
+}
+
+int fail(const char* fmt, ...) {
+  va_list args;
+  va_start(args, fmt);
+  vsnprintf(error_buffer(), 512, fmt, args);
+  va_end(args);
+  return 1;
+}
+
+int check_launch(const char* what) {
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return fail("%s: %s", what, cudaGetErrorString(e));
+  return 0;
+}
+
+}  // namespace asb
+
+extern "C" const char* asb_last_error() { return asb::error_buffer(); }
+
+// Architecture the kernels were compiled for; the loader checks it against the device.
+extern "C" int asb_compiled_arch() { return 100; }

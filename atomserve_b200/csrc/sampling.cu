@@ -1,0 +1,372 @@
+// Sampling on the device, one block per row of float32 logits [B, V].
+//
+// The rules are the reference sampler's (atomserve/sampler.py:82-129): top-k on the raw
+// logits (0 or >= V keeps all; temperature 0 is the single best), divide by the temperature,
+// softmax over the kept, top-p drops a token once the probability mass ranked above it has
+// reached top_p (the best always stays), then an exponential race: argmax of p_i / E_i with
+// E_i ~ Exp(1) picks token i with probability p_i / sum(p). The presence penalty is a
+// separate scatter that runs first (atomserve/sampler.py:144-168).
+//
+// The reference sorts (torch.topk, or its 1024-thread Metal kernel, atomserve/kernels.py:336-435).
+// Here nothing is sorted: the k-th largest logit is found by a radix select on order-preserving
+// integer keys (four 8-bit digits, counting histograms in shared memory), and the top-p cut
+// by the same walk over histograms of probability mass, kept as 64-bit fixed point so that
+// the sums do not depend on the order of the atomic additions. Ties at a cut are broken towards
+// the lower token id, by a third select over the ids. When top-k leaves at most 1024
+// candidates they are compacted into shared memory and the later passes read only those.
+//
+// Random numbers are Philox-4x32-10 keyed by the row's seed; the counter is (token id, the
+// row's draw counter). A seeded request passes its own seed and counts its own draws, so what
+// it draws does not depend on its neighbours in the batch (atomserve/sampler.py:123-127).
+#include "common.cuh"
+
+namespace {
+
+constexpr int kThreads = 1024;
+constexpr int kBins = 256;
+constexpr int kHistCopies = 8;
+constexpr int kCompact = 1024;
+
+__device__ __forceinline__ uint32_t order_key(float f) {
+  const uint32_t u = __float_as_uint(f);
+  return (u & 0x80000000u) ? ~u : (u | 0x80000000u);  // ascending with the float order
+}
+
+struct Philox {
+  static __device__ __forceinline__ void round(uint32_t (&c)[4], uint32_t k0, uint32_t k1) {
+    const uint32_t hi0 = __umulhi(0xD2511F53u, c[0]), lo0 = 0xD2511F53u * c[0];
+    const uint32_t hi1 = __umulhi(0xCD9E8D57u, c[2]), lo1 = 0xCD9E8D57u * c[2];
+    const uint32_t n0 = hi1 ^ c[1] ^ k0, n2 = hi0 ^ c[3] ^ k1;
+    c[0] = n0; c[1] = lo1; c[2] = n2; c[3] = lo0;
+  }
+  static __device__ __forceinline__ uint32_t draw(uint64_t seed, uint64_t counter, uint32_t index) {
+    uint32_t c[4] = {index, (uint32_t)counter, (uint32_t)(counter >> 32), 0x5a17u};
+    uint32_t k0 = (uint32_t)seed, k1 = (uint32_t)(seed >> 32);
+#pragma unroll
+    for (int i = 0; i < 10; ++i) {
+      round(c, k0, k1);
+      k0 += 0x9E3779B9u;
+      k1 += 0xBB67AE85u;
+    }
+    return c[0];
+  }
+};
+
+// A row as the passes see it: the full logits (id == position) or the compacted candidates.
+struct RowView {
+  const float* val;
+  const int* id;  // null: identity
+  int n;
+  __device__ __forceinline__ float value(int i) const { return val[i]; }
+  __device__ __forceinline__ int token(int i) const { return id ? id[i] : i; }
+};
+
+struct Scratch {
+  unsigned long long hist[kHistCopies][kBins];
+  float red[32];
+  int red_i[32];
+  unsigned long long bcast[4];
+  float cand_val[kCompact];
+  int cand_id[kCompact];
+  int cand_n;
+};
+
+// Descending radix select over 32-bit keys. `item(i, key, weight)` says whether element i takes
+// part, its key and its non-negative integer weight. Finds the largest key c such that the
+// weight of all taking-part elements with key > c is < target <= that weight plus the weight
+// of key == c. Returns c, and in `above` the weight strictly above c. (With weight 1 and
+// target k this is the k-th largest key.) If the total weight is below target, returns 0 with
+// `above` = total: everything is kept.
+template <typename Item>
+__device__ uint32_t radix_select(const RowView& row, Scratch& s, unsigned long long target,
+                                 unsigned long long* above, unsigned long long* equal, Item item) {
+  uint32_t prefix = 0, mask = 0;
+  unsigned long long acc = 0;
+  for (int shift = 24; shift >= 0; shift -= 8) {
+    for (int i = threadIdx.x; i < kHistCopies * kBins; i += blockDim.x) (&s.hist[0][0])[i] = 0ull;
+    __syncthreads();
+    unsigned long long* h = s.hist[(threadIdx.x >> 5) % kHistCopies];
+    for (int i = threadIdx.x; i < row.n; i += blockDim.x) {
+      uint32_t key;
+      unsigned long long w;
+      if (item(i, key, w) && (key & mask) == prefix && w) atomicAdd(&h[(key >> shift) & 255u], w);
+    }
+    __syncthreads();
+    if (threadIdx.x < kBins) {
+      unsigned long long t = 0;
+      for (int c = 0; c < kHistCopies; ++c) t += s.hist[c][threadIdx.x];
+      s.hist[0][threadIdx.x] = t;
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      int digit = -1;
+      unsigned long long a = acc;
+      for (int b = kBins - 1; b >= 0; --b) {
+        const unsigned long long hb = s.hist[0][b];
+        if (a + hb >= target) { digit = b; break; }
+        a += hb;
+      }
+      s.bcast[0] = a;
+      s.bcast[1] = (unsigned long long)(long long)digit;
+      s.bcast[3] = digit >= 0 ? s.hist[0][digit] : 0ull;
+    }
+    __syncthreads();
+    acc = s.bcast[0];
+    const long long digit = (long long)s.bcast[1];
+    *equal = s.bcast[3];  // after the last digit: the weight of key == result
+    __syncthreads();
+    if (digit < 0) {  // the whole set weighs less than target
+      *above = acc;
+      return 0u;
+    }
+    prefix |= (uint32_t)digit << shift;
+    mask |= 255u << shift;
+  }
+  *above = acc;
+  return prefix;
+}
+
+// The cut of one stage: keep key > cut_key, and of key == cut_key the tokens with id <= cut_id.
+struct Cut {
+  uint32_t key;
+  int id;
+  __device__ __forceinline__ bool keeps(uint32_t k, int token) const {
+    return k > key || (k == key && token <= id);
+  }
+};
+
+// After a select that found `key` with `need` more units wanted among the ties: the id below
+// which ties are kept. Unit weights (top-k) keep exactly `need` ties.
+template <typename Item>
+__device__ Cut cut_with_ties(const RowView& row, Scratch& s, uint32_t key, unsigned long long need,
+                             unsigned long long equal, unsigned long long unit, Item item) {
+  Cut cut{key, 0x7fffffff};
+  if (key == 0u || unit == 0ull) return cut;
+  // how many ties are wanted: the smallest t with t * unit >= need
+  const unsigned long long want = (need + unit - 1) / unit;
+  if (want * unit >= equal) return cut;  // all of them: no pass over the ids
+  unsigned long long dummy, dummy2;
+  auto by_id = [&](int i, uint32_t& k2, unsigned long long& w2) {
+    uint32_t k;
+    unsigned long long w;
+    if (!item(i, k, w) || k != key) return false;
+    k2 = ~(uint32_t)row.token(i);  // descending on ~id is ascending on id
+    w2 = 1ull;
+    return true;
+  };
+  const uint32_t idk = radix_select(row, s, want, &dummy, &dummy2, by_id);
+  if (idk != 0u) cut.id = (int)~idk;
+  return cut;
+}
+
+__device__ int row_argmax(const RowView& row, Scratch& s, float* best_value) {
+  float best = -INFINITY;
+  int best_id = 0x7fffffff;
+  for (int i = threadIdx.x; i < row.n; i += blockDim.x) {
+    const float v = row.value(i);
+    const int t = row.token(i);
+    if (v > best || (v == best && t < best_id)) { best = v; best_id = t; }
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+    const int oi = __shfl_xor_sync(0xffffffffu, best_id, o);
+    if (ov > best || (ov == best && oi < best_id)) { best = ov; best_id = oi; }
+  }
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  __syncthreads();
+  if (lane == 0) { s.red[warp] = best; s.red_i[warp] = best_id; }
+  __syncthreads();
+  if (warp == 0) {
+    const int nw = (blockDim.x + 31) >> 5;
+    best = lane < nw ? s.red[lane] : -INFINITY;
+    best_id = lane < nw ? s.red_i[lane] : 0x7fffffff;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+      const int oi = __shfl_xor_sync(0xffffffffu, best_id, o);
+      if (ov > best || (ov == best && oi < best_id)) { best = ov; best_id = oi; }
+    }
+    if (lane == 0) { s.red[0] = best; s.red_i[0] = best_id; }
+  }
+  __syncthreads();
+  const int id = s.red_i[0] == 0x7fffffff ? 0 : s.red_i[0];  // a row of NaN or -inf only
+  if (best_value) *best_value = s.red[0];
+  __syncthreads();
+  return id;
+}
+
+// Probability mass of one token as 64-bit fixed point: exp((v - max) / T) * 2^32.
+__device__ __forceinline__ unsigned long long mass_of(float v, float vmax, float inv_t) {
+  const float w = expf((v - vmax) * inv_t);  // in [0, 1]
+  return (unsigned long long)((double)w * 4294967296.0);
+}
+
+__global__ void __launch_bounds__(kThreads)
+sample_rows_kernel(int* __restrict__ out, const float* __restrict__ logits, int V,
+                   const float* __restrict__ temperature, const int* __restrict__ top_k,
+                   const float* __restrict__ top_p, const unsigned long long* __restrict__ seed,
+                   const unsigned long long* __restrict__ counter) {
+  __shared__ Scratch s;
+  const int b = blockIdx.x;
+  RowView row{logits + (size_t)b * V, nullptr, V};
+  const float temp = temperature[b];
+
+  float vmax;
+  const int best = row_argmax(row, s, &vmax);
+  if (!(temp > 0.f)) {  // greedy: the single best, lowest id among equals
+    if (threadIdx.x == 0) out[b] = best;
+    return;
+  }
+  const float inv_t = 1.f / temp;
+
+  // top-k
+  const int k = top_k[b];
+  Cut kcut{0u, 0x7fffffff};
+  if (k > 0 && k < V) {
+    auto unit = [&](int i, uint32_t& key, unsigned long long& w) {
+      key = order_key(row.value(i));
+      w = 1ull;
+      return true;
+    };
+    unsigned long long above, equal;
+    const uint32_t key = radix_select(row, s, (unsigned long long)k, &above, &equal, unit);
+    kcut = cut_with_ties(row, s, key, (unsigned long long)k - above, equal, 1ull, unit);
+    if (k <= kCompact) {  // later passes read the candidates from shared memory
+      if (threadIdx.x == 0) s.cand_n = 0;
+      __syncthreads();
+      for (int i = threadIdx.x; i < V; i += blockDim.x) {
+        const float v = row.value(i);
+        if (kcut.keeps(order_key(v), i)) {
+          const int at = atomicAdd(&s.cand_n, 1);
+          if (at < kCompact) { s.cand_val[at] = v; s.cand_id[at] = i; }
+        }
+      }
+      __syncthreads();
+      row = RowView{s.cand_val, s.cand_id, min(s.cand_n, kCompact)};
+      kcut = Cut{0u, 0x7fffffff};
+    }
+  }
+
+  // total mass of the kept, then the top-p cut
+  auto massed = [&](int i, uint32_t& key, unsigned long long& w) {
+    const float v = row.value(i);
+    key = order_key(v);
+    if (!kcut.keeps(key, row.token(i))) return false;
+    w = mass_of(v, vmax, inv_t);
+    return true;
+  };
+  unsigned long long total = 0;
+  for (int i = threadIdx.x; i < row.n; i += blockDim.x) {
+    uint32_t key;
+    unsigned long long w;
+    if (massed(i, key, w)) total += w;
+  }
+  {
+    // integer sum over the block: exact, so independent of the order
+    for (int o = 16; o > 0; o >>= 1) total += __shfl_xor_sync(0xffffffffu, total, o);
+    __syncthreads();
+    if ((threadIdx.x & 31) == 0) s.hist[0][threadIdx.x >> 5] = total;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      unsigned long long t = 0;
+      for (int w = 0; w < (int)(blockDim.x >> 5); ++w) t += s.hist[0][w];
+      s.bcast[2] = t;
+    }
+    __syncthreads();
+    total = s.bcast[2];
+    __syncthreads();
+  }
+
+  Cut pcut{0u, 0x7fffffff};
+  const float p = top_p[b];
+  if (p < 1.f) {
+    // keep a token while the mass ranked above it is < p * total: find the first key whose
+    // cumulative mass (itself included) exceeds p * total, ties by ascending id
+    unsigned long long target = (unsigned long long)ceil((double)p * (double)total);
+    if (target < 1ull) target = 1ull;  // the best token always stays
+    if (target > total) target = total;
+    unsigned long long above, equal;
+    const uint32_t key = radix_select(row, s, target, &above, &equal, massed);
+    // mass of one tied token (all ties share the key, hence the value)
+    unsigned long long unit = mass_of(__uint_as_float((key & 0x80000000u) ? (key & 0x7fffffffu) : ~key), vmax, inv_t);
+    pcut = cut_with_ties(row, s, key, target - above, equal, unit, massed);
+  }
+
+  // exponential race among the kept
+  const unsigned long long sd = seed[b], ctr = counter[b];
+  float best_score = -1.f;
+  int best_token = 0x7fffffff;
+  for (int i = threadIdx.x; i < row.n; i += blockDim.x) {
+    const float v = row.value(i);
+    const uint32_t key = order_key(v);
+    const int token = row.token(i);
+    if (!kcut.keeps(key, token) || !pcut.keeps(key, token)) continue;
+    const float w = expf((v - vmax) * inv_t);
+    const uint32_t bits = Philox::draw(sd, ctr, (uint32_t)token);
+    const float u = ((float)(bits >> 8) + 0.5f) * (1.f / 16777216.f);  // (0, 1)
+    const float e = fmaxf(-logf(u), 1e-10f);
+    const float score = w / e;
+    if (score > best_score || (score == best_score && token < best_token)) {
+      best_score = score;
+      best_token = token;
+    }
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float os = __shfl_xor_sync(0xffffffffu, best_score, o);
+    const int ot = __shfl_xor_sync(0xffffffffu, best_token, o);
+    if (os > best_score || (os == best_score && ot < best_token)) { best_score = os; best_token = ot; }
+  }
+  __syncthreads();
+  if ((threadIdx.x & 31) == 0) { s.red[threadIdx.x >> 5] = best_score; s.red_i[threadIdx.x >> 5] = best_token; }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    for (int w = 1; w < (int)(blockDim.x >> 5); ++w)
+      if (s.red[w] > best_score || (s.red[w] == best_score && s.red_i[w] < best_token)) {
+        best_score = s.red[w];
+        best_token = s.red_i[w];
+      }
+    out[b] = best_token == 0x7fffffff ? best : best_token;
+  }
+}
+
+__global__ void argmax_rows_kernel(int* __restrict__ out, const float* __restrict__ logits, int V) {
+  __shared__ Scratch s;
+  RowView row{logits + (size_t)blockIdx.x * V, nullptr, V};
+  const int best = row_argmax(row, s, nullptr);
+  if (threadIdx.x == 0) out[blockIdx.x] = best;
+}
+
+__global__ void presence_penalty_kernel(float* __restrict__ logits, const int* __restrict__ rows,
+                                        const int* __restrict__ tokens,
+                                        const float* __restrict__ amounts, int n, int V) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n && tokens[i] >= 0 && tokens[i] < V) logits[(size_t)rows[i] * V + tokens[i]] -= amounts[i];
+}
+
+}  // namespace
+
+extern "C" int asb_argmax_rows(int* out, const float* logits, int B, int V, cudaStream_t stream) {
+  if (B == 0) return 0;
+  argmax_rows_kernel<<<B, kThreads, 0, stream>>>(out, logits, V);
+  return asb::check_launch("argmax_rows");
+}
+
+// Each (row, token) pair must appear once: the penalty is subtracted once per distinct token.
+extern "C" int asb_presence_penalty(float* logits, const int* rows, const int* tokens,
+                                    const float* amounts, int n, int V, cudaStream_t stream) {
+  if (n == 0) return 0;
+  presence_penalty_kernel<<<(n + 255) / 256, 256, 0, stream>>>(logits, rows, tokens, amounts, n, V);
+  return asb::check_launch("presence_penalty");
+}
+
+extern "C" int asb_sample_rows(int* out, const float* logits, int B, int V,
+                               const float* temperature, const int* top_k, const float* top_p,
+                               const unsigned long long* seed, const unsigned long long* counter,
+                               cudaStream_t stream) {
+  if (B == 0) return 0;
+  if (V < 1) return asb::fail("sample_rows: vocabulary %d", V);
+  sample_rows_kernel<<<B, kThreads, 0, stream>>>(out, logits, V, temperature, top_k, top_p, seed, counter);
+  return asb::check_launch("sample_rows");
+}

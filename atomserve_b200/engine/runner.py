@@ -1,0 +1,231 @@
+"""The step function: a batch of (request, its next tokens) in, logits at the wanted places out.
+
+A `Row` is one request's share of a step: any number >= 1 of new tokens at positions
+`start, start + 1, ...`, everything before `start` being in the cache already, and `want`, the
+places among these tokens whose logits are asked for. A step may mix whole prompts, portions
+of prompts cut anywhere and single decoded tokens; all rows run as one flat batch of T tokens
+with no padding, the keys and values of every token are written to the request's pages, and
+the function returns float32 logits [number of wanted places, vocab] in the order of the rows
+and of `want` (atomserve/runner.py:42-56, 87-180 is the reference's form of this contract).
+
+The runner reads requests and never changes them: reserving pages before a step and
+advancing counters after it belong to the caller (the scheduler, or the trace replayer).
+
+Everything the kernels need to know about the batch is packed into one int32 buffer on the
+host and copied to the device once per step (atomserve/runner.py:215-241). Steps made only of
+single tokens are replayed from CUDA graphs, captured per (requests, table width) bucket.
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+
+import numpy as np
+import torch
+
+from atomserve_b200.cache.manager import CacheManager, RequestCache
+from atomserve_b200.parts.base import CacheView, StepContext
+from atomserve_b200.parts.model import DecoderModel
+
+
+@dataclass
+class Row:
+    tokens: list[int]
+    start: int
+    cache: RequestCache
+    want: list[int] = field(default_factory=list)  # indices into `tokens`
+
+
+def slot_of(block_table: list[int], position: int, block_size: int) -> int:
+    """Cache slot of `position`: page * block_size + offset (atomserve/runner.py:37-39)."""
+    return block_table[position // block_size] * block_size + position % block_size
+
+
+def _round_up(n: int, to: int) -> int:
+    return -(-n // to) * to
+
+
+class _Packed:
+    """Lays several int32 arrays out in one buffer; the same names and sizes give the same
+    offsets, so a captured graph finds its inputs where it left them."""
+
+    def __init__(self):
+        self.parts: list[tuple[str, int, int]] = []
+        self.size = 0
+
+    def add(self, name: str, length: int) -> None:
+        self.parts.append((name, self.size, length))
+        self.size += _round_up(max(length, 1), 4)  # 16-byte aligned parts
+
+    def views(self, buffer: torch.Tensor) -> dict[str, torch.Tensor]:
+        return {name: buffer[off : off + n] for name, off, n in self.parts}
+
+
+class ModelRunner:
+    def __init__(self, model: DecoderModel, cache: CacheManager, max_batched_tokens: int = 8192,
+                 cuda_graphs: bool = True):  # fmt: skip
+        self.model, self.cache = model, cache
+        self.device = model.device
+        self.block_size = cache.block_size
+        self.views: list[CacheView | None] = [cache.entry_view(i) for i in range(len(model.schedule))]
+        # Graphs replay the same kernels on new inputs; a part that updates state of its own in
+        # place would be run again by capture and warm-up, so such models step eagerly.
+        self.use_graphs = cuda_graphs and self.device.type == "cuda" and not cache.entry_state
+        self._copy_done: torch.cuda.Event | None = None
+        self._graphs: dict[tuple, tuple] = {}
+        self._host: torch.Tensor | None = None
+        self._dev: torch.Tensor | None = None
+        self.num_launches_hint = 0
+
+    # ---- building the batch ---------------------------------------------------------------------
+
+    def validate(self, rows: list[Row]) -> None:
+        bs = self.block_size
+        vocab = self.model.spec.vocab_size
+        for r in rows:
+            n = len(r.tokens)
+            if n < 1:
+                raise ValueError("a row must bring at least one token")
+            if min(r.tokens) < 0 or max(r.tokens) >= vocab:
+                raise ValueError(f"a token id lies outside [0, {vocab})")
+            if r.start < 0:
+                raise ValueError(f"a row starts at position {r.start}")
+            if any(not 0 <= w < n for w in r.want):
+                raise ValueError(f"wanted places {r.want} lie outside the row's {n} tokens")
+            if len(r.cache.block_tables) != len(self.cache.groups):
+                raise ValueError("the row's request has block tables for another set of cache groups")
+            for g, table in zip(self.cache.groups, r.cache.block_tables):
+                if (r.start + n) > len(table) * bs:
+                    raise ValueError(f"block table holds {len(table) * bs} slots, the row needs {r.start + n}")
+                first = self.cache.first_needed_block(g, r.start)
+                if any(b < 0 for b in table[first : -(-(r.start + n) // bs)]):
+                    raise ValueError("a page the row still reads has been released")
+
+    def _layout(self, T: int, R: int, W: list[int], B: int) -> _Packed:
+        lay = _Packed()
+        lay.add("token_ids", T)
+        lay.add("positions", T)
+        lay.add("req_q_start", R + 1)
+        lay.add("req_pos_start", R)
+        lay.add("state_slots", R)
+        lay.add("logits_rows", B)
+        for g, w in enumerate(W):
+            lay.add(f"slots{g}", T)
+            lay.add(f"tables{g}", R * w)
+        return lay
+
+    def _buffers(self, size: int) -> tuple[torch.Tensor, torch.Tensor]:
+        if self._host is None or self._host.shape[0] < size:
+            cap = max(size, 1 << 16)
+            pin = self.device.type == "cuda"
+            self._host = torch.empty(cap, dtype=torch.int32, pin_memory=pin)
+            self._dev = torch.empty(cap, dtype=torch.int32, device=self.device)
+            self._graphs.clear()  # captured graphs point into the old buffer
+        return self._host, self._dev
+
+    def prepare(self, rows: list[Row], pad_requests: int | None = None, pad_width: int | None = None):
+        """Pack the rows; returns (ctx, per-group (slots, tables), layout key)."""
+        self.validate(rows)
+        bs = self.block_size
+        R = len(rows)
+        T = sum(len(r.tokens) for r in rows)
+        widths = []
+        for g in range(len(self.cache.groups)):
+            w = max(-(-(r.start + len(r.tokens)) // bs) for r in rows)
+            widths.append(pad_width if pad_width is not None else w)
+        B = sum(len(r.want) for r in rows)
+        lay = self._layout(T, R, widths, B)
+        host, dev = self._buffers(lay.size)
+        if self._copy_done is not None:
+            self._copy_done.synchronize()  # the last step's upload has left the host buffer
+        hv = lay.views(host)
+        tok, pos = hv["token_ids"].numpy(), hv["positions"].numpy()
+        qs, ps, ss, lr = (hv[k].numpy() for k in ("req_q_start", "req_pos_start", "state_slots", "logits_rows"))
+        flat = b = 0
+        max_context = 0
+        for i, r in enumerate(rows):
+            n = len(r.tokens)
+            tok[flat : flat + n] = r.tokens
+            pos[flat : flat + n] = range(r.start, r.start + n)
+            qs[i], ps[i], ss[i] = flat, r.start, r.cache.state_slot
+            for w in r.want:
+                lr[b] = flat + w
+                b += 1
+            flat += n
+            max_context = max(max_context, r.start + n)
+        qs[R] = flat
+        for g, width in enumerate(widths):
+            slots, tables = hv[f"slots{g}"].numpy(), hv[f"tables{g}"].numpy().reshape(R, width)
+            flat = 0
+            for i, r in enumerate(rows):
+                table = r.cache.block_tables[g]
+                n = len(r.tokens)
+                used = min(len(table), width)
+                tables[i, :used] = table[:used]
+                tables[i, used:] = 0
+                p = np.arange(r.start, r.start + n)
+                slots[flat : flat + n] = np.asarray(table, dtype=np.int64)[p // bs] * bs + p % bs
+                flat += n
+        dev[: lay.size].copy_(host[: lay.size], non_blocking=True)
+        if self.device.type == "cuda":
+            self._copy_done = torch.cuda.Event()
+            self._copy_done.record()
+        dv = lay.views(dev)
+        ctx = StepContext(
+            num_tokens=T, num_requests=R, token_ids=dv["token_ids"], positions=dv["positions"],
+            req_q_start=dv["req_q_start"], req_pos_start=dv["req_pos_start"],
+            state_slots=dv["state_slots"], logits_rows=dv["logits_rows"], max_context=max_context,
+            host_q_lens=[len(r.tokens) for r in rows], host_pos_start=[r.start for r in rows],
+            host_state_slots=[r.cache.state_slot for r in rows],
+        )  # fmt: skip
+        groups = [(dv[f"slots{g}"], dv[f"tables{g}"].view(R, w)) for g, w in enumerate(widths)]
+        return ctx, groups, (T, R, tuple(widths), B)
+
+    def _bind(self, groups) -> None:
+        for i, view in enumerate(self.views):
+            if view is not None and i in self.cache.entry_group:
+                g, _ = self.cache.entry_group[i]
+                view.slots, view.block_tables = groups[g]
+
+    # ---- running --------------------------------------------------------------------------------
+
+    @torch.inference_mode()
+    def step(self, rows: list[Row]) -> torch.Tensor:
+        """Run one step; float32 logits [sum(len(row.want)), vocab]."""
+        if not rows:
+            return torch.empty(0, self.model.spec.vocab_size, device=self.device, dtype=torch.float32)
+        if self.use_graphs and all(len(r.tokens) == 1 for r in rows):
+            return self._step_graph(rows)
+        ctx, groups, _ = self.prepare(rows)
+        self._bind(groups)
+        return self.model.forward(ctx, self.views)
+
+    def _step_graph(self, rows: list[Row]) -> torch.Tensor:
+        """Decode-only step through a captured graph. The graph is keyed by everything that
+        fixes kernel shapes and buffer offsets: tokens, table width (rounded up to a bucket),
+        wanted rows, and the bucket of the longest context (which sets the key partitions)."""
+        bs = self.block_size
+        need_w = max(-(-(r.start + 1) // bs) for r in rows)
+        pad_w = 16
+        while pad_w < need_w:
+            pad_w *= 2
+        ctx, groups, key = self.prepare(rows, pad_width=pad_w)
+        ctx_bucket = 256
+        while ctx_bucket < ctx.max_context:
+            ctx_bucket *= 2
+        ctx.max_context = ctx_bucket
+        key = (*key, ctx_bucket)
+        self._bind(groups)
+        entry = self._graphs.get(key)
+        if entry is None:
+            # warm up outside capture (lazy library initialisation must not be captured)
+            self.model.forward(ctx, self.views)
+            torch.cuda.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                out = self.model.forward(ctx, self.views)
+            entry = (graph, out)
+            self._graphs[key] = entry
+        graph, out = entry
+        graph.replay()
+        return out

@@ -1,0 +1,25 @@
+"""Python faces of the CUDA kernels. Each function checks its tensors, allocates the output
+and launches on the current stream. float32 tensors run the true 32-bit kernels, bfloat16
+tensors the serving kernels; nothing here computes on the CPU."""
+
+from atomserve_b200.ops.attention import attention_tile_shape, paged_attention
+from atomserve_b200.ops.elementwise import embedding, qk_norm_rope_store, rms_norm, rotary, silu_mul
+from atomserve_b200.ops.library import KernelLibraryError, require_device
+from atomserve_b200.ops.linear import linear
+from atomserve_b200.ops.sampling import argmax_rows, presence_penalty, sample_rows
+
+__all__ = [
+    "KernelLibraryError",
+    "argmax_rows",
+    "attention_tile_shape",
+    "embedding",
+    "linear",
+    "paged_attention",
+    "presence_penalty",
+    "qk_norm_rope_store",
+    "require_device",
+    "rms_norm",
+    "rotary",
+    "sample_rows",
+    "silu_mul",
+]

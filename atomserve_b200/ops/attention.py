@@ -1,0 +1,85 @@
+"""Paged grouped-query attention over cache pages for a flat batch of requests."""
+
+from __future__ import annotations
+
+import ctypes
+
+import torch
+
+from atomserve_b200.ops.library import KernelLibraryError, check, dtype_code, lib, ptr, require_cuda, stream
+
+KEY_TILE = 32
+TARGET_BLOCKS = 296  # two blocks for each of the 148 SMs before the key range is split
+
+
+def attention_tile_shape(group: int) -> tuple[int, int]:
+    """(tokens per query tile, query heads per block) for `group` query heads per kv head."""
+    qt, gc = ctypes.c_int(), ctypes.c_int()
+    lib().asb_attention_tile_shape(group, ctypes.byref(qt), ctypes.byref(gc))
+    return qt.value, gc.value
+
+
+def plan_partitions(num_tokens: int, num_requests: int, num_kv_heads: int, group: int,
+                    max_context: int, window: int) -> tuple[int, int]:  # fmt: skip
+    """(partition size, partitions): split the keys only when the batch alone cannot fill the GPU.
+
+    Partitions are aligned to absolute key positions, so the choice never changes which keys a
+    row sees, only how its sum is grouped."""
+    qt, gc = attention_tile_shape(group)
+    blocks = (-(-num_tokens // qt) + num_requests) * num_kv_heads * -(-group // gc)
+    span = max_context if window <= 0 else min(max_context, window + qt - 1)
+    if blocks >= TARGET_BLOCKS or span <= 256:
+        return 1 << 30, 1
+    want = -(-TARGET_BLOCKS // blocks)
+    size = max(256, -(-(-(-span // want)) // 256) * 256)
+    if window <= 0:
+        parts = (max_context - 1) // size + 1
+    else:
+        parts = min((max_context - 1) // size + 1, -(-span // size) + 1)
+    return (size, parts) if parts > 1 else (1 << 30, 1)
+
+
+def paged_attention(
+    q: torch.Tensor,
+    k_cache: torch.Tensor,
+    v_cache: torch.Tensor,
+    block_tables: torch.Tensor,
+    req_q_start: torch.Tensor,
+    req_pos_start: torch.Tensor,
+    *,
+    num_requests: int,
+    max_context: int,
+    window: int | None,
+    scale: float,
+    partitions: tuple[int, int] | None = None,
+) -> torch.Tensor:
+    """softmax(q k^T * scale) v for every new token, keys read in place from the pages.
+
+    q: [T, H, hd]; k_cache, v_cache: [num_blocks, KV, block_size, hd]; block_tables: [R, W]
+    int32; req_q_start: [R + 1] int32 (rows of each request in q); req_pos_start: [R] int32.
+    max_context: the largest position + 1 any request reaches in this step (host int).
+    A query at position p sees keys j <= p of its request, and j > p - window with a window.
+    """
+    require_cuda(q, k_cache, v_cache, block_tables, req_q_start, req_pos_start)
+    T, H, hd = q.shape
+    KV, bs = k_cache.shape[1], k_cache.shape[2]
+    if not q.is_contiguous() or k_cache.shape != v_cache.shape or k_cache.shape[3] != hd:
+        raise KernelLibraryError("paged_attention: q must be contiguous and the caches [blocks, KV, bs, hd]")
+    if k_cache.dtype != q.dtype or v_cache.dtype != q.dtype:
+        raise KernelLibraryError("paged_attention: cache and query dtypes differ")
+    for t in (block_tables, req_q_start, req_pos_start):
+        if t.dtype != torch.int32 or not t.is_contiguous():
+            raise KernelLibraryError("paged_attention: index tensors must be contiguous int32")
+    win = int(window) if window else 0
+    ps, np_ = partitions or plan_partitions(T, num_requests, KV, H // KV, max_context, win)
+    out = torch.empty_like(q)
+    part_m = part_l = part_acc = None
+    if np_ > 1:
+        part_m = torch.empty(T * H * np_, device=q.device, dtype=torch.float32)
+        part_l = torch.empty_like(part_m)
+        part_acc = torch.empty(T * H * np_ * hd, device=q.device, dtype=torch.float32)
+    check(lib().asb_paged_attention(
+        ptr(out), ptr(q), ptr(k_cache), ptr(v_cache), ptr(block_tables), ptr(req_q_start),
+        ptr(req_pos_start), ptr(part_m), ptr(part_l), ptr(part_acc), T, num_requests, H, KV, hd, bs,
+        block_tables.shape[1], win, ps, np_, float(scale), dtype_code(q), stream()))  # fmt: skip
+    return out

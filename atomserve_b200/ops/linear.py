@@ -1,0 +1,50 @@
+"""y = x W^T (+ residual), weights in checkpoint layout [out_features, in_features].
+
+float32 operands run this package's CUDA-core kernel with float32 multiply-adds (no tensor-core
+mode of reduced precision). bfloat16 operands go to the vendor GEMM library through torch, as
+the reference engine does for its matrix products (atomserve/quant.py:89-91); the float32
+result form (`out_dtype=torch.float32`, for logits) asks the library for its float32
+accumulator, so logits are never rounded to bfloat16.
+"""
+
+from __future__ import annotations
+
+import torch
+
+from atomserve_b200.ops.library import KernelLibraryError, check, dtype_code, lib, ptr, require_cuda, stream
+
+
+def gemm_simt(x: torch.Tensor, w: torch.Tensor, residual: torch.Tensor | None, out_dtype: torch.dtype) -> torch.Tensor:
+    M, K = x.shape
+    N = w.shape[0]
+    out = torch.empty(M, N, device=x.device, dtype=out_dtype)
+    check(lib().asb_gemm_simt(ptr(out), ptr(x), ptr(w), ptr(residual), M, N, K, dtype_code(x),
+                              dtype_code(out), stream()))  # fmt: skip
+    return out
+
+
+def linear(
+    x: torch.Tensor,
+    w: torch.Tensor,
+    residual: torch.Tensor | None = None,
+    out_dtype: torch.dtype | None = None,
+) -> torch.Tensor:
+    require_cuda(x, w, residual)
+    if x.dim() != 2 or w.dim() != 2 or x.shape[1] != w.shape[1]:
+        raise KernelLibraryError(f"linear: x {tuple(x.shape)} does not match w {tuple(w.shape)}")
+    if x.dtype != w.dtype or not x.is_contiguous() or not w.is_contiguous():
+        raise KernelLibraryError("linear: x and w must be contiguous and of one dtype")
+    out_dtype = out_dtype or x.dtype
+    if residual is not None and (residual.shape != (x.shape[0], w.shape[0]) or residual.dtype != out_dtype or not residual.is_contiguous()):
+        raise KernelLibraryError("linear: residual must be [M, N], contiguous, in the output dtype")
+    if x.dtype == torch.float32:
+        if out_dtype != torch.float32:
+            raise KernelLibraryError("linear: float32 operands give float32 results")
+        return gemm_simt(x, w, residual, torch.float32)
+    if out_dtype == torch.float32:
+        if residual is not None:
+            return gemm_simt(x, w, residual, torch.float32)
+        return torch.mm(x, w.t(), out_dtype=torch.float32)  # float32 accumulator, not rounded
+    if residual is None:
+        return torch.mm(x, w.t())
+    return torch.addmm(residual, x, w.t())

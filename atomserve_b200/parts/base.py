@@ -1,0 +1,187 @@
+"""Interfaces of the parts a model is assembled from, their registries, and the per-step
+context they compute in.
+
+A part is built from its `PartSpec` parameters and the model's hidden size; it names the
+checkpoint tensors it needs, receives them once, and computes on the flat batch. No part
+knows which model it is in or which layer it is.
+
+  Norm            forward(x, rows=None) -> same width
+  PositionEncoding  what a mixer needs to encode positions (for rotary: inverse frequencies)
+  Mixer           forward(h, residual, ctx, cache, write_cache) -> residual + mix(h);
+                  cache_spec() says what it keeps between steps (pages of keys and values,
+                  fixed-size state, or nothing)
+  FeedForward     forward(h, residual, ctx) -> residual + ff(h)
+  Block           arranges a mixer and a feed-forward with their norms around the residual
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Any, Callable
+
+import torch
+
+from atomserve_b200.parts.spec import PartSpec, TensorSpec
+
+
+# ---- what a mixer keeps between steps -------------------------------------------------------
+
+
+@dataclass(frozen=True)
+class KVCacheSpec:
+    """Pages of keys and values: per token `num_kv_heads * head_dim` of each. `window`: only the
+    last `window` positions are ever read, so older pages can be given back early."""
+
+    num_kv_heads: int
+    head_dim: int
+    window: int | None = None
+
+
+@dataclass(frozen=True)
+class StateSpec:
+    """Fixed-size per-request state: one tensor of `shape` per request slot, zero at admission."""
+
+    name: str
+    shape: tuple[int, ...]
+    dtype: torch.dtype = torch.float32
+
+
+@dataclass
+class CacheView:
+    """What one entry of the run order sees of the cache during a step.
+
+    For paged keys/values: `k`, `v` are [num_blocks, KV, block_size, head_dim]; `slots` [T] int32
+    says where each new token is written; `block_tables` [R, W] int32 where each request's
+    positions live. For state: `state[name]` is [num_slots, *shape], indexed by ctx.state_slots.
+    """
+
+    k: torch.Tensor | None = None
+    v: torch.Tensor | None = None
+    slots: torch.Tensor | None = None
+    block_tables: torch.Tensor | None = None
+    block_size: int = 0
+    state: dict[str, torch.Tensor] = field(default_factory=dict)
+
+
+# ---- the step's batch as parts see it -------------------------------------------------------
+
+
+@dataclass
+class StepContext:
+    """One step's flat batch: T new tokens of R requests, each request's tokens contiguous.
+
+    Device tensors are int32. Host copies (`host_*`) are for parts that plan on the host.
+    """
+
+    num_tokens: int
+    num_requests: int
+    token_ids: torch.Tensor  # [T]
+    positions: torch.Tensor  # [T] absolute position of each token in its request
+    req_q_start: torch.Tensor  # [R + 1] first row of each request
+    req_pos_start: torch.Tensor  # [R] position of each request's first new token
+    state_slots: torch.Tensor  # [R] per-request state slot
+    logits_rows: torch.Tensor  # [B'] rows whose logits are wanted
+    max_context: int  # largest position + 1 reached by any request in this step
+    host_q_lens: list[int] = field(default_factory=list)
+    host_pos_start: list[int] = field(default_factory=list)
+    host_state_slots: list[int] = field(default_factory=list)
+
+
+# ---- interfaces -----------------------------------------------------------------------------
+
+
+class Part:
+    """Common to all parts: the tensors it needs and how it takes them."""
+
+    def tensor_specs(self) -> list[TensorSpec]:
+        return []
+
+    def load(self, tensors: dict[str, torch.Tensor]) -> None:
+        """Receive the tensors named by tensor_specs (on the device, in their final dtype)."""
+
+
+class Norm(Part):
+    def forward(self, x: torch.Tensor, rows: torch.Tensor | None = None) -> torch.Tensor:
+        raise NotImplementedError
+
+
+class PositionEncoding(Part):
+    """How positions enter a mixer. `prepare(device)` builds its tables once."""
+
+    def prepare(self, device: torch.device) -> None:
+        pass
+
+
+class Mixer(Part):
+    def cache_spec(self) -> KVCacheSpec | None:
+        return None
+
+    def state_specs(self) -> list[StateSpec]:
+        return []
+
+    def forward(self, h: torch.Tensor, residual: torch.Tensor, ctx: StepContext,
+                cache: CacheView | None, write_cache: bool = True) -> torch.Tensor:  # fmt: skip
+        raise NotImplementedError
+
+
+class FeedForward(Part):
+    def forward(self, h: torch.Tensor, residual: torch.Tensor, ctx: StepContext) -> torch.Tensor:
+        raise NotImplementedError
+
+
+class Block(Part):
+    def __init__(self, mixer: Mixer, feed_forward: FeedForward, mixer_norm: Norm, feed_forward_norm: Norm):
+        self.mixer, self.feed_forward = mixer, feed_forward
+        self.mixer_norm, self.feed_forward_norm = mixer_norm, feed_forward_norm
+
+    def parts(self) -> list[Part]:
+        return [self.mixer_norm, self.mixer, self.feed_forward_norm, self.feed_forward]
+
+    def tensor_specs(self) -> list[TensorSpec]:
+        return [s for p in self.parts() for s in p.tensor_specs()]
+
+    def load(self, tensors: dict[str, torch.Tensor]) -> None:
+        for p in self.parts():
+            p.load(tensors)
+
+    def forward(self, x: torch.Tensor, ctx: StepContext, cache: CacheView | None,
+                write_cache: bool = True) -> torch.Tensor:  # fmt: skip
+        raise NotImplementedError
+
+
+# ---- registries ------------------------------------------------------------------------------
+
+_REGISTRIES: dict[str, dict[str, Callable[..., Any]]] = {
+    "norm": {}, "position": {}, "mixer": {}, "feed_forward": {}, "block": {}, "embedding": {}, "head": {},
+}  # fmt: skip
+
+
+def register_part(family: str, kind: str, factory: Callable[..., Any]) -> None:
+    """Make `kind` buildable. `factory(hidden_size=..., prefix=..., **params)` returns the part
+    (a block's factory takes the four built parts instead)."""
+    if family not in _REGISTRIES:
+        raise KeyError(f"unknown part family {family!r}; families: {sorted(_REGISTRIES)}")
+    _REGISTRIES[family][kind] = factory
+
+
+def build_part(family: str, spec: PartSpec, hidden_size: int) -> Any:
+    _ensure_builtin()
+    try:
+        factory = _REGISTRIES[family][spec.kind]
+    except KeyError:
+        raise KeyError(f"no {family} part of kind {spec.kind!r}; known: {sorted(_REGISTRIES[family])}") from None
+    return factory(hidden_size=hidden_size, prefix=spec.prefix, **spec.params)
+
+
+def build_block(kind: str, mixer: Mixer, feed_forward: FeedForward, mixer_norm: Norm, feed_forward_norm: Norm) -> Block:
+    _ensure_builtin()
+    try:
+        factory = _REGISTRIES["block"][kind]
+    except KeyError:
+        raise KeyError(f"no block of kind {kind!r}; known: {sorted(_REGISTRIES['block'])}") from None
+    return factory(mixer, feed_forward, mixer_norm, feed_forward_norm)
+
+
+def _ensure_builtin() -> None:
+    if "rms_norm" not in _REGISTRIES["norm"]:
+        from atomserve_b200.parts import attention, block, embedding, mlp, norms, rotary  # noqa: F401

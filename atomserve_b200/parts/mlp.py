@@ -1,0 +1,37 @@
+"""Dense SwiGLU feed-forward: residual + down( silu(gate(h)) * up(h) ), no biases
+(atomserve/model.py:339-360)."""
+
+from __future__ import annotations
+
+import torch
+
+from atomserve_b200 import ops
+from atomserve_b200.parts.base import FeedForward, StepContext, register_part
+from atomserve_b200.parts.spec import TensorSpec
+
+
+class SwiGLU(FeedForward):
+    def __init__(self, hidden_size: int, prefix: str, intermediate_size: int):
+        self.hidden_size, self.prefix, self.intermediate_size = hidden_size, prefix, intermediate_size
+        self.gate_up_proj = self.down_proj = None
+
+    def tensor_specs(self) -> list[TensorSpec]:
+        p, d, i = self.prefix, self.hidden_size, self.intermediate_size
+        return [
+            TensorSpec(p + "gate_proj.weight", (i, d)),
+            TensorSpec(p + "up_proj.weight", (i, d)),
+            TensorSpec(p + "down_proj.weight", (d, i)),
+        ]
+
+    def load(self, tensors: dict[str, torch.Tensor]) -> None:
+        p = self.prefix
+        # gate rows first, then up rows (atomserve/loader.py:121)
+        self.gate_up_proj = torch.cat([tensors[p + "gate_proj.weight"], tensors[p + "up_proj.weight"]]).contiguous()
+        self.down_proj = tensors[p + "down_proj.weight"]
+
+    def forward(self, h: torch.Tensor, residual: torch.Tensor, ctx: StepContext) -> torch.Tensor:
+        hidden = ops.silu_mul(ops.linear(h, self.gate_up_proj))
+        return ops.linear(hidden, self.down_proj, residual)
+
+
+register_part("feed_forward", "swiglu", SwiGLU)

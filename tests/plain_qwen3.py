@@ -77,30 +77,36 @@ def attention(
     return torch.einsum("hts,shd->thd", probs, v)
 
 
+def _same(x: torch.Tensor) -> torch.Tensor:
+    return x
+
+
 def attention_block(
-    x: torch.Tensor, w: dict, prefix: str, cfg: dict, positions: torch.Tensor, window: int | None
-) -> torch.Tensor:
+    x: torch.Tensor, w: dict, prefix: str, cfg: dict, positions: torch.Tensor, window: int | None,
+    rnd=_same,
+) -> torch.Tensor:  # fmt: skip
     """q/k/v projections, per-head RMSNorm of q and k before RoPE (one [hd] gain for all
-    heads, v untouched), attention, output projection. atomserve/model.py:292-336."""
+    heads, v untouched), attention, output projection. atomserve/model.py:292-336.
+    `rnd` rounds every intermediate result (see `forward`)."""
     T = x.shape[0]
     H, KV, hd = cfg["num_attention_heads"], cfg["num_key_value_heads"], head_dim_of(cfg)
-    q = (x @ w[prefix + "self_attn.q_proj.weight"].T).view(T, H, hd)
-    k = (x @ w[prefix + "self_attn.k_proj.weight"].T).view(T, KV, hd)
-    v = (x @ w[prefix + "self_attn.v_proj.weight"].T).view(T, KV, hd)
-    q = rms_norm(q, w[prefix + "self_attn.q_norm.weight"], cfg["rms_norm_eps"])
-    k = rms_norm(k, w[prefix + "self_attn.k_norm.weight"], cfg["rms_norm_eps"])
+    q = rnd(x @ w[prefix + "self_attn.q_proj.weight"].T).view(T, H, hd)
+    k = rnd(x @ w[prefix + "self_attn.k_proj.weight"].T).view(T, KV, hd)
+    v = rnd(x @ w[prefix + "self_attn.v_proj.weight"].T).view(T, KV, hd)
+    q = rnd(rms_norm(q, w[prefix + "self_attn.q_norm.weight"], cfg["rms_norm_eps"]))
+    k = rnd(rms_norm(k, w[prefix + "self_attn.k_norm.weight"], cfg["rms_norm_eps"]))
     angles = rope_angles(positions, hd, cfg["rope_theta"])
-    q, k = apply_rope(q, angles), apply_rope(k, angles)
-    out = attention(q, k, v, window)
+    q, k = rnd(apply_rope(q, angles)), rnd(apply_rope(k, angles))
+    out = rnd(attention(q, k, v, window))
     return out.reshape(T, H * hd) @ w[prefix + "self_attn.o_proj.weight"].T
 
 
-def swiglu_mlp(x: torch.Tensor, w: dict, prefix: str) -> torch.Tensor:
+def swiglu_mlp(x: torch.Tensor, w: dict, prefix: str, rnd=_same) -> torch.Tensor:
     """down( silu(gate(x)) * up(x) ), silu(g) = g / (1 + exp(-g)). atomserve/model.py:339-360,
     atomserve/kernels.py:447-448."""
-    gate = x @ w[prefix + "mlp.gate_proj.weight"].T
-    up = x @ w[prefix + "mlp.up_proj.weight"].T
-    return ((gate / (1.0 + torch.exp(-gate))) * up) @ w[prefix + "mlp.down_proj.weight"].T
+    gate = rnd(x @ w[prefix + "mlp.gate_proj.weight"].T)
+    up = rnd(x @ w[prefix + "mlp.up_proj.weight"].T)
+    return rnd((gate / (1.0 + torch.exp(-gate))) * up) @ w[prefix + "mlp.down_proj.weight"].T
 
 
 def head_dim_of(cfg: dict) -> int:
@@ -116,23 +122,31 @@ def layer_window(cfg: dict, layer: int) -> int | None:
     return None
 
 
-def forward(w: dict, cfg: dict, ids: list[int], dtype: torch.dtype = torch.float32) -> torch.Tensor:
+def forward(
+    w: dict, cfg: dict, ids: list[int], dtype: torch.dtype = torch.float32,
+    activations: torch.dtype | None = None,
+) -> torch.Tensor:  # fmt: skip
     """Logits at every position of one whole sequence: [len(ids), vocab].
 
     Embedding gather without scaling; per layer x = x + attn(norm(x)), x = x + mlp(norm(x));
     final norm; lm_head, which is the embedding when tie_word_embeddings.
-    atomserve/model.py:363-385, atomserve/loader.py:131-138."""
+    atomserve/model.py:363-385, atomserve/loader.py:131-138.
+
+    `activations=torch.bfloat16` rounds the result of every operation to bfloat16, as the
+    reference's PyTorch path does when it serves in bf16 (atomserve/cli.py:56-60): the
+    yardstick for how far a bfloat16 engine may lie from the float32 logits."""
     w = {name: t.to(dtype) for name, t in w.items()}
+    rnd = _same if activations is None else (lambda t: t.to(activations).to(dtype))
     eps = cfg["rms_norm_eps"]
     positions = torch.arange(len(ids))
     x = w["model.embed_tokens.weight"][torch.tensor(ids, dtype=torch.long)]
     for i in range(cfg["num_hidden_layers"]):
         p = f"model.layers.{i}."
-        h = rms_norm(x, w[p + "input_layernorm.weight"], eps)
-        x = x + attention_block(h, w, p, cfg, positions, layer_window(cfg, i))
-        h = rms_norm(x, w[p + "post_attention_layernorm.weight"], eps)
-        x = x + swiglu_mlp(h, w, p)
-    x = rms_norm(x, w["model.norm.weight"], eps)
+        h = rnd(rms_norm(x, w[p + "input_layernorm.weight"], eps))
+        x = rnd(x + attention_block(h, w, p, cfg, positions, layer_window(cfg, i), rnd))
+        h = rnd(rms_norm(x, w[p + "post_attention_layernorm.weight"], eps))
+        x = rnd(x + swiglu_mlp(h, w, p, rnd))
+    x = rnd(rms_norm(x, w["model.norm.weight"], eps))
     head = "model.embed_tokens.weight" if cfg.get("tie_word_embeddings", False) else "lm_head.weight"
     return x @ w[head].T
 

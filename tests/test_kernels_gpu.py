@@ -1,0 +1,327 @@
+"""Each CUDA kernel alone against its plain reference, at sizes other than the engine's."""
+
+import math
+
+import pytest
+import torch
+
+import plain_qwen3 as plain
+
+pytestmark = pytest.mark.gpu
+DTYPES = [torch.float32, torch.bfloat16]
+
+
+def tol(dtype):
+    return dict(atol=1e-5, rtol=1e-5) if dtype == torch.float32 else dict(atol=2e-2, rtol=2e-2)
+
+
+@pytest.fixture(scope="module")
+def ops():
+    from atomserve_b200 import ops
+
+    ops.require_device()
+    return ops
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("width", [48, 100, 4096])
+def test_embedding(ops, dtype, width):
+    table = torch.randn(331, width, device="cuda").to(dtype)
+    ids = torch.tensor([0, 330, 7, 7, 19], dtype=torch.int32, device="cuda")
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    out = ops.embedding(ids, table, status)
+    assert torch.equal(out, table[ids.long()])
+    assert int(status) == 0
+    bad = torch.tensor([3, 331], dtype=torch.int32, device="cuda")
+    out = ops.embedding(bad, table, status)
+    assert int(status) == 1 and torch.equal(out[1], torch.zeros_like(out[1]))
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("rows,width,eps", [(1, 16, 1e-6), (7, 100, 1e-5), (33, 4096, 1e-6), (3, 5120, 3e-6)])
+def test_rms_norm(ops, dtype, rows, width, eps):
+    x = (torch.randn(rows, width, device="cuda") * 3).to(dtype)
+    gain = 1 + 0.1 * torch.randn(width, device="cuda")
+    ref = plain.rms_norm(x.float().cpu(), gain.cpu(), eps)
+    out = ops.rms_norm(x, gain, eps)
+    assert torch.allclose(out.float().cpu(), ref, **tol(dtype))
+    pick = torch.tensor([rows - 1, 0], dtype=torch.int32, device="cuda")
+    out = ops.rms_norm(x, gain, eps, pick)
+    assert torch.allclose(out.float().cpu(), ref[[rows - 1, 0]], **tol(dtype))
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("rows,inter", [(1, 24), (7, 176), (300, 12288)])
+def test_silu_mul(ops, dtype, rows, inter):
+    gu = (torch.randn(rows, 2 * inter, device="cuda") * 2).to(dtype)
+    g, u = gu.float().cpu()[:, :inter], gu.float().cpu()[:, inter:]
+    ref = g / (1 + torch.exp(-g)) * u
+    assert torch.allclose(ops.silu_mul(gu).float().cpu(), ref, **tol(dtype))
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("M,N,K", [(1, 64, 64), (5, 100, 37), (70, 130, 259), (128, 512, 1024)])
+def test_linear(ops, dtype, M, N, K):
+    x = torch.randn(M, K, device="cuda").to(dtype)
+    w = (torch.randn(N, K, device="cuda") / math.sqrt(K)).to(dtype)
+    res = torch.randn(M, N, device="cuda").to(dtype)
+    ref = x.double().cpu() @ w.double().cpu().T
+    t = dict(atol=1e-5, rtol=1e-5) if dtype == torch.float32 else dict(atol=3e-2, rtol=2e-2)
+    assert torch.allclose(ops.linear(x, w).double().cpu(), ref, **t)
+    assert torch.allclose(ops.linear(x, w, res).double().cpu(), ref + res.double().cpu(), **t)
+    full = ops.linear(x, w, out_dtype=torch.float32)
+    assert full.dtype == torch.float32
+    assert torch.allclose(full.double().cpu(), ref, atol=1e-3 if dtype == torch.bfloat16 else 1e-5, rtol=1e-3)
+
+
+def test_linear_rows_do_not_depend_on_the_batch(ops):
+    """float32: a row's result is bit-equal whether it runs alone or among others."""
+    x = torch.randn(70, 259, device="cuda")
+    w = torch.randn(130, 259, device="cuda")
+    whole = ops.linear(x, w)
+    assert torch.equal(ops.linear(x[17:18].contiguous(), w), whole[17:18])
+    assert torch.equal(ops.linear(x[60:].contiguous(), w), whole[60:])
+
+
+def rope_reference(x, positions, hd, theta, rotary_dim=None):
+    rd = rotary_dim or hd
+    angles = plain.rope_angles(positions, rd, theta)
+    rotated = plain.apply_rope(x[..., :rd], angles)
+    return torch.cat([rotated, x[..., rd:]], dim=-1)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("hd,rd,theta", [(16, 16, 1e4), (48, 48, 5e4), (128, 128, 1e6), (256, 64, 1e4)])
+def test_rotary_alone(ops, dtype, hd, rd, theta):
+    from atomserve_b200.parts.rotary import Rotary
+
+    rot = Rotary(hidden_size=0, prefix="", head_dim=hd, theta=theta, rotary_dim=rd)
+    rot.prepare(torch.device("cuda"))
+    pos = torch.tensor([0, 1, 300, 4097, 39999], dtype=torch.int32, device="cuda")
+    x = torch.randn(5, 3, hd, device="cuda").to(dtype)
+    ref = rope_reference(x.float().cpu(), pos.cpu().long(), hd, theta, rd)
+    out = rot.apply(x, pos)
+    assert torch.allclose(out.float().cpu(), ref, **(dict(atol=2e-4, rtol=1e-4) if dtype == torch.float32 else tol(dtype)))
+    assert torch.equal(out[0], x[0])  # position 0 is the identity
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("H,KV,hd,bs", [(4, 2, 16, 16), (5, 1, 48, 8), (32, 8, 128, 16), (16, 16, 80, 4)])
+def test_qk_norm_rope_store(ops, dtype, H, KV, hd, bs):
+    T, nblocks, eps, theta = 6, 9, 1e-5, 1e6
+    qkv = torch.randn(T, (H + 2 * KV) * hd, device="cuda").to(dtype)
+    qg, kg = (1 + 0.1 * torch.randn(hd, device="cuda") for _ in range(2))
+    inv_freq = plain.rope_inv_freq(hd, theta).cuda()
+    pos = torch.tensor([0, 1, 300, 4097, 39999, 17], dtype=torch.int32, device="cuda")
+    slot_list = [bs * 7 + 1, 0, bs * 3 + bs - 1, 5 % bs + bs * 2, bs * 8, -1]
+    slots = torch.tensor(slot_list, dtype=torch.int32, device="cuda")
+    kc = torch.zeros(nblocks, KV, bs, hd, device="cuda", dtype=dtype)
+    vc = torch.zeros_like(kc)
+    q = ops.qk_norm_rope_store(qkv, H, KV, hd, pos, q_gain=qg, k_gain=kg, eps=eps, inv_freq=inv_freq,
+                               rotary_dim=hd, slots=slots, k_cache=kc, v_cache=vc)  # fmt: skip
+    x = qkv.float().cpu().view(T, H + 2 * KV, hd)
+    angles = plain.rope_angles(pos.cpu().long(), hd, theta)
+    q_ref = plain.apply_rope(plain.rms_norm(x[:, :H], qg.cpu(), eps), angles)
+    k_ref = plain.apply_rope(plain.rms_norm(x[:, H : H + KV], kg.cpu(), eps), angles)
+    t = dict(atol=3e-4, rtol=1e-4) if dtype == torch.float32 else tol(dtype)
+    assert torch.allclose(q.float().cpu(), q_ref, **t)
+    kflat = kc.float().cpu().permute(0, 2, 1, 3).reshape(nblocks * bs, KV, hd)
+    vflat = vc.cpu().permute(0, 2, 1, 3).reshape(nblocks * bs, KV, hd)
+    written = [s for s in slot_list if s >= 0]
+    for i, s in enumerate(slot_list):
+        if s >= 0:
+            assert torch.allclose(kflat[s], k_ref[i], **t)
+            assert torch.equal(vflat[s], qkv.cpu().view(T, H + 2 * KV, hd)[i, H + KV :])  # v bit-equal
+    untouched = torch.ones(nblocks * bs, dtype=torch.bool)
+    untouched[written] = False
+    assert float(kflat[untouched].abs().max()) == 0 and float(vflat[untouched].float().abs().max()) == 0
+
+
+def paged_setup(ctx_lens, q_lens, H, KV, hd, bs, dtype, seed=0, special=None):
+    """Random q/k/v for R requests; keys/values scattered over shuffled pages. Returns device
+    inputs and the dense per-request k, v for the reference. `special` = (request, position):
+    that key and the request's last query are made to match strongly."""
+    g = torch.Generator().manual_seed(seed)
+    R = len(ctx_lens)
+    nblocks = sum(-(-c // bs) for c in ctx_lens) + 3
+    order = torch.randperm(nblocks, generator=g).tolist()
+    kc = torch.zeros(nblocks, KV, bs, hd)
+    vc = torch.zeros(nblocks, KV, bs, hd)
+    width = max(-(-c // bs) for c in ctx_lens)
+    tables = torch.zeros(R, width, dtype=torch.int32)
+    dense, qs = [], []
+    for r, (c, n) in enumerate(zip(ctx_lens, q_lens)):
+        k = torch.randn(c, KV, hd, generator=g)
+        v = torch.randn(c, KV, hd, generator=g)
+        q = torch.randn(n, H, hd, generator=g)
+        if special is not None and special[0] == r:
+            u = torch.randn(hd, generator=g)
+            u = u / u.norm() * math.sqrt(hd) * 4
+            k[special[1]] = u
+            q[-1] = u
+        k, v, q = (t.to(dtype).float() for t in (k, v, q))
+        blocks = [order.pop() for _ in range(-(-c // bs))]
+        tables[r, : len(blocks)] = torch.tensor(blocks, dtype=torch.int32)
+        for p in range(c):
+            kc[blocks[p // bs], :, p % bs] = k[p]
+            vc[blocks[p // bs], :, p % bs] = v[p]
+        dense.append((k, v))
+        qs.append(q)
+    q_start = torch.tensor([0] + list(torch.tensor(q_lens).cumsum(0)), dtype=torch.int32)
+    pos_start = torch.tensor([c - n for c, n in zip(ctx_lens, q_lens)], dtype=torch.int32)
+    dev = dict(
+        q=torch.cat(qs).to(dtype).cuda(), k_cache=kc.to(dtype).cuda(), v_cache=vc.to(dtype).cuda(),
+        block_tables=tables.cuda(), req_q_start=q_start.cuda(), req_pos_start=pos_start.cuda(),
+    )  # fmt: skip
+    return dev, dense, qs
+
+
+def attention_reference(qs, dense, ctx_lens, q_lens, window):
+    outs = []
+    for q, (k, v), c, n in zip(qs, dense, ctx_lens, q_lens):
+        # run the whole context as queries with zeros in front, keep the last n rows
+        full_q = torch.cat([torch.zeros(c - n, *q.shape[1:]), q])
+        outs.append(plain.attention(full_q, k, v, window)[c - n :])
+    return torch.cat(outs)
+
+
+ATTN_CASES = [
+    # H, KV, hd, bs, ctx_lens, q_lens, window
+    (4, 2, 16, 16, [1, 37, 512, 513, 1500], [1, 1, 1, 1, 1], None),
+    (32, 8, 128, 16, [700, 33], [1, 33], None),
+    (5, 1, 48, 8, [64, 130, 9], [64, 2, 9], None),
+    (8, 8, 80, 4, [300, 45], [7, 45], None),
+    (6, 3, 32, 8, [200, 77, 24, 25], [1, 30, 24, 2], 24),
+    (64, 1, 64, 32, [129], [3], None),
+    (16, 8, 256, 16, [90], [90], 17),
+]
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("case", ATTN_CASES)
+def test_paged_attention(ops, dtype, case):
+    H, KV, hd, bs, ctx_lens, q_lens, window = case
+    dev, dense, qs = paged_setup(ctx_lens, q_lens, H, KV, hd, bs, dtype)
+    ref = attention_reference(qs, dense, ctx_lens, q_lens, window)
+    out = ops.paged_attention(**dev, num_requests=len(ctx_lens), max_context=max(ctx_lens), window=window, scale=hd**-0.5)
+    t = dict(atol=2e-5, rtol=1e-4) if dtype == torch.float32 else dict(atol=2e-2, rtol=2e-2)
+    assert torch.allclose(out.float().cpu(), ref, **t)
+    # the same with the keys split into partitions of 64 and merged
+    parts = (64, (max(ctx_lens) - 1) // 64 + 1)
+    out2 = ops.paged_attention(**dev, num_requests=len(ctx_lens), max_context=max(ctx_lens), window=window,
+                               scale=hd**-0.5, partitions=parts)  # fmt: skip
+    assert torch.allclose(out2.float().cpu(), ref, **t)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("where", [0, 15, 16, 17, 255, 256, 511, 640, 999])
+def test_attention_finds_one_far_key(ops, dtype, where):
+    """One key among a thousand matches the query strongly: the output must be its value,
+    wherever in its page and partition it lies."""
+    H, KV, hd, bs, ctx = 8, 2, 64, 16, 1000
+    dev, dense, qs = paged_setup([ctx], [1], H, KV, hd, bs, dtype, seed=where, special=(0, where))
+    for parts in (None, (256, 4)):
+        out = ops.paged_attention(**dev, num_requests=1, max_context=ctx, window=None, scale=hd**-0.5, partitions=parts)
+        v = dense[0][1][where]  # [KV, hd]
+        expect = v.repeat_interleave(H // KV, dim=0)
+        assert torch.allclose(out[0].float().cpu(), expect, atol=2e-2, rtol=2e-2)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_attention_window_edge(ops, dtype):
+    """The key at p - window + 1 is seen, the key at p - window is not."""
+    H, KV, hd, bs, ctx, window = 4, 2, 32, 8, 120, 24
+    p = ctx - 1
+    for where, seen in ((p - window + 1, True), (p - window, False)):
+        dev, dense, qs = paged_setup([ctx], [1], H, KV, hd, bs, dtype, seed=3, special=(0, where))
+        out = ops.paged_attention(**dev, num_requests=1, max_context=ctx, window=window, scale=hd**-0.5)
+        expect = dense[0][1][where].repeat_interleave(H // KV, dim=0)
+        close = torch.allclose(out[0].float().cpu(), expect, atol=2e-2, rtol=2e-2)
+        assert close == seen
+
+
+def test_sampling_greedy_and_support(ops):
+    logits = torch.tensor([[0.1, 3.0, 0.2, 3.0], [5.0, 1.0, 0.0, -1.0]], device="cuda")
+    assert ops.argmax_rows(logits).tolist() == [1, 0]  # lowest id among equals
+
+    probs = torch.tensor([0.4, 0.3, 0.2, 0.1])
+
+    def draws(n, temperature, top_k, top_p, seed=1):
+        lg = probs.log().repeat(n, 1).cuda().contiguous()
+        return ops.sample_rows(
+            lg, torch.full((n,), temperature, device="cuda"), torch.full((n,), top_k, dtype=torch.int32, device="cuda"),
+            torch.full((n,), top_p, device="cuda"), torch.full((n,), seed, dtype=torch.int64, device="cuda"),
+            torch.arange(n, dtype=torch.int64, device="cuda"),
+        ).cpu()  # fmt: skip
+
+    counts = draws(20000, 1.0, 0, 1.0).bincount(minlength=4)
+    assert torch.allclose(counts / 20000, probs, atol=0.015)
+    assert set(draws(2000, 1.0, 2, 1.0).tolist()) == {0, 1}
+    assert set(draws(200, 1.0, 1, 1.0).tolist()) == {0}
+    assert set(draws(2000, 1.0, 0, 0.6).tolist()) == {0, 1}
+    assert set(draws(200, 1.0, 0, 0.01).tolist()) == {0}
+    assert set(draws(50, 0.0, 3, 0.5).tolist()) == {0}
+    # temperature reshapes the distribution: p^(1/T) renormalised
+    counts = draws(20000, 0.5, 0, 1.0).bincount(minlength=4)
+    sharp = probs**2 / (probs**2).sum()
+    assert torch.allclose(counts / 20000, sharp, atol=0.015)
+
+
+@pytest.mark.parametrize("V,k,p,temp", [(331, 20, 0.95, 0.6), (5000, 64, 0.8, 0.7), (151936, 20, 0.95, 0.6),
+                                        (2000, 0, 0.9, 1.0), (3000, 1500, 0.5, 1.3)])  # fmt: skip
+def test_sampling_support_matches_plain(ops, V, k, p, temp):
+    """Everything drawn lies in the plain sampler's support, and frequent tokens agree."""
+    g = torch.Generator().manual_seed(V)
+    logits = torch.randn(V, generator=g) * 3
+    dist = plain.sampling_distribution(logits, temp, k, p)
+    n = 4000
+    out = ops.sample_rows(
+        logits.repeat(n, 1).cuda().contiguous(), torch.full((n,), temp, device="cuda"),
+        torch.full((n,), k, dtype=torch.int32, device="cuda"), torch.full((n,), p, device="cuda"),
+        torch.full((n,), 9, dtype=torch.int64, device="cuda"), torch.arange(n, dtype=torch.int64, device="cuda"),
+    ).cpu().long()  # fmt: skip
+    assert bool((dist[out] > 0).all())
+    freq = out.bincount(minlength=V) / n
+    assert float((freq - dist).abs().max()) < 0.04
+
+
+def test_sampling_ties_at_the_cut(ops):
+    """Equal logits at the k-th place: exactly k tokens stay, the lower ids."""
+    logits = torch.tensor([[1.0, 2.0, 2.0, 2.0, 2.0, 0.5, 3.0]], device="cuda").repeat(500, 1).contiguous()
+    n = 500
+    out = ops.sample_rows(
+        logits, torch.ones(n, device="cuda"), torch.full((n,), 3, dtype=torch.int32, device="cuda"),
+        torch.ones(n, device="cuda"), torch.zeros(n, dtype=torch.int64, device="cuda"),
+        torch.arange(n, dtype=torch.int64, device="cuda"),
+    ).cpu()  # fmt: skip
+    assert set(out.tolist()) == {6, 1, 2}
+
+
+def test_seeded_rows_do_not_depend_on_neighbours(ops):
+    g = torch.Generator().manual_seed(0)
+    row = torch.randn(1000, generator=g)
+    others = torch.randn(2, 1000, generator=g)
+
+    def run(rows, seeds, counters):
+        n = rows.shape[0]
+        return ops.sample_rows(
+            rows.cuda().contiguous(), torch.ones(n, device="cuda"), torch.full((n,), 50, dtype=torch.int32, device="cuda"),
+            torch.ones(n, device="cuda"), torch.tensor(seeds, dtype=torch.int64, device="cuda"),
+            torch.tensor(counters, dtype=torch.int64, device="cuda"),
+        ).tolist()  # fmt: skip
+
+    alone = [run(row[None], [7], [i])[0] for i in range(20)]
+    crowd = [run(torch.stack([others[0], row, others[1]]), [1, 7, 2], [i + 5, i, i + 9])[1] for i in range(20)]
+    assert alone == crowd and len(set(alone)) > 3
+
+
+def test_presence_penalty(ops):
+    logits = torch.zeros(2, 10, device="cuda")
+    ops.presence_penalty(
+        logits, torch.tensor([0, 0, 1], dtype=torch.int32, device="cuda"),
+        torch.tensor([3, 4, 9], dtype=torch.int32, device="cuda"), torch.tensor([1.5, 1.5, 0.5], device="cuda"),
+    )  # fmt: skip
+    expect = torch.zeros(2, 10)
+    expect[0, 3] = expect[0, 4] = -1.5
+    expect[1, 9] = -0.5
+    assert torch.equal(logits.cpu(), expect)

@@ -1,0 +1,207 @@
+"""The engine's step function, cache and kernels against the plain implementation, through the
+trace replayer: every way of cutting requests into steps must give the oracle's logits."""
+
+import json
+import subprocess
+import sys
+
+import numpy as np
+import pytest
+import torch
+
+import plain_qwen3 as plain
+from helpers import FLOAT32_TOLERANCE, bfloat16_tolerance, checkpoint, prompts, rel_error, write_folder
+from tiny_configs import TINY
+
+pytestmark = pytest.mark.gpu
+DTYPES = ["float32", "bfloat16"]
+LENGTHS = {"a": [5, 17, 33, 70], "b": [1, 9, 24, 40, 75], "c": [3, 50, 90, 41]}
+
+
+@pytest.fixture(scope="module")
+def models(tmp_path_factory):
+    """name -> (config, block size, folder, prompts, oracle per prompt). An oracle is the
+    float32 logits with their bfloat16 allowance attached (`Oracle`)."""
+    out = {}
+    for name, (cfg, bs) in TINY.items():
+        w = checkpoint(cfg, seed=21)
+        folder = write_folder(cfg, w, tmp_path_factory.mktemp(f"tiny_{name}"))
+        ps = prompts(cfg, LENGTHS[name], seed=4)
+        out[name] = (cfg, bs, folder, ps, [Oracle(w, cfg, p) for p in ps])
+    return out
+
+
+class Oracle:
+    """Float32 logits of a whole prompt from the plain implementation; indexing gives the rows
+    asked for, still carrying the prompt's bfloat16 allowance."""
+
+    def __init__(self, w=None, cfg=None, prompt=None, logits=None, allowance=None):
+        if logits is None:
+            logits = plain.forward(w, cfg, prompt)
+            allowance = bfloat16_tolerance(w, cfg, prompt, logits)
+        self.logits, self.allowance = logits, allowance
+
+    def __getitem__(self, rows):
+        return Oracle(logits=self.logits[rows], allowance=self.allowance)
+
+
+def replayer(folder, dtype, bs, max_tokens, graphs=True):
+    from atomserve_b200.engine.replay import TraceReplayer
+
+    return TraceReplayer(folder, dtype, max_tokens, bs, cuda_graphs=graphs)
+
+
+def check(got, oracle, dtype, what):
+    ref = oracle.logits
+    assert got.shape == ref.shape, f"{what}: shape {tuple(got.shape)} for {tuple(ref.shape)}"
+    err = rel_error(got.cpu(), ref)
+    limit = FLOAT32_TOLERANCE if dtype == "float32" else oracle.allowance
+    assert err < limit, f"{what}: relative error {err:.3g}, allowed {limit:.3g}"
+    if dtype == "float32":
+        assert torch.equal(got.cpu().argmax(-1), ref.argmax(-1)), what
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", ["a", "b", "c"])
+def test_each_request_alone_and_whole(models, name, dtype):
+    cfg, bs, folder, ps, oracle = models[name]
+    rp = replayer(folder, dtype, bs, 128)
+    for i, (p, ref) in enumerate(zip(ps, oracle)):
+        logits = rp.step([dict(id=i, tokens=p, want=list(range(len(p))))], end=[i])
+        check(logits, ref, dtype, f"{name} request {i} whole")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", ["a", "b", "c"])
+def test_prefill_then_last_32_one_by_one(models, name, dtype):
+    cfg, bs, folder, ps, oracle = models[name]
+    rp = replayer(folder, dtype, bs, 128)
+    for i, (p, ref) in enumerate(zip(ps, oracle)):
+        head = max(len(p) - 32, 0)
+        got = []
+        if head:
+            got.append(rp.step([dict(id=i, tokens=p[:head], want=[head - 1])], end=[]))
+            check(got[0], ref[head - 1 : head], dtype, f"{name} request {i} head")
+        for j in range(head, len(p)):
+            logits = rp.step([dict(id=i, tokens=[p[j]], want=[0])], end=[i] if j == len(p) - 1 else [])
+            check(logits, ref[j : j + 1], dtype, f"{name} request {i} position {j}")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", ["a", "b", "c"])
+def test_portions_of_changing_size(models, name, dtype):
+    cfg, bs, folder, ps, oracle = models[name]
+    rp = replayer(folder, dtype, bs, 128)
+    sizes = [2, 7, 3, 16, 2, 17, 5, 31, 2, 9]
+    for i, (p, ref) in enumerate(zip(ps, oracle)):
+        at, k = 0, i
+        while at < len(p):
+            n = min(sizes[k % len(sizes)], len(p) - at)
+            k += 1
+            last = at + n == len(p)
+            logits = rp.step([dict(id=i, tokens=p[at : at + n], want=list(range(n)))], end=[i] if last else [])
+            check(logits, ref[at : at + n], dtype, f"{name} request {i} portion {at}:{at + n}")
+            at += n
+
+
+def mixed_trace(ps, rng, max_live=4):
+    """Steps that keep up to `max_live` requests going: each live request brings a portion of
+    random size (prompt phase) or one token (its last 8 tokens), some sit a step out."""
+    steps, live, waiting, done_at = [], {}, list(range(len(ps))), {}
+    while waiting or live:
+        while waiting and len(live) < max_live:
+            live[waiting.pop(0)] = 0
+        entries, end = [], []
+        for i in list(live):
+            if len(live) > 1 and rng.random() < 0.2:
+                continue
+            at, total = live[i], len(ps[i])
+            n = 1 if at >= total - 8 else min(int(rng.integers(2, 20)), total - 8 - at) or 1
+            entries.append(dict(id=i, tokens=ps[i][at : at + n], want=list(range(n)), at=at))
+            live[i] = at + n
+            if at + n == total:
+                end.append(i)
+                del live[i]
+        if entries:
+            steps.append((entries, end))
+    return steps
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", ["a", "b", "c"])
+def test_mixed_requests_reusing_pages(models, name, dtype):
+    """Up to four live requests, portions beside single tokens, in a pool so small that pages
+    freed by finished requests are taken again by later ones; every request appears three times,
+    so that later copies run entirely on used pages."""
+    cfg, bs, folder, ps, oracle = models[name]
+    ps2, oracle2 = ps * 3, oracle * 3
+    biggest = sorted((-(-len(p) // 64) * 64 for p in ps), reverse=True)
+    rp = replayer(folder, dtype, bs, sum(biggest[:4]))
+    rng = np.random.default_rng(7)
+    for entries, end in mixed_trace(ps2, rng):
+        logits = rp.step([dict(id=e["id"], tokens=e["tokens"], want=e["want"]) for e in entries], end=end)
+        row = 0
+        for e in entries:
+            n = len(e["tokens"])
+            check(logits[row : row + n], oracle2[e["id"]][e["at"] : e["at"] + n], dtype,
+                  f"{name} request {e['id']} at {e['at']}")  # fmt: skip
+            row += n
+    total_tokens = sum(len(p) for p in ps2)
+    assert total_tokens > rp.cache.num_blocks * bs, "the pool was large enough to never reuse a page"
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_long_decoding(models, dtype):
+    """300 tokens one by one (across many pages and, for config c, far beyond its window)."""
+    for name in ("b", "c"):
+        cfg, bs, folder, _, _ = models[name]
+        w = checkpoint(cfg, seed=21)
+        p = prompts(cfg, [300], seed=9)[0]
+        ref = Oracle(w, cfg, p)
+        for graphs in (True, False):
+            rp = replayer(folder, dtype, bs, 320, graphs)
+            for j, t in enumerate(p):
+                logits = rp.step([dict(id="x", tokens=[t], want=[0])], end=[])
+                if j % 7 == 0 or j > 290:
+                    check(logits, ref[j : j + 1], dtype, f"{name} decode position {j} graphs={graphs}")
+
+
+def test_window_pages_are_given_back(models):
+    cfg, bs, folder, _, _ = models["c"]
+    rp = replayer(folder, "float32", bs, 320)
+    p = prompts(cfg, [200], seed=2)[0]
+    for t in p:
+        rp.step([dict(id="w", tokens=[t], want=[])], end=[])
+    rc, _ = rp.live["w"]
+    full = [g for g in rp.cache.groups if g.window is None][0]
+    windowed = [g for g in rp.cache.groups if g.window is not None][0]
+    held = {id(g): sum(b >= 0 for b in t) for g, t in zip(rp.cache.groups, rc.block_tables)}
+    assert held[id(full)] == -(-200 // bs)
+    assert held[id(windowed)] <= -(-cfg["sliding_window"] // bs) + 1
+    assert windowed.allocator.num_free == rp.cache.num_blocks - held[id(windowed)]
+
+
+def test_trace_run_program(models, tmp_path):
+    """The program itself: steps on stdin, `done` lines, .f32 files, exit code 0."""
+    cfg, bs, folder, ps, oracle = models["b"]
+    steps = [
+        dict(step=0, entries=[dict(id="a", tokens=ps[2][:10], want=[0, 9]), dict(id="b", tokens=ps[1], want=[8])], end=["b"]),
+        dict(step=1, entries=[dict(id="a", tokens=ps[2][10:12], want=[])], end=[]),
+        dict(step=2, entries=[dict(id="a", tokens=ps[2][12:], want=[len(ps[2]) - 13])], end=["a"]),
+    ]
+    root = __import__("pathlib").Path(__file__).resolve().parent.parent
+    for dtype in DTYPES:
+        out = tmp_path / dtype
+        done = subprocess.run(
+            [sys.executable, str(root / "bin" / "trace_run"), "--model", str(folder), "--dtype", dtype,
+             "--out", str(out), "--max-tokens", "128", "--block-size", str(bs)],
+            input="\n".join(json.dumps(s) for s in steps) + "\n", capture_output=True, text=True, timeout=600,
+        )  # fmt: skip
+        assert done.returncode == 0, done.stderr[-2000:]
+        assert done.stdout.split() == ["done", "0", "done", "1", "done", "2"]
+        assert not (out / "1.f32").exists()
+        s0 = torch.from_numpy(np.fromfile(out / "0.f32", dtype="<f4").reshape(3, cfg["vocab_size"]))
+        check(s0[:2], oracle[2][[0, 9]], dtype, "step 0 request a")
+        check(s0[2:], oracle[1][8:9], dtype, "step 0 request b")
+        s2 = torch.from_numpy(np.fromfile(out / "2.f32", dtype="<f4").reshape(1, cfg["vocab_size"]))
+        check(s2, oracle[2][-1:], dtype, "step 2")
