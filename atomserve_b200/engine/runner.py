@@ -229,3 +229,16 @@ class ModelRunner:
         graph, out = entry
         graph.replay()
         return out
+
+
+def rows_for(seqs, num_new_tokens: list[int]) -> list[Row]:
+    """The usual rows of a scheduled step: each sequence's next uncomputed tokens, with logits
+    wanted at the last one only if that reaches the end of its known tokens
+    (atomserve/runner.py:59-68)."""
+    rows = []
+    for seq, n in zip(seqs, num_new_tokens, strict=True):
+        start = seq.num_computed_tokens
+        if n < 1 or start + n > seq.num_tokens:
+            raise ValueError(f"cannot run tokens {start}:{start + n} of {seq.num_tokens}")
+        rows.append(Row(seq.token_ids[start : start + n], start, seq.cache, [n - 1] if seq.reaches_end(n) else []))
+    return rows

@@ -1,0 +1,160 @@
+"""Scheduler, cache manager, runner and engine together on the CPU, with the tests' torch parts
+standing where the CUDA kernels are (tests/toy_parts.py): greedy tokens must equal the plain
+implementation's under batching, chunking, preemption, prefix reuse and a window
+(the reference's tests/test_engine.py:21-96 in this engine's terms)."""
+
+import threading
+
+import pytest
+import torch
+
+import plain_qwen3 as plain
+import toy_parts
+from atomserve_b200.cache import CacheManager
+from atomserve_b200.config import EngineConfig
+from atomserve_b200.engine.engine import Engine
+from atomserve_b200.engine.runner import ModelRunner, Row
+from atomserve_b200.engine.scheduler import Scheduler
+from atomserve_b200.engine.sequence import SamplingParams
+from helpers import checkpoint, prompts
+from tiny_configs import TINY
+
+GREEDY = dict(temperature=0.0, ignore_eos=True)
+
+
+def widen(w):
+    """Larger matrices so that greedy tokens vary instead of repeating one id."""
+    return {k: (v * 6 if v.dim() == 2 else v) for k, v in w.items()}
+
+
+@pytest.fixture(scope="module", params=["a", "b", "c"])
+def setup(request):
+    cfg, bs = TINY[request.param]
+    w = widen(checkpoint(cfg, seed=8, sharp=False, bf16_exact=False))
+    return cfg, bs, w, toy_parts.toy_model(cfg, w)
+
+
+def engine_for(model, bs, **kw):
+    config = EngineConfig(**{"block_size": bs, "num_blocks": 64, "max_model_len": 64 * bs, "max_num_seqs": 8,
+                             "max_num_batched_tokens": 256, **kw})  # fmt: skip
+    cache = CacheManager(model.cache_requirements(), bs, config.num_blocks, config.max_num_seqs, torch.float32, "cpu")
+    return Engine(ModelRunner(model, cache), Scheduler(config, cache), toy_parts.ArgmaxSampler())
+
+
+def test_step_function_matches_the_oracle_in_a_mixed_batch(setup):
+    cfg, bs, w, model = setup
+    cache = CacheManager(model.cache_requirements(), bs, 32, 4, torch.float32, "cpu")
+    runner = ModelRunner(model, cache)
+    a, b = prompts(cfg, [29, 11], seed=1)
+    ra, rb = cache.new_request(), cache.new_request()
+    cache.admit(ra), cache.admit(rb)
+    cache.reserve(ra, 0, 20)
+    first = runner.step([Row(a[:20], 0, ra, [0, 19])])
+    cache.reserve(ra, 20, 9), cache.reserve(rb, 0, 11)
+    second = runner.step([Row(a[20:], 20, ra, list(range(9))), Row(b, 0, rb, [10, 3])])
+    oa, ob = plain.forward(w, cfg, a), plain.forward(w, cfg, b)
+    assert torch.allclose(first, oa[[0, 19]], atol=2e-4)
+    assert torch.allclose(second[:9], oa[20:], atol=2e-4)
+    assert torch.allclose(second[9:], ob[[10, 3]], atol=2e-4)
+
+
+def test_runner_rejects_bad_rows(setup):
+    cfg, bs, w, model = setup
+    cache = CacheManager(model.cache_requirements(), bs, 8, 2, torch.float32, "cpu")
+    runner = ModelRunner(model, cache)
+    rc = cache.new_request()
+    cache.reserve(rc, 0, 3)
+    with pytest.raises(ValueError, match="at least one token"):
+        runner.step([Row([], 0, rc, [])])
+    with pytest.raises(ValueError, match="wanted places"):
+        runner.step([Row([1, 2], 0, rc, [2])])
+    with pytest.raises(ValueError, match="block table holds"):
+        runner.step([Row(list(range(bs + 1)), 0, rc, [])])
+    with pytest.raises(ValueError, match="token id"):
+        runner.step([Row([cfg["vocab_size"]], 0, rc, [])])
+
+
+def test_greedy_equals_plain_alone_batched_chunked(setup):
+    cfg, bs, w, model = setup
+    ps = prompts(cfg, [5, 17, 33], seed=3)
+    expect = [plain.greedy_generate(w, cfg, p, 8) for p in ps]
+    params = SamplingParams(max_tokens=8, **GREEDY)
+    assert engine_for(model, bs).generate(ps, params) == expect  # batched
+    for p, e in zip(ps, expect):
+        assert engine_for(model, bs).generate([p], params) == [e]  # alone
+    chunked = engine_for(model, bs, max_num_batched_tokens=8, max_num_seqs=4)
+    assert chunked.generate(ps, params) == expect
+    assert chunked.num_steps > 8 + 3
+
+
+def test_preemption_under_few_pages_keeps_outputs(setup):
+    cfg, bs, w, model = setup
+    ps = prompts(cfg, [bs + 3, bs + 5, 2 * bs - 1], seed=5)
+    n = bs + 8  # every request grows by at least a page, and the pool cannot hold all three
+    expect = [plain.greedy_generate(w, cfg, p, n) for p in ps]
+    eng = engine_for(model, bs, num_blocks=7, max_model_len=7 * bs, enable_prefix_caching=False)
+    assert eng.generate(ps, SamplingParams(max_tokens=n, **GREEDY)) == expect
+    assert eng.stats()["preemptions"] > 0 and eng.stats()["kv_blocks_used"] == 0
+
+
+def test_prefix_cache_hits_equal_uncached(setup):
+    cfg, bs, w, model = setup
+    shared = prompts(cfg, [3 * bs + 2], seed=6)[0]
+    ps = [shared + [1, 2, 3], shared + [4]]
+    expect = [plain.greedy_generate(w, cfg, p, 6) for p in ps]
+    eng = engine_for(model, bs)
+    params = SamplingParams(max_tokens=6, **GREEDY)
+    got = [eng.generate([p], params)[0] for p in ps]
+    assert got == expect
+    if eng.scheduler.prefix_caching:
+        assert eng.stats()["cached_prompt_tokens"] == 3 * bs
+    else:
+        assert cfg.get("use_sliding_window") and eng.stats()["cached_prompt_tokens"] == 0
+
+
+def test_concurrent_clients_abort_and_validation(setup):
+    cfg, bs, w, model = setup
+    eng = engine_for(model, bs)
+    with pytest.raises(ValueError, match="prompt has 0"):
+        eng.submit([], SamplingParams())
+    with pytest.raises(ValueError, match="max_tokens"):
+        eng.submit([1], SamplingParams(max_tokens=0))
+    with pytest.raises(ValueError, match="outside"):
+        eng.submit([cfg["vocab_size"]], SamplingParams())
+    eng.start()
+    ps = prompts(cfg, [4, 9, 14, 6], seed=7)
+    expect = [plain.greedy_generate(w, cfg, p, 5) for p in ps]
+    results = [None] * 4
+
+    def client(i):
+        results[i] = list(eng.submit(ps[i], SamplingParams(max_tokens=5, **GREEDY)))
+
+    threads = [threading.Thread(target=client, args=(i,)) for i in range(4)]
+    [t.start() for t in threads]
+    [t.join(timeout=120) for t in threads]
+    assert results == expect
+    handle = eng.submit(ps[2], SamplingParams(max_tokens=4000, **GREEDY))
+    it = iter(handle)
+    next(it)
+    handle.abort()
+    list(it)
+    assert handle.finish_reason == "abort" and handle.ttft is not None
+    eng.shutdown()
+    assert eng.stats()["kv_blocks_used"] == 0 and eng.stats()["running"] == 0
+
+
+def test_engine_survives_a_failing_step(setup):
+    cfg, bs, w, model = setup
+    eng = engine_for(model, bs)
+    real = eng.execute
+    eng.execute = lambda out: (_ for _ in ()).throw(RuntimeError("boom"))
+    eng.start()
+    handle = eng.submit([1, 2], SamplingParams(max_tokens=3, **GREEDY))
+    with pytest.raises(RuntimeError, match="engine step failed"):
+        list(handle)
+    assert handle.finish_reason == "error"
+    eng.execute = real
+    again = eng.submit([1, 2], SamplingParams(max_tokens=3, **GREEDY))
+    assert list(again) == plain.greedy_generate(w, cfg, [1, 2], 3)
+    eng.shutdown()
+    assert eng.stats()["kv_blocks_used"] == 0

@@ -1,0 +1,251 @@
+"""Parts defined by the tests, registered through the package's public registries.
+
+Two uses. (1) Every hot part again in plain torch (`torch_*` kinds and the architecture
+"ToyTorchLM"), reading and writing the paged cache through the same CacheView: with these
+the scheduler, cache manager, runner and engine run whole on the CPU. (2) `ema_mixer`, a mixer
+with state of its own (one vector per request, kept in the state slots), to show that such a
+part is registered, built and stepped without touching the package.
+
+They follow the package's interfaces and nothing else of it; the oracle stays plain_qwen3.
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass
+
+import torch
+
+import plain_qwen3 as plain
+from atomserve_b200.config.registry import register_architecture
+from atomserve_b200.parts import (
+    CacheView, FeedForward, KVCacheSpec, LayerCall, LayerSpec, Mixer, ModelSpec, Norm, Part,
+    PartSpec, StateSpec, StepContext, TensorSpec, register_part,
+)  # fmt: skip
+
+
+class TorchRMSNorm(Norm):
+    def __init__(self, hidden_size, prefix, eps):
+        self.width, self.eps, self.name = hidden_size, eps, prefix + "weight"
+
+    def tensor_specs(self):
+        return [TensorSpec(self.name, (self.width,), kind="gain", init="gain")]
+
+    def load(self, tensors):
+        self.gain = tensors[self.name]
+
+    def forward(self, x, rows=None):
+        if rows is not None:
+            x = x[rows.long()]
+        return plain.rms_norm(x.float(), self.gain, self.eps).to(x.dtype)
+
+
+class TorchEmbedding(Part):
+    def __init__(self, hidden_size, prefix, vocab_size):
+        self.shape, self.name = (vocab_size, hidden_size), prefix + "weight"
+
+    def tensor_specs(self):
+        return [TensorSpec(self.name, self.shape)]
+
+    def load(self, tensors):
+        self.table = tensors[self.name]
+
+    def forward(self, token_ids):
+        return self.table[token_ids.long()]
+
+
+class TorchHead(Part):
+    def __init__(self, hidden_size, prefix, vocab_size, tied):
+        self.shape, self.name, self.tied = (vocab_size, hidden_size), prefix + "weight", tied
+
+    def tensor_specs(self):
+        return [] if self.tied else [TensorSpec(self.name, self.shape)]
+
+    def load(self, tensors):
+        if not self.tied:
+            self.weight = tensors[self.name]
+
+    def tie(self, embedding):
+        self.weight = embedding.table
+
+    def forward(self, hidden):
+        return hidden.float() @ self.weight.float().T
+
+
+class TorchSwiGLU(FeedForward):
+    def __init__(self, hidden_size, prefix, intermediate_size):
+        self.d, self.i, self.p = hidden_size, intermediate_size, prefix
+
+    def tensor_specs(self):
+        return [TensorSpec(self.p + "gate_proj.weight", (self.i, self.d)),
+                TensorSpec(self.p + "up_proj.weight", (self.i, self.d)),
+                TensorSpec(self.p + "down_proj.weight", (self.d, self.i))]  # fmt: skip
+
+    def load(self, tensors):
+        self.w = {n: tensors[self.p + n + "_proj.weight"] for n in ("gate", "up", "down")}
+
+    def forward(self, h, residual, ctx):
+        gate, up = h @ self.w["gate"].T, h @ self.w["up"].T
+        return residual + (torch.nn.functional.silu(gate) * up) @ self.w["down"].T
+
+
+class TorchAttention(Mixer):
+    """Paged GQA attention with q/k norm and rotary encoding, one request at a time."""
+
+    def __init__(self, hidden_size, prefix, num_heads, num_kv_heads, head_dim, eps, theta, window=None):
+        self.d, self.p, self.H, self.KV, self.hd = hidden_size, prefix, num_heads, num_kv_heads, head_dim
+        self.eps, self.theta, self.window = eps, theta, window
+
+    def cache_spec(self):
+        return KVCacheSpec(self.KV, self.hd, self.window)
+
+    def tensor_specs(self):
+        p, d, hd = self.p, self.d, self.hd
+        return [TensorSpec(p + "q_proj.weight", (self.H * hd, d)), TensorSpec(p + "k_proj.weight", (self.KV * hd, d)),
+                TensorSpec(p + "v_proj.weight", (self.KV * hd, d)), TensorSpec(p + "o_proj.weight", (d, self.H * hd)),
+                TensorSpec(p + "q_norm.weight", (hd,), "gain", "gain"), TensorSpec(p + "k_norm.weight", (hd,), "gain", "gain")]  # fmt: skip
+
+    def load(self, tensors):
+        self.w = {n: tensors[self.p + n + ".weight"] for n in ("q_proj", "k_proj", "v_proj", "o_proj", "q_norm", "k_norm")}
+
+    def forward(self, h, residual, ctx, cache, write_cache=True):
+        T, H, KV, hd = h.shape[0], self.H, self.KV, self.hd
+        angles = plain.rope_angles(ctx.positions.long().cpu(), hd, self.theta).to(h.device)
+        q = plain.apply_rope(plain.rms_norm((h @ self.w["q_proj"].T).view(T, H, hd), self.w["q_norm"], self.eps), angles)
+        bs = cache.block_size
+        if write_cache:
+            k = plain.apply_rope(plain.rms_norm((h @ self.w["k_proj"].T).view(T, KV, hd), self.w["k_norm"], self.eps), angles)
+            v = (h @ self.w["v_proj"].T).view(T, KV, hd)
+            slots = cache.slots.long()
+            cache.k[slots // bs, :, slots % bs] = k.to(cache.k.dtype)
+            cache.v[slots // bs, :, slots % bs] = v.to(cache.v.dtype)
+        out = torch.empty(T, H, hd, dtype=h.dtype, device=h.device)
+        row = 0
+        for r, (n, start) in enumerate(zip(ctx.host_q_lens, ctx.host_pos_start)):
+            end = start + n
+            lo = 0 if self.window is None else max(0, start - self.window + 1)
+            pos = torch.arange(lo, end, device=h.device)
+            blocks = cache.block_tables[r].long()[pos // bs]
+            keys, values = cache.k[blocks, :, pos % bs].float(), cache.v[blocks, :, pos % bs].float()
+            group = H // KV
+            kk, vv = keys.repeat_interleave(group, 1), values.repeat_interleave(group, 1)
+            scores = torch.einsum("thd,shd->hts", q[row : row + n].float(), kk) * hd**-0.5
+            qpos = torch.arange(start, end, device=h.device)
+            visible = pos[None, :] <= qpos[:, None]
+            if self.window is not None:
+                visible &= pos[None, :] > qpos[:, None] - self.window
+            scores = scores.masked_fill(~visible[None], float("-inf"))
+            out[row : row + n] = torch.einsum("hts,shd->thd", scores.softmax(-1), vv).to(h.dtype)
+            row += n
+        return residual + out.view(T, H * hd) @ self.w["o_proj"].T
+
+
+class EmaMixer(Mixer):
+    """A mixer with constant-size state: s_t = decay * s_{t-1} + (1 - decay) * W x_t, y_t = s_t,
+    one state vector per request, carried across steps in the request's state slot."""
+
+    def __init__(self, hidden_size, prefix, decay):
+        self.d, self.p, self.decay = hidden_size, prefix, decay
+
+    def state_specs(self):
+        return [StateSpec("ema", (self.d,), torch.float32)]
+
+    def tensor_specs(self):
+        return [TensorSpec(self.p + "in_proj.weight", (self.d, self.d))]
+
+    def load(self, tensors):
+        self.w = tensors[self.p + "in_proj.weight"]
+
+    def forward(self, h, residual, ctx, cache, write_cache=True):
+        u = (h @ self.w.T).float()
+        out = torch.empty_like(u)
+        state = cache.state["ema"]
+        row = 0
+        for n, slot in zip(ctx.host_q_lens, ctx.host_state_slots):
+            s = state[slot].clone()
+            for t in range(row, row + n):
+                s = self.decay * s + (1 - self.decay) * u[t]
+                out[t] = s
+            state[slot] = s
+            row += n
+        return residual + out.to(h.dtype)
+
+
+def ema_reference(u: torch.Tensor, decay: float) -> torch.Tensor:
+    s, out = torch.zeros_like(u[0]), []
+    for t in range(u.shape[0]):
+        s = decay * s + (1 - decay) * u[t]
+        out.append(s)
+    return torch.stack(out)
+
+
+register_part("norm", "torch_rms_norm", TorchRMSNorm)
+register_part("embedding", "torch_embedding", TorchEmbedding)
+register_part("head", "torch_head", TorchHead)
+register_part("feed_forward", "torch_swiglu", TorchSwiGLU)
+register_part("mixer", "torch_attention", TorchAttention)
+register_part("mixer", "ema_mixer", EmaMixer)
+
+
+@dataclass(frozen=True)
+class ToyConfig:
+    """A Qwen3-shaped model whose parts are the torch ones above (same tensor names, so the
+    plain implementation is its oracle too)."""
+
+    raw: tuple  # the Qwen3 config dict as sorted items
+
+    architecture = "ToyTorchLM"
+
+    @classmethod
+    def from_dict(cls, raw):
+        return cls(tuple(sorted((k, tuple(v) if isinstance(v, list) else v) for k, v in raw.items())))
+
+    def to_dict(self):
+        return {k: list(v) if isinstance(v, tuple) else v for k, v in self.raw}
+
+
+def toy_spec(config: ToyConfig) -> ModelSpec:
+    c = config.to_dict()
+    hd, eps = plain.head_dim_of(c), c["rms_norm_eps"]
+    layers = []
+    for i in range(c["num_hidden_layers"]):
+        p = f"model.layers.{i}."
+        layers.append(LayerSpec(
+            "pre_norm",
+            PartSpec("torch_attention", dict(num_heads=c["num_attention_heads"], num_kv_heads=c["num_key_value_heads"],
+                                             head_dim=hd, eps=eps, theta=c["rope_theta"],
+                                             window=plain.layer_window(c, i)), p + "self_attn."),
+            PartSpec("torch_swiglu", dict(intermediate_size=c["intermediate_size"]), p + "mlp."),
+            PartSpec("torch_rms_norm", dict(eps=eps), p + "input_layernorm."),
+            PartSpec("torch_rms_norm", dict(eps=eps), p + "post_attention_layernorm."),
+        ))  # fmt: skip
+    tied = c.get("tie_word_embeddings", False)
+    return ModelSpec(
+        hidden_size=c["hidden_size"], vocab_size=c["vocab_size"], max_positions=c["max_position_embeddings"],
+        embedding=PartSpec("torch_embedding", dict(vocab_size=c["vocab_size"]), "model.embed_tokens."),
+        layers=tuple(layers), schedule=tuple(LayerCall(i) for i in range(len(layers))),
+        final_norm=PartSpec("torch_rms_norm", dict(eps=eps), "model.norm."),
+        head=PartSpec("torch_head", dict(vocab_size=c["vocab_size"], tied=tied), "lm_head."),
+        ignored_tensors=("lm_head.weight",) if tied else (),
+    )  # fmt: skip
+
+
+register_architecture("ToyTorchLM", ToyConfig, toy_spec)
+
+
+def toy_model(cfg: dict, w: dict, device="cpu"):
+    """A ToyTorchLM of a Qwen3 config dict with the given float32 checkpoint."""
+    from atomserve_b200.parts import build_model
+
+    model = build_model(toy_spec(ToyConfig.from_dict({**cfg, "architectures": ["ToyTorchLM"]})))
+    model.load({k: v.to(device) for k, v in w.items()})
+    return model
+
+
+class ArgmaxSampler:
+    """Greedy sampling in torch, for engines that run on the CPU in tests."""
+
+    def sample(self, logits, seqs):
+        return logits.argmax(-1).tolist() if seqs else []
+
+    def release(self, seq_id):
+        pass
