@@ -48,9 +48,12 @@ FLOAT32_TOLERANCE = 2e-5
 
 
 def bfloat16_tolerance(w: dict, cfg: dict, prompt: list[int], ref: torch.Tensor) -> float:
-    """How far bfloat16 logits may lie from the float32 oracle on this prompt: as far as the
-    plain implementation itself moves when every operation's result is rounded to bfloat16
-    (the engine rounds at fewer places and accumulates in float32, so it must do no worse),
-    and never less than 1% of the largest logit."""
+    """How far (in absolute terms) bfloat16 logits may lie from the float32 oracle anywhere in
+    this prompt. The yardstick is the plain implementation itself with every operation's result
+    rounded to bfloat16: the engine rounds at fewer places and accumulates in float32, so its
+    noise is of that size or smaller. Both are single draws of rounding noise, so the engine
+    is allowed twice the yardstick's largest error, and never less than 1% of the prompt's
+    largest logit. (What this cannot see, the float32 runs of the same tests do: they share
+    every kernel and all host logic and are held to 2e-5.)"""
     rounded = plain.forward(w, cfg, prompt, activations=torch.bfloat16)
-    return max(rel_error(rounded, ref), 0.01)
+    return max(2 * float((rounded - ref).abs().max()), 0.01 * float(ref.abs().max()))

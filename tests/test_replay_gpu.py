@@ -45,6 +45,9 @@ class Oracle:
         return Oracle(logits=self.logits[rows], allowance=self.allowance)
 
 
+BF16_REPORT: list[tuple[str, float]] = []  # (what, error / allowance) of every bfloat16 check
+
+
 def replayer(folder, dtype, bs, max_tokens, graphs=True):
     from atomserve_b200.engine.replay import TraceReplayer
 
@@ -54,11 +57,14 @@ def replayer(folder, dtype, bs, max_tokens, graphs=True):
 def check(got, oracle, dtype, what):
     ref = oracle.logits
     assert got.shape == ref.shape, f"{what}: shape {tuple(got.shape)} for {tuple(ref.shape)}"
-    err = rel_error(got.cpu(), ref)
-    limit = FLOAT32_TOLERANCE if dtype == "float32" else oracle.allowance
-    assert err < limit, f"{what}: relative error {err:.3g}, allowed {limit:.3g}"
     if dtype == "float32":
+        err = rel_error(got.cpu(), ref)
+        assert err < FLOAT32_TOLERANCE, f"{what}: relative error {err:.3g}"
         assert torch.equal(got.cpu().argmax(-1), ref.argmax(-1)), what
+    else:
+        err = float((got.cpu() - ref).abs().max())
+        assert err <= oracle.allowance, f"{what}: error {err:.3g}, allowed {oracle.allowance:.3g}"
+        BF16_REPORT.append((what, err / oracle.allowance))
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
@@ -205,3 +211,11 @@ def test_trace_run_program(models, tmp_path):
         check(s0[2:], oracle[1][8:9], dtype, "step 0 request b")
         s2 = torch.from_numpy(np.fromfile(out / "2.f32", dtype="<f4").reshape(1, cfg["vocab_size"]))
         check(s2, oracle[2][-1:], dtype, "step 2")
+
+
+def test_zz_report_bfloat16_margins():
+    """Not a check: prints how much of its allowance the bfloat16 engine used."""
+    if BF16_REPORT:
+        worst = sorted(BF16_REPORT, key=lambda x: -x[1])[:5]
+        mean = sum(r for _, r in BF16_REPORT) / len(BF16_REPORT)
+        print(f"\nbfloat16 error / allowance: mean {mean:.2f} over {len(BF16_REPORT)} checks; worst {worst}")
