@@ -257,6 +257,19 @@ int launch(const AttentionParams& p, int num_tokens, cudaStream_t stream) {
 
 }  // namespace
 
+// Merge partition results written by any of the attention kernels: rows = tokens * heads.
+extern "C" int asb_attention_reduce(void* out, const float* part_m, const float* part_l,
+                                    const float* part_acc, int rows, int NP, int hd, int dtype,
+                                    cudaStream_t stream) {
+  if (rows == 0) return 0;
+  int threads = 32;
+  while (threads < hd && threads < 256) threads <<= 1;
+  ASB_DISPATCH_DTYPE(dtype, T,
+                     attention_reduce_kernel<T><<<rows, threads, 0, stream>>>(
+                         (T*)out, part_m, part_l, part_acc, NP, hd));
+  return asb::check_launch("attention_reduce");
+}
+
 // Query tile geometry for G query heads per kv head: GC heads per block, QT tokens per tile.
 extern "C" void asb_attention_tile_shape(int G, int* QT, int* GC) {
   *GC = G < kMaxRows ? G : kMaxRows;

@@ -10,6 +10,8 @@ from atomserve_b200.ops.library import KernelLibraryError, check, dtype_code, li
 
 KEY_TILE = 32
 TARGET_BLOCKS = 296  # two blocks for each of the 148 SMs before the key range is split
+SHORT_ROWS = 8  # requests with at most this many new tokens run row by row in the decode kernel
+DECODE_TARGET_BLOCKS = 592  # four resident decode blocks per SM keep the HBM stream busy
 
 
 def attention_tile_shape(group: int) -> tuple[int, int]:
@@ -39,6 +41,22 @@ def plan_partitions(num_tokens: int, num_requests: int, num_kv_heads: int, group
     return (size, parts) if parts > 1 else (1 << 30, 1)
 
 
+def plan_decode_partitions(rows: int, num_kv_heads: int, group: int, max_context: int, window: int) -> tuple[int, int]:
+    """(partition size, partitions) for the tensor-core decode kernel: one block per (row, kv
+    head, partition); keys are split until the GPU is full, never below 256 keys a block."""
+    blocks = rows * num_kv_heads * -(-group // 16)
+    span = max_context if window <= 0 else min(max_context, window)
+    if blocks >= DECODE_TARGET_BLOCKS or span <= 256:
+        return 1 << 30, 1
+    want = -(-DECODE_TARGET_BLOCKS // blocks)
+    size = max(256, -(-(-(-span // want)) // 64) * 64)
+    if window <= 0:
+        parts = (max_context - 1) // size + 1
+    else:
+        parts = min((max_context - 1) // size + 1, -(-span // size) + 1)
+    return (size, parts) if parts > 1 else (1 << 30, 1)
+
+
 def paged_attention(
     q: torch.Tensor,
     k_cache: torch.Tensor,
@@ -52,6 +70,8 @@ def paged_attention(
     window: int | None,
     scale: float,
     partitions: tuple[int, int] | None = None,
+    host_q_lens: list[int] | None = None,
+    generic: bool = False,
 ) -> torch.Tensor:
     """softmax(q k^T * scale) v for every new token, keys read in place from the pages.
 
@@ -59,6 +79,11 @@ def paged_attention(
     int32; req_q_start: [R + 1] int32 (rows of each request in q); req_pos_start: [R] int32.
     max_context: the largest position + 1 any request reaches in this step (host int).
     A query at position p sees keys j <= p of its request, and j > p - window with a window.
+
+    bfloat16 with head size 64 or 128 runs the tensor-core kernels (decode kernel for requests
+    that bring at most 8 tokens, prefill kernel for longer portions; `host_q_lens`, the tokens
+    each request brings, tells which are needed); everything else, and `generic=True`, runs the
+    general CUDA-core kernel.
     """
     require_cuda(q, k_cache, v_cache, block_tables, req_q_start, req_pos_start)
     T, H, hd = q.shape
@@ -71,8 +96,11 @@ def paged_attention(
         if t.dtype != torch.int32 or not t.is_contiguous():
             raise KernelLibraryError("paged_attention: index tensors must be contiguous int32")
     win = int(window) if window else 0
-    ps, np_ = partitions or plan_partitions(T, num_requests, KV, H // KV, max_context, win)
     out = torch.empty_like(q)
+    if q.dtype == torch.bfloat16 and not generic and lib().asb_attention_mma_supported(hd, H // KV):
+        return _paged_attention_mma(q, out, k_cache, v_cache, block_tables, req_q_start, req_pos_start,
+                                    num_requests, max_context, win, scale, partitions, host_q_lens)  # fmt: skip
+    ps, np_ = partitions or plan_partitions(T, num_requests, KV, H // KV, max_context, win)
     part_m = part_l = part_acc = None
     if np_ > 1:
         part_m = torch.empty(T * H * np_, device=q.device, dtype=torch.float32)
@@ -82,4 +110,36 @@ def paged_attention(
         ptr(out), ptr(q), ptr(k_cache), ptr(v_cache), ptr(block_tables), ptr(req_q_start),
         ptr(req_pos_start), ptr(part_m), ptr(part_l), ptr(part_acc), T, num_requests, H, KV, hd, bs,
         block_tables.shape[1], win, ps, np_, float(scale), dtype_code(q), stream()))  # fmt: skip
+    return out
+
+
+def _paged_attention_mma(q, out, k_cache, v_cache, block_tables, req_q_start, req_pos_start, num_requests,
+                         max_context, win, scale, partitions, host_q_lens):  # fmt: skip
+    T, H, hd = q.shape
+    KV, bs = k_cache.shape[1], k_cache.shape[2]
+    if host_q_lens is None:
+        has_short = has_long = True
+        all_single = False
+        short_rows = T
+    else:
+        has_short = any(n <= SHORT_ROWS for n in host_q_lens)
+        has_long = any(n > SHORT_ROWS for n in host_q_lens)
+        all_single = all(n == 1 for n in host_q_lens)
+        short_rows = sum(n for n in host_q_lens if n <= SHORT_ROWS)
+    ps, np_ = 1 << 30, 1
+    if has_short and not has_long:
+        ps, np_ = partitions or plan_decode_partitions(short_rows, KV, H // KV, max_context, win)
+    part_m = part_l = part_acc = None
+    if np_ > 1:
+        part_m = torch.empty(T * H * np_, device=q.device, dtype=torch.float32)
+        part_l = torch.empty_like(part_m)
+        part_acc = torch.empty(T * H * np_ * hd, device=q.device, dtype=torch.float32)
+    check(lib().asb_paged_attention_mma(
+        ptr(out), ptr(q), ptr(k_cache), ptr(v_cache), ptr(block_tables), ptr(req_q_start),
+        ptr(req_pos_start), ptr(part_m), ptr(part_l), ptr(part_acc), T, num_requests, H, KV, hd, bs,
+        block_tables.shape[1], win, ps, np_, float(scale), int(has_short), int(has_long), int(all_single),
+        stream()))  # fmt: skip
+    if np_ > 1:
+        check(lib().asb_attention_reduce(ptr(out), ptr(part_m), ptr(part_l), ptr(part_acc), T * H, np_, hd,
+                                         dtype_code(q), stream()))  # fmt: skip
     return out

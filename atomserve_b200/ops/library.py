@@ -31,6 +31,9 @@ _SIGNATURES = {
     "asb_silu_mul": [_P, _P, _I, _I, _I, _P],
     "asb_qk_norm_rope_store": [_P] * 9 + [_I] * 6 + [_F, _I, _P],
     "asb_paged_attention": [_P] * 10 + [_I] * 10 + [_F, _I, _P],
+    "asb_paged_attention_mma": [_P] * 10 + [_I] * 10 + [_F, _I, _I, _I, _P],
+    "asb_attention_reduce": [_P, _P, _P, _P, _I, _I, _I, _I, _P],
+    "asb_attention_mma_supported": [_I, _I],
     "asb_gemm_simt": [_P, _P, _P, _P, _I, _I, _I, _I, _I, _P],
     "asb_argmax_rows": [_P, _P, _I, _I, _P],
     "asb_presence_penalty": [_P, _P, _P, _P, _I, _I, _P],
@@ -76,7 +79,11 @@ def declare(name: str, argtypes: list) -> None:
         fn.argtypes, fn.restype = argtypes, c_int
 
 
+LAUNCHES = [0]  # entry-point calls of this library so far (each launches one to two kernels)
+
+
 def check(code: int) -> None:
+    LAUNCHES[0] += 1
     if code != 0:
         raise KernelLibraryError(lib().asb_last_error().decode())
 

@@ -81,7 +81,7 @@ class GQAttention(Mixer):
         out = ops.paged_attention(
             q, cache.k, cache.v, cache.block_tables, ctx.req_q_start, ctx.req_pos_start,
             num_requests=ctx.num_requests, max_context=ctx.max_context, window=self.window,
-            scale=self.scale,
+            scale=self.scale, host_q_lens=ctx.host_q_lens or None,
         )  # fmt: skip
         return ops.linear(out.view(-1, H * hd), self.o_proj, residual)
 

@@ -1,0 +1,308 @@
+"""Decode and prefill throughput of the engine at Qwen3-8B sizes on one B200.
+
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--layers L] [--impl reference]
+
+A step is one decode step. The default run builds a random-weight model with the layer sizes of
+Qwen3-8B, prefills 8 requests of 2,048 synthetic token ids and times K decode steps on the
+device (CUDA events); the same through the engine's public API with host tokens in and out
+gives `e2e`. It also times a 2,048-token prefill and decode at batch 1 and 64, and prints one
+JSON line. Weights (15 GB) are read once per step and exceed the L2 cache, so no flush is
+needed between timed iterations.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import pathlib
+import subprocess
+import sys
+import time
+
+ROOT = pathlib.Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+QWEN3_8B = dict(
+    architectures=["Qwen3ForCausalLM"], vocab_size=151936, hidden_size=4096, intermediate_size=12288,
+    num_hidden_layers=36, num_attention_heads=32, num_key_value_heads=8, head_dim=128,
+    rms_norm_eps=1e-6, rope_theta=1000000.0, tie_word_embeddings=False, max_position_embeddings=40960,
+)  # fmt: skip
+PROMPT_TOKENS = 2048
+CONTEXT = 4096
+BLOCK_SIZE = 16
+PUBLISHED_8B_BATCH1 = 15.7  # tok/s, the reference's Qwen3-8B bf16 batch-1 decode on an M4 Pro
+
+
+def peaks() -> dict:
+    path = ROOT / "MEASURED_PEAKS.json"
+    if path.exists():
+        raw = json.loads(path.read_text())
+        return {"hbm_gbs": float(raw["hbm_gbs"]), "bf16_tflops": float(raw["bf16_tflops"]),
+                "bf16_tflops_sustained": float(raw.get("bf16_tflops_sustained", raw["bf16_tflops"])), "source": "measured"}  # fmt: skip
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "source": "fallback"}
+
+
+def prompts(batch: int, length: int) -> list[list[int]]:
+    """Distinct synthetic prompts (the reference's bench/engine.py:90-92)."""
+    return [[(1000 + 37 * b + i) % 150000 for i in range(length)] for b in range(batch)]
+
+
+class ClockSampler:
+    def __init__(self):
+        self.proc, self.path = None, ROOT / "gpurun_out" / "bench_clocks.csv"
+
+    def __enter__(self):
+        try:
+            self.path.parent.mkdir(exist_ok=True)
+            self.file = open(self.path, "w")
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "--query-gpu=clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+                 "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+                 "clocks_event_reasons.sw_power_cap", "--format=csv,noheader,nounits", "-lms", "100", "-i", "0"],
+                stdout=self.file, stderr=subprocess.DEVNULL,
+            )  # fmt: skip
+        except OSError:
+            self.proc = None
+        return self
+
+    def __exit__(self, *exc):
+        if self.proc is not None:
+            self.proc.terminate()
+            self.proc.wait()
+            self.file.close()
+
+    def summary(self) -> dict:
+        rows = []
+        try:
+            for line in self.path.read_text().splitlines():
+                parts = [p.strip() for p in line.split(",")]
+                if len(parts) >= 7 and parts[0].isdigit():
+                    rows.append(parts)
+        except OSError:
+            pass
+        if not rows:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["unsampled"]}
+        sm = sorted(int(r[0]) for r in rows)
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = [n for i, n in enumerate(names) if any(r[3 + i].lower().startswith("active") for r in rows)]
+        return {"sm_mhz": sm[len(sm) // 2], "sm_max_mhz": int(rows[0][1]), "reasons": reasons, "samples": len(rows)}
+
+
+def build_engine(layers: int, max_seqs: int):
+    import torch
+
+    from atomserve_b200.config import EngineConfig
+    from atomserve_b200.config.registry import config_from_dict
+    from atomserve_b200.engine.engine import create_engine
+    from atomserve_b200.weights import random_model
+
+    _, config = config_from_dict({**QWEN3_8B, "num_hidden_layers": layers})
+    model = random_model(config, seed=0, dtype="bfloat16", device="cuda")
+    blocks = max_seqs * (CONTEXT // BLOCK_SIZE) + 64
+    engine_config = EngineConfig(block_size=BLOCK_SIZE, num_blocks=blocks, max_num_seqs=max_seqs,
+                                 max_num_batched_tokens=PROMPT_TOKENS, max_model_len=CONTEXT,
+                                 enable_prefix_caching=False)  # fmt: skip
+    torch.cuda.synchronize()
+    return config, model, create_engine(model, engine_config, sampler_seed=0)
+
+
+def step_bytes(config, batch: int, context: int) -> float:
+    """Bytes a decode step has to read: every weight it uses once (all layers and the head;
+    embedding rows are negligible) and the cached keys and values of the live requests."""
+    c = config
+    per_layer = (c.num_attention_heads + 2 * c.num_key_value_heads) * c.head_dim * c.hidden_size \
+        + c.hidden_size * c.num_attention_heads * c.head_dim + 3 * c.intermediate_size * c.hidden_size
+    weights = 2 * (c.num_hidden_layers * per_layer + c.vocab_size * c.hidden_size)
+    kv = 2 * 2 * c.num_key_value_heads * c.head_dim * c.num_hidden_layers * context * batch
+    return float(weights + kv)
+
+
+def prefill_flops(config, tokens: int) -> float:
+    c = config
+    per_layer = (c.num_attention_heads + 2 * c.num_key_value_heads) * c.head_dim * c.hidden_size \
+        + c.hidden_size * c.num_attention_heads * c.head_dim + 3 * c.intermediate_size * c.hidden_size
+    linear = 2.0 * tokens * c.num_hidden_layers * per_layer + 2.0 * c.vocab_size * c.hidden_size
+    attention = c.num_hidden_layers * 4.0 * c.num_attention_heads * c.head_dim * tokens * tokens / 2
+    return linear + attention
+
+
+def time_decode(engine, batch: int, steps: int, warmup: int):
+    """Prefill `batch` requests (untimed), then time `steps` decode steps two ways: on the
+    device around the step function plus argmax, and end to end through Engine.step()."""
+    import torch
+
+    from atomserve_b200 import ops
+    from atomserve_b200.engine.runner import Row
+    from atomserve_b200.engine.sequence import SamplingParams
+    from atomserve_b200.ops.library import LAUNCHES
+
+    runner, cache = engine.runner, engine.runner.cache
+    # --- device-timed: the step function on fixed token ids, positions advancing ---
+    reqs = []
+    for p in prompts(batch, PROMPT_TOKENS):
+        rc = cache.new_request()
+        assert cache.admit(rc) and cache.reserve(rc, 0, PROMPT_TOKENS)
+        runner.step([Row(p, 0, rc, [])])
+        reqs.append(rc)
+    pos = PROMPT_TOKENS
+
+    def one_step(position):
+        rows = []
+        for i, rc in enumerate(reqs):
+            assert cache.reserve(rc, position, 1)
+            rows.append(Row([(7 + 13 * i + position) % 150000], position, rc, [0]))
+        return ops.argmax_rows(runner.step(rows))
+
+    for _ in range(warmup):
+        one_step(pos)
+        pos += 1
+    torch.cuda.synchronize()
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    launches_before = LAUNCHES[0]
+    start.record()
+    for _ in range(steps):
+        one_step(pos)
+        pos += 1
+    end.record()
+    torch.cuda.synchronize()
+    device_ms = start.elapsed_time(end) / steps
+    launches = LAUNCHES[0] - launches_before
+    mid_context = PROMPT_TOKENS + warmup + steps // 2
+    for rc in reqs:
+        cache.free(rc)
+
+    # --- end to end: Engine.step(), host token ids in, sampled ids out, every step ---
+    # long enough that nobody finishes inside the timed region (later requests start later)
+    params = SamplingParams(temperature=0.0, max_tokens=warmup + steps + batch + 16, ignore_eos=True)
+    handles = [engine.submit(p, params) for p in prompts(batch, PROMPT_TOKENS)]
+    while any(h.first_token_at is None for h in handles):
+        engine.step()
+    for _ in range(warmup):
+        engine.step()
+    torch.cuda.synchronize()
+    before = engine.num_generated_tokens
+    t0 = time.perf_counter()
+    for _ in range(steps - 1):
+        engine.step()
+    torch.cuda.synchronize()
+    e2e_s = time.perf_counter() - t0
+    e2e_tokens = engine.num_generated_tokens - before
+    while engine.step():
+        pass
+    for h in handles:
+        list(h)
+    return device_ms, launches, mid_context, e2e_tokens / e2e_s
+
+
+def time_prefill(engine, steps: int, warmup: int) -> float:
+    import torch
+
+    from atomserve_b200.engine.runner import Row
+
+    runner, cache = engine.runner, engine.runner.cache
+    rc = cache.new_request()
+    assert cache.admit(rc) and cache.reserve(rc, 0, PROMPT_TOKENS)
+    row = [Row(prompts(1, PROMPT_TOKENS)[0], 0, rc, [PROMPT_TOKENS - 1])]
+    for _ in range(warmup):
+        runner.step(row)
+    torch.cuda.synchronize()
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    for _ in range(steps):
+        runner.step(row)
+    end.record()
+    torch.cuda.synchronize()
+    cache.free(rc)
+    return start.elapsed_time(end) / steps
+
+
+def main() -> int:
+    parser = argparse.ArgumentParser()
+    parser.add_argument("--gpus", type=int, default=1)
+    parser.add_argument("--steps", type=int, default=64)
+    parser.add_argument("--warmup", type=int, default=8)
+    parser.add_argument("--layers", type=int, default=QWEN3_8B["num_hidden_layers"],
+                        help="fewer layers than the model has (same layer sizes), where time or memory needs it")  # fmt: skip
+    parser.add_argument("--batch", type=int, default=8)
+    parser.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    parser.add_argument("--only", choices=["decode", "prefill"], help="time just this (for profiling small cases)")
+    args = parser.parse_args()
+    if args.impl == "reference":
+        print(json.dumps({"impl": "reference", "unavailable":
+                          "the reference runs on Apple MPS or CPU only (no CUDA path) and does not install here: "
+                          "it needs Python >= 3.14 and the uv_build backend, neither in this image"}))  # fmt: skip
+        return 0
+    if args.gpus != 1:
+        print(f"bench.py measures one GPU; --gpus {args.gpus} is not supported (the engine is single-GPU)")
+        return 2
+    warmup = max(args.warmup, 3)
+
+    import torch
+
+    from atomserve_b200.ops import require_device
+
+    require_device()
+    pk = peaks()
+    config, model, engine = build_engine(args.layers, max_seqs=64)
+    if args.only == "decode":
+        ms, launches, ctx, e2e = time_decode(engine, args.batch, args.steps, warmup)
+        print(json.dumps({"only": "decode", "batch": args.batch, "layers": args.layers, "ms_per_step": round(ms, 4),
+                          "e2e_tokens_per_s": round(e2e, 1), "gpu_launches": launches}))  # fmt: skip
+        return 0
+    if args.only == "prefill":
+        ms = time_prefill(engine, steps=args.steps, warmup=warmup)
+        print(json.dumps({"only": "prefill", "layers": args.layers, "tokens": PROMPT_TOKENS, "ms": round(ms, 3)}))
+        return 0
+    with ClockSampler() as clocks:
+        device_ms, launches, ctx, e2e = time_decode(engine, args.batch, args.steps, warmup)
+    points = {}
+    for b in (1, 64):
+        ms, _, _, e = time_decode(engine, b, max(args.steps // 2, 8), 3)
+        points[f"decode_b{b}"] = round(b * 1000.0 / ms, 1)
+        points[f"decode_b{b}_e2e"] = round(e, 1)
+    prefill_ms = time_prefill(engine, steps=5, warmup=3)
+
+    value = args.batch * 1000.0 / device_ms
+    achieved = step_bytes(config, args.batch, ctx) / (device_ms * 1e-3) / 1e9
+    flops = prefill_flops(config, PROMPT_TOKENS)
+    line = {
+        "metric": "decode tok/s at batch 8 (Qwen3-8B shape, context 2048-4096); prefill tok/s at 2,048 tokens",
+        "value": round(value, 1),
+        "unit": "tokens/s",
+        "n_gpus": 1,
+        "steps": args.steps,
+        "warmup": warmup,
+        "ms_per_step": round(device_ms, 4),
+        "higher_is_better": True,
+        "scaling": "weak",
+        "vs_baseline": None,
+        "dtype": "bf16",
+        "data": "synthetic token ids, random-init weights N(0, 0.02)",
+        "config": {
+            "model": "Qwen3-8B shape", "layers": args.layers, "layers_full": QWEN3_8B["num_hidden_layers"],
+            "hidden": config.hidden_size, "heads": config.num_attention_heads, "kv_heads": config.num_key_value_heads,
+            "head_dim": config.head_dim, "intermediate": config.intermediate_size, "vocab": config.vocab_size,
+            "global_batch": args.batch, "seq_len": CONTEXT, "prompt_tokens": PROMPT_TOKENS, "block_size": BLOCK_SIZE,
+            "parallelism": "single-gpu", "l2": "weights read per step exceed L2; no flush needed", "sampling": "greedy",
+        },
+        "e2e": {"value": round(e2e, 1), "unit": "tokens/s", "h2d_bytes_per_step": 4 * (6 * args.batch + 8 + 2 * args.batch * (CONTEXT // BLOCK_SIZE)),
+                "d2h_bytes_per_step": 4 * args.batch},
+        "gpu_launches": launches * 1,
+        "prefill": {"value": round(PROMPT_TOKENS * 1000.0 / prefill_ms, 1), "tokens": PROMPT_TOKENS, "ms": round(prefill_ms, 3),
+                    "frac": round(flops / (prefill_ms * 1e-3) / (pk["bf16_tflops"] * 1e12), 4)},
+        "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
+                     "frac": round(achieved / pk["hbm_gbs"], 4), "peaks": pk["source"]},
+        "points": points,
+        "clocks": clocks.summary(),
+    }  # fmt: skip
+    if args.layers == QWEN3_8B["num_hidden_layers"] and args.batch == 1:
+        line["vs_baseline"] = round(value / PUBLISHED_8B_BATCH1, 2)
+    elif "decode_b1" in points and args.layers == QWEN3_8B["num_hidden_layers"]:
+        line["vs_baseline"] = round(points["decode_b1"] / PUBLISHED_8B_BATCH1, 2)
+        line["vs_baseline_note"] = "decode_b1 over the reference's published Qwen3-8B batch-1 15.7 tok/s (M4 Pro)"
+    print(json.dumps(line))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

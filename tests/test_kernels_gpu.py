@@ -194,6 +194,13 @@ ATTN_CASES = [
     (6, 3, 32, 8, [200, 77, 24, 25], [1, 30, 24, 2], 24),
     (64, 1, 64, 32, [129], [3], None),
     (16, 8, 256, 16, [90], [90], 17),
+    # head sizes 64 and 128: the tensor-core kernels in bfloat16
+    (10, 2, 64, 8, [300, 77, 150, 9], [1, 40, 5, 9], None),
+    (64, 1, 64, 32, [129, 500], [3, 100], None),
+    (32, 8, 128, 16, [2065, 1000, 65], [1, 1, 1], None),
+    (16, 4, 128, 16, [600, 200], [600, 8], 100),
+    (6, 3, 64, 4, [200, 77, 24, 25], [1, 30, 24, 2], 24),
+    (8, 8, 128, 16, [130], [130], None),
 ]
 
 
@@ -203,14 +210,17 @@ def test_paged_attention(ops, dtype, case):
     H, KV, hd, bs, ctx_lens, q_lens, window = case
     dev, dense, qs = paged_setup(ctx_lens, q_lens, H, KV, hd, bs, dtype)
     ref = attention_reference(qs, dense, ctx_lens, q_lens, window)
-    out = ops.paged_attention(**dev, num_requests=len(ctx_lens), max_context=max(ctx_lens), window=window, scale=hd**-0.5)
+    common = dict(num_requests=len(ctx_lens), max_context=max(ctx_lens), window=window, scale=hd**-0.5)
     t = dict(atol=2e-5, rtol=1e-4) if dtype == torch.float32 else dict(atol=2e-2, rtol=2e-2)
-    assert torch.allclose(out.float().cpu(), ref, **t)
-    # the same with the keys split into partitions of 64 and merged
-    parts = (64, (max(ctx_lens) - 1) // 64 + 1)
-    out2 = ops.paged_attention(**dev, num_requests=len(ctx_lens), max_context=max(ctx_lens), window=window,
-                               scale=hd**-0.5, partitions=parts)  # fmt: skip
-    assert torch.allclose(out2.float().cpu(), ref, **t)
+    parts = (64, (max(ctx_lens) - 1) // 64 + 1)  # the keys split into partitions of 64 and merged
+    for generic in (True, False):  # the general kernel, then whichever kernel serving would pick
+        out = ops.paged_attention(**dev, **common, generic=generic, host_q_lens=q_lens)
+        assert torch.allclose(out.float().cpu(), ref, **t), f"generic={generic}"
+        if generic or max(q_lens) <= 8:
+            out2 = ops.paged_attention(**dev, **common, generic=generic, host_q_lens=q_lens, partitions=parts)
+            assert torch.allclose(out2.float().cpu(), ref, **t), f"generic={generic} partitioned"
+    out3 = ops.paged_attention(**dev, **common)  # without host knowledge of the portions
+    assert torch.allclose(out3.float().cpu(), ref, **t)
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
@@ -220,8 +230,9 @@ def test_attention_finds_one_far_key(ops, dtype, where):
     wherever in its page and partition it lies."""
     H, KV, hd, bs, ctx = 8, 2, 64, 16, 1000
     dev, dense, qs = paged_setup([ctx], [1], H, KV, hd, bs, dtype, seed=where, special=(0, where))
-    for parts in (None, (256, 4)):
-        out = ops.paged_attention(**dev, num_requests=1, max_context=ctx, window=None, scale=hd**-0.5, partitions=parts)
+    for parts, generic in ((None, False), ((256, 4), False), (None, True), ((256, 4), True)):
+        out = ops.paged_attention(**dev, num_requests=1, max_context=ctx, window=None, scale=hd**-0.5,
+                                  partitions=parts, generic=generic, host_q_lens=[1])  # fmt: skip
         v = dense[0][1][where]  # [KV, hd]
         expect = v.repeat_interleave(H // KV, dim=0)
         assert torch.allclose(out[0].float().cpu(), expect, atol=2e-2, rtol=2e-2)
@@ -230,14 +241,17 @@ def test_attention_finds_one_far_key(ops, dtype, where):
 @pytest.mark.parametrize("dtype", DTYPES)
 def test_attention_window_edge(ops, dtype):
     """The key at p - window + 1 is seen, the key at p - window is not."""
-    H, KV, hd, bs, ctx, window = 4, 2, 32, 8, 120, 24
-    p = ctx - 1
-    for where, seen in ((p - window + 1, True), (p - window, False)):
-        dev, dense, qs = paged_setup([ctx], [1], H, KV, hd, bs, dtype, seed=3, special=(0, where))
-        out = ops.paged_attention(**dev, num_requests=1, max_context=ctx, window=window, scale=hd**-0.5)
-        expect = dense[0][1][where].repeat_interleave(H // KV, dim=0)
-        close = torch.allclose(out[0].float().cpu(), expect, atol=2e-2, rtol=2e-2)
-        assert close == seen
+    for hd in (32, 64):
+        H, KV, bs, ctx, window = 4, 2, 8, 120, 24
+        p = ctx - 1
+        for where, seen in ((p - window + 1, True), (p - window, False)):
+            for n in (1, 12):  # as a single decoded token, and as the last row of a portion
+                dev, dense, qs = paged_setup([ctx], [n], H, KV, hd, bs, dtype, seed=3, special=(0, where))
+                out = ops.paged_attention(**dev, num_requests=1, max_context=ctx, window=window, scale=hd**-0.5,
+                                          host_q_lens=[n])  # fmt: skip
+                expect = dense[0][1][where].repeat_interleave(H // KV, dim=0)
+                close = torch.allclose(out[-1].float().cpu(), expect, atol=2e-2, rtol=2e-2)
+                assert close == seen, (hd, where, n)
 
 
 def test_sampling_greedy_and_support(ops):
