@@ -77,6 +77,91 @@ __global__ void qk_norm_rope_store_kernel(
   for (int e = 2 * half + lane; e < hd; e += 32) dst[e] = asb::from_float<T>(s[e]);
 }
 
+// Vector form for head sizes 32, 64, 128, 256 with the whole head rotated: each lane holds EPT
+// consecutive elements, lanes 0-15 the first half of the head and lanes 16-31 the second, so a
+// rotate-half partner is one shuffle away and nothing passes through shared memory. A warp
+// takes kHeadsPerWarp heads of one token and computes the token's sines and cosines once.
+constexpr int kHeadsPerWarp = 4;
+
+template <typename T, int EPT>
+__global__ void qk_norm_rope_store_vec_kernel(
+    T* __restrict__ q_out, T* __restrict__ k_cache, T* __restrict__ v_cache,
+    const T* __restrict__ qkv, const float* __restrict__ q_gain, const float* __restrict__ k_gain,
+    const float* __restrict__ inv_freq, const int* __restrict__ positions,
+    const int* __restrict__ slots, int H, int KV, int block_size, float eps) {
+  constexpr int hd = EPT * 32;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int t = blockIdx.x;
+  const int head_first = (blockIdx.y * kWarps + warp) * kHeadsPerWarp;
+  const int heads = H + 2 * KV;
+  if (head_first >= heads) return;
+  const int slot = slots ? slots[t] : -1;
+  const int e0 = lane * EPT;  // this lane's first element
+
+  float cs[EPT], sn[EPT];
+  if (inv_freq) {
+    const float pos = (float)positions[t];
+    const int i0 = (lane & 15) * EPT;
+#pragma unroll
+    for (int k = 0; k < EPT; ++k) sincosf(pos * inv_freq[i0 + k], &sn[k], &cs[k]);
+  }
+  struct alignas(sizeof(T) * EPT > 16 ? 16 : sizeof(T) * EPT) Vec { T v[EPT]; };
+
+  for (int head = head_first; head < min(head_first + kHeadsPerWarp, heads); ++head) {
+    const bool is_q = head < H;
+    const bool is_k = !is_q && head < H + KV;
+    T* dst;
+    if (is_q) {
+      dst = q_out + ((size_t)t * H + head) * hd;
+    } else {
+      if (slot < 0) continue;
+      const int kvh = is_k ? head - H : head - H - KV;
+      const size_t block = slot / block_size, off = slot % block_size;
+      dst = (is_k ? k_cache : v_cache) + ((block * KV + kvh) * block_size + off) * (size_t)hd;
+    }
+    const Vec in = *reinterpret_cast<const Vec*>(qkv + ((size_t)t * heads + head) * hd + e0);
+    if (!is_q && !is_k) {
+      *reinterpret_cast<Vec*>(dst + e0) = in;
+      continue;
+    }
+    float x[EPT];
+    float ss = 0.f;
+#pragma unroll
+    for (int k = 0; k < EPT; ++k) {
+      x[k] = asb::to_float(in.v[k]);
+      ss += x[k] * x[k];
+    }
+    const float* gain = is_q ? q_gain : k_gain;
+    if (gain) {
+      ss = asb::warp_sum(ss);
+      const float rstd = rsqrtf(ss / (float)hd + eps);
+#pragma unroll
+      for (int k = 0; k < EPT; ++k) x[k] = x[k] * rstd * gain[e0 + k];
+    }
+    Vec o;
+#pragma unroll
+    for (int k = 0; k < EPT; ++k) {
+      float y = x[k];
+      if (inv_freq) {
+        const float other = __shfl_xor_sync(0xffffffffu, x[k], 16);
+        y = lane < 16 ? x[k] * cs[k] - other * sn[k] : x[k] * cs[k] + other * sn[k];
+      }
+      o.v[k] = asb::from_float<T>(y);
+    }
+    *reinterpret_cast<Vec*>(dst + e0) = o;
+  }
+}
+
+template <typename T, int EPT>
+void launch_vec(T* q_out, T* k_cache, T* v_cache, const T* qkv, const float* q_gain,
+                const float* k_gain, const float* inv_freq, const int* positions, const int* slots,
+                int num_tokens, int H, int KV, int block_size, float eps, cudaStream_t stream) {
+  const int heads_per_block = kWarps * kHeadsPerWarp;
+  dim3 grid(num_tokens, (H + 2 * KV + heads_per_block - 1) / heads_per_block);
+  qk_norm_rope_store_vec_kernel<T, EPT><<<grid, kWarps * 32, 0, stream>>>(
+      q_out, k_cache, v_cache, qkv, q_gain, k_gain, inv_freq, positions, slots, H, KV, block_size, eps);
+}
+
 }  // namespace
 
 extern "C" int asb_qk_norm_rope_store(void* q_out, void* k_cache, void* v_cache, const void* qkv,
@@ -90,6 +175,22 @@ extern "C" int asb_qk_norm_rope_store(void* q_out, void* k_cache, void* v_cache,
   if (inv_freq && (rotary_dim < 2 || rotary_dim > hd || rotary_dim % 2))
     return asb::fail("qk_norm_rope_store: rotary_dim %d must be even and <= head_dim %d", rotary_dim, hd);
   if (KV > 0 && (!k_cache || !v_cache) && slots) return asb::fail("qk_norm_rope_store: slots given without a cache");
+  const bool whole_head = !inv_freq || rotary_dim == hd;
+  const bool aligned = ((uintptr_t)q_out % 16 == 0) && ((uintptr_t)qkv % 16 == 0) &&
+                       ((uintptr_t)k_cache % 16 == 0) && ((uintptr_t)v_cache % 16 == 0);
+  if (whole_head && aligned && (hd == 32 || hd == 64 || hd == 128 || hd == 256)) {
+#define ASB_ROPE_VEC(E)                                                                          \
+  ASB_DISPATCH_DTYPE(dtype, T,                                                                   \
+                     launch_vec<T, E>((T*)q_out, (T*)k_cache, (T*)v_cache, (const T*)qkv, q_gain, \
+                                      k_gain, inv_freq, positions, slots, num_tokens, H, KV,     \
+                                      block_size, eps, stream))
+    if (hd == 32) { ASB_ROPE_VEC(1); }
+    else if (hd == 64) { ASB_ROPE_VEC(2); }
+    else if (hd == 128) { ASB_ROPE_VEC(4); }
+    else { ASB_ROPE_VEC(8); }
+#undef ASB_ROPE_VEC
+    return asb::check_launch("qk_norm_rope_store");
+  }
   dim3 grid(num_tokens, (H + 2 * KV + kWarps - 1) / kWarps);
   ASB_DISPATCH_DTYPE(dtype, T,
                      qk_norm_rope_store_kernel<T><<<grid, kWarps * 32, 0, stream>>>(

@@ -162,7 +162,30 @@ __device__ Cut cut_with_ties(const RowView& row, Scratch& s, uint32_t key, unsig
 __device__ int row_argmax(const RowView& row, Scratch& s, float* best_value) {
   float best = -INFINITY;
   int best_id = 0x7fffffff;
-  for (int i = threadIdx.x; i < row.n; i += blockDim.x) {
+  int done = 0;
+  if (row.id == nullptr && ((uintptr_t)row.val & 15) == 0) {
+    // the full row: 16-byte loads, four in flight per thread
+    const float4* v4 = reinterpret_cast<const float4*>(row.val);
+    const int n4 = row.n >> 2;
+    for (int i = threadIdx.x; i < n4; i += blockDim.x * 4) {
+      float4 x[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int at = i + u * blockDim.x;
+        x[u] = at < n4 ? v4[at] : make_float4(-INFINITY, -INFINITY, -INFINITY, -INFINITY);
+      }
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int t0 = (i + u * blockDim.x) * 4;
+        const float e[4] = {x[u].x, x[u].y, x[u].z, x[u].w};
+#pragma unroll
+        for (int k = 0; k < 4; ++k)
+          if (e[k] > best || (e[k] == best && t0 + k < best_id)) { best = e[k]; best_id = t0 + k; }
+      }
+    }
+    done = n4 << 2;
+  }
+  for (int i = done + threadIdx.x; i < row.n; i += blockDim.x) {
     const float v = row.value(i);
     const int t = row.token(i);
     if (v > best || (v == best && t < best_id)) { best = v; best_id = t; }

@@ -82,6 +82,9 @@ def main(argv: list[str] | None = None) -> int:
     out = Path(args.out)
     out.mkdir(parents=True, exist_ok=True)
     print("trace_run: loading model and kernels", file=sys.stderr, flush=True)
+    from atomserve_b200.ops import library
+
+    library.lib()  # compiles the kernels now if this checkout has no current build
     replayer = TraceReplayer(args.model, args.dtype, args.max_tokens, args.block_size)
     print("trace_run: ready", file=sys.stderr, flush=True)
     for line in sys.stdin:

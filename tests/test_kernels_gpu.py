@@ -91,7 +91,8 @@ def rope_reference(x, positions, hd, theta, rotary_dim=None):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("hd,rd,theta", [(16, 16, 1e4), (48, 48, 5e4), (128, 128, 1e6), (256, 64, 1e4)])
+@pytest.mark.parametrize("hd,rd,theta", [(16, 16, 1e4), (48, 48, 5e4), (128, 128, 1e6), (256, 64, 1e4), (32, 32, 1e4),
+                                         (64, 64, 1e6), (256, 256, 5e5)])  # fmt: skip
 def test_rotary_alone(ops, dtype, hd, rd, theta):
     from atomserve_b200.parts.rotary import Rotary
 
@@ -106,7 +107,8 @@ def test_rotary_alone(ops, dtype, hd, rd, theta):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("H,KV,hd,bs", [(4, 2, 16, 16), (5, 1, 48, 8), (32, 8, 128, 16), (16, 16, 80, 4)])
+@pytest.mark.parametrize("H,KV,hd,bs", [(4, 2, 16, 16), (5, 1, 48, 8), (32, 8, 128, 16), (16, 16, 80, 4), (6, 3, 32, 8),
+                                        (9, 3, 64, 16), (4, 4, 256, 8)])  # fmt: skip
 def test_qk_norm_rope_store(ops, dtype, H, KV, hd, bs):
     T, nblocks, eps, theta = 6, 9, 1e-5, 1e6
     qkv = torch.randn(T, (H + 2 * KV) * hd, device="cuda").to(dtype)
