@@ -34,6 +34,7 @@ _SIGNATURES = {
     "asb_paged_attention_mma": [_P] * 10 + [_I] * 10 + [_F, _I, _I, _I, _P],
     "asb_attention_reduce": [_P, _P, _P, _P, _I, _I, _I, _I, _P],
     "asb_attention_mma_supported": [_I, _I],
+    "asb_gemm_tcgen05": [_P, _P, _P, _P, _I, _I, _I, _I, _P, _P, _P],
     "asb_gemm_simt": [_P, _P, _P, _P, _I, _I, _I, _I, _I, _P],
     "asb_argmax_rows": [_P, _P, _I, _I, _P],
     "asb_presence_penalty": [_P, _P, _P, _P, _I, _I, _P],

@@ -23,6 +23,45 @@ def gemm_simt(x: torch.Tensor, w: torch.Tensor, residual: torch.Tensor | None, o
     return out
 
 
+_STATUS: dict[torch.device, torch.Tensor] = {}
+
+
+def gemm_status(device: torch.device) -> torch.Tensor:
+    """The device word the tensor-core GEMM sets if one of its pipeline waits runs out."""
+    if device not in _STATUS:
+        _STATUS[device] = torch.zeros(1, dtype=torch.int32, device=device)
+    return _STATUS[device]
+
+
+def check_gemm_status(device: torch.device | str = "cuda") -> None:
+    """Raise if any tensor-core GEMM since the last check gave up a wait (reads the device)."""
+    status = gemm_status(torch.device(device) if not isinstance(device, torch.device) else device)
+    code = int(status.item())
+    if code:
+        status.zero_()
+        raise KernelLibraryError(f"gemm_tcgen05: a pipeline wait ran out (role {code}: 1 TMA, 2 MMA, 3 epilogue)")
+
+
+def gemm_tcgen05(x: torch.Tensor, w: torch.Tensor, residual: torch.Tensor | None, out_dtype: torch.dtype) -> torch.Tensor:
+    """bfloat16 x [M, K] . w [N, K]^T on tcgen05 tensor cores (TMA operands, TMEM accumulator)."""
+    import ctypes
+
+    M, K = x.shape
+    N = w.shape[0]
+    out = torch.empty(M, N, device=x.device, dtype=out_dtype)
+    splits = ctypes.c_int()
+    lib().asb_gemm_tcgen05_workspace.restype = ctypes.c_longlong
+    need = lib().asb_gemm_tcgen05_workspace(M, N, K, ctypes.byref(splits))
+    workspace = torch.empty(need, device=x.device, dtype=torch.float32) if need else None
+    check(lib().asb_gemm_tcgen05(ptr(out), ptr(x), ptr(w), ptr(residual), M, N, K, int(out_dtype == torch.float32),
+                                 ptr(workspace), ptr(gemm_status(x.device)), stream()))  # fmt: skip
+    return out
+
+
+def tcgen05_supported(x: torch.Tensor, w: torch.Tensor) -> bool:
+    return x.dtype == torch.bfloat16 and x.shape[1] % 8 == 0 and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0
+
+
 def linear(
     x: torch.Tensor,
     w: torch.Tensor,

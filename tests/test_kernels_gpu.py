@@ -341,3 +341,34 @@ def test_presence_penalty(ops):
     expect[0, 3] = expect[0, 4] = -1.5
     expect[1, 9] = -0.5
     assert torch.equal(logits.cpu(), expect)
+
+
+GEMM_SHAPES = [
+    (1, 128, 64), (3, 100, 72), (16, 256, 512), (17, 384, 4096), (33, 130, 1024), (64, 4096, 4096),
+    (8, 4096, 12288), (65, 256, 128), (128, 300, 264), (300, 512, 1000), (2048, 1024, 512),
+]  # fmt: skip
+
+
+@pytest.mark.parametrize("M,N,K", GEMM_SHAPES)
+def test_gemm_tcgen05(ops, M, N, K):
+    """The tcgen05/TMEM/TMA GEMM against float64, in every epilogue, swapped and split shapes
+    included; its status word must stay zero (no pipeline wait ran out)."""
+    from atomserve_b200.ops.linear import check_gemm_status, gemm_tcgen05
+
+    g = torch.Generator().manual_seed(M * 7 + N + K)
+    x = torch.randn(M, K, generator=g).bfloat16().cuda()
+    w = (torch.randn(N, K, generator=g) / math.sqrt(K)).bfloat16().cuda()
+    res = torch.randn(M, N, generator=g).bfloat16().cuda()
+    ref = x.double().cpu() @ w.double().cpu().T
+    full = gemm_tcgen05(x, w, None, torch.float32)
+    check_gemm_status()
+    assert torch.allclose(full.double().cpu(), ref, atol=2e-3, rtol=1e-3), float((full.double().cpu() - ref).abs().max())
+    plain_out = gemm_tcgen05(x, w, None, torch.bfloat16)
+    with_res = gemm_tcgen05(x, w, res, torch.bfloat16)
+    check_gemm_status()
+    assert torch.allclose(plain_out.double().cpu(), ref, atol=3e-2, rtol=2e-2)
+    assert torch.allclose(with_res.double().cpu(), ref + res.double().cpu(), atol=3e-2, rtol=2e-2)
+    # a row's result does not depend on the rows beside it (same kernel shape: same tile path)
+    if M > 1:
+        again = gemm_tcgen05(x, w, None, torch.float32)
+        assert torch.equal(again, full)
