@@ -10,13 +10,22 @@
 // (rows become TMEM columns, tile of BN = 16..256). With many tokens P = x and Q = w. With few
 // tokens (decoding) the operands swap: P = w, so that the 128-row MMA shape is filled with
 // weight rows and the handful of tokens is the narrow N; the kernel then streams weights at
-// HBM speed with a deep TMA pipeline, and splits K over grid.z when there are too few weight
-// tiles to occupy every SM (partials are summed by `splitk_reduce_kernel`).
+// HBM speed with a deep TMA pipeline.
+//
+// The kernel is persistent: one block per SM walks a list of work segments (output tile, range
+// of K blocks), the TMA pipeline running on across segment boundaries. Two schedules: whole
+// tiles dealt round-robin (many tokens), or the flattened (tile, K block) sequence cut into one
+// equal contiguous range per block (few tokens), so that every SM streams the same number of
+// weight bytes whatever the number of tiles. A segment that covers all of K is stored
+// directly; one that covers a part writes float32 partial sums to a workspace slot, and
+// `segment_reduce_kernel` sums a tile's slots afterwards.
 //
 // Warp roles (192 threads): warp 0 issues TMA loads, warp 1 allocates TMEM and issues MMAs,
 // warps 2-5 run the epilogue (warp w reads TMEM lanes 32*(w%4)..+31). Stages are handed over
 // with mbarriers: full[s] (TMA bytes landed) and empty[s] (tcgen05.commit after the MMAs that
-// read stage s), and one barrier tells the epilogue that the accumulator is complete.
+// read stage s). The accumulator is double-buffered in TMEM: acc_full[b] tells the epilogue
+// that buffer b is complete, acc_empty[b] tells the MMA warp that it has been read out, so the
+// epilogue of one segment overlaps the MMAs of the next.
 //
 // Every wait on a barrier is bounded. A wait that runs out sets *status (non-zero) and the
 // role stops waiting; all roles still meet at the final barrier, TMEM is freed and the block
@@ -36,15 +45,63 @@ constexpr uint32_t kMaxPolls = 1u << 24;
 enum Epilogue : int { kStoreBf16 = 0, kStoreBf16Residual = 1, kStoreF32 = 2, kStorePartial = 3 };
 
 struct GemmParams {
-  void* out;             // bf16 or f32 [M, N]; for partials f32 [splits, M, N]
+  void* out;             // bf16 or f32 [M, N]
   const void* residual;  // bf16 [M, N] or null
+  float* workspace;      // f32 [tiles][max_slots][128][BN] partial sums (stream schedule)
   int* status;           // device word, set non-zero by a wait that ran out
   int p_rows, q_rows;    // rows of P and Q (M and N, or N and M when swapped)
   int ldo;               // row stride of out (N)
-  int K, kb_per_split;   // K blocks of BK each split handles
   int swap;              // 1: P = w (lanes are output columns), Q = x
-  int epilogue;
-  long long split_stride;  // elements between split partials (M * N)
+  int epilogue;          // for whole segments: kStoreBf16 / kStoreBf16Residual / kStoreF32
+  int tiles_p, num_tiles;  // tile t -> (t % tiles_p, t / tiles_p)
+  int kb_per_tile;       // K blocks of BK per tile
+  int stream;            // 0: whole tiles round-robin; 1: equal contiguous ranges of K blocks
+  int max_slots;         // workspace slots per tile
+};
+
+// First flattened K block of block c's range when `total` K blocks are cut into `parts` ranges.
+__host__ __device__ __forceinline__ long long range_begin(long long total, int parts, int c) {
+  return total * c / parts;
+}
+
+// The block whose range holds flattened K block `pos` (the largest c with range_begin(c) <= pos).
+__host__ __device__ __forceinline__ int block_of(long long total, int parts, long long pos) {
+  int c = (int)(pos * parts / total);
+  if (c >= parts) c = parts - 1;
+  while (c + 1 < parts && range_begin(total, parts, c + 1) <= pos) ++c;
+  while (c > 0 && range_begin(total, parts, c) > pos) --c;
+  return c;
+}
+
+// Walks the segments of one block: the same sequence in every warp role.
+struct SegmentWalk {
+  int tile, kb0, kb1;       // current segment
+  long long pos, end;       // stream schedule
+  int step, stream, kb_per_tile, num_tiles;
+  __device__ SegmentWalk(const GemmParams& p) {
+    stream = p.stream; kb_per_tile = p.kb_per_tile; num_tiles = p.num_tiles; step = gridDim.x;
+    if (stream) {
+      const long long total = (long long)p.num_tiles * p.kb_per_tile;
+      pos = range_begin(total, gridDim.x, blockIdx.x);
+      end = range_begin(total, gridDim.x, blockIdx.x + 1);
+    } else {
+      pos = blockIdx.x; end = p.num_tiles;
+    }
+  }
+  __device__ bool next() {
+    if (pos >= end) return false;
+    if (stream) {
+      tile = (int)(pos / kb_per_tile);
+      kb0 = (int)(pos - (long long)tile * kb_per_tile);
+      const long long left = end - pos;
+      kb1 = (int)((long long)kb_per_tile - kb0 < left ? kb_per_tile : kb0 + left);
+      pos += kb1 - kb0;
+    } else {
+      tile = (int)pos; kb0 = 0; kb1 = kb_per_tile;
+      pos += step;
+    }
+    return true;
+  }
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -121,9 +178,13 @@ struct Config {
   static constexpr int kTileQ = BN * BK * 2;
   static constexpr int kStage = kTileP + kTileQ;
   static constexpr int kStages = BN >= 256 ? 4 : (BN >= 128 ? 6 : 8);
-  static constexpr int kTmemCols = BN < 32 ? 32 : BN;
+  static constexpr int kTmemCols = 2 * BN < 32 ? 32 : 2 * BN;   // two accumulators
   static constexpr int kSmem = kStages * kStage + 1024 /* alignment slack */ + 256 /* barriers */;
 };
+
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
 
 template <int BN>
 __global__ void __launch_bounds__(kThreads, 1)
@@ -136,21 +197,21 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_cons
   const uint32_t bars = base + C::kStages * C::kStage;
   auto full_bar = [&](int s) { return bars + 8u * s; };
   auto empty_bar = [&](int s) { return bars + 8u * (C::kStages + s); };
-  const uint32_t acc_bar = bars + 8u * (2 * C::kStages);
-  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(aligned + C::kStages * C::kStage + 8 * (2 * C::kStages + 1));
+  auto acc_full = [&](int b) { return bars + 8u * (2 * C::kStages + b); };
+  auto acc_empty = [&](int b) { return bars + 8u * (2 * C::kStages + 2 + b); };
+  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(aligned + C::kStages * C::kStage + 8 * (2 * C::kStages + 4));
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int p0 = blockIdx.x * BM, q0 = blockIdx.y * BN;
-  const int total_kb = (p.K + BK - 1) / BK;
-  const int kb_begin = blockIdx.z * p.kb_per_split;
-  const int num_kb = min(p.kb_per_split, total_kb - kb_begin);
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < C::kStages; ++s) {
       mbar_init(full_bar(s), 1);
       mbar_init(empty_bar(s), 1);
     }
-    mbar_init(acc_bar, 1);
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(acc_full(b), 1);
+      mbar_init(acc_empty(b), 4);  // one arrival per epilogue warp
+    }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 1) {
@@ -163,82 +224,127 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_cons
   const uint32_t tmem_base = *tmem_slot;
 
   if (warp == 0) {
-    if (lane == 0 && num_kb > 0) {
-      for (int i = 0; i < num_kb; ++i) {
-        const int s = i % C::kStages;
-        const uint32_t phase = (uint32_t)(i / C::kStages) & 1u;
-        if (!mbar_wait(empty_bar(s), phase ^ 1u, p.status, 1)) break;
-        mbar_expect_tx(full_bar(s), C::kStage);
-        const int k0 = (kb_begin + i) * BK;
-        tma_load_2d(base + s * C::kStage, &map_p, full_bar(s), k0, p0);
-        tma_load_2d(base + s * C::kStage + C::kTileP, &map_q, full_bar(s), k0, q0);
+    if (lane == 0) {
+      SegmentWalk walk(p);
+      uint32_t it = 0;  // K blocks loaded so far by this block, across segments
+      bool ok = true;
+      while (ok && walk.next()) {
+        const int p0 = (walk.tile % p.tiles_p) * BM, q0 = (walk.tile / p.tiles_p) * BN;
+        for (int kb = walk.kb0; kb < walk.kb1; ++kb, ++it) {
+          const int s = it % C::kStages;
+          const uint32_t phase = (it / C::kStages) & 1u;
+          ok = mbar_wait(empty_bar(s), phase ^ 1u, p.status, 1);
+          if (!ok) break;
+          mbar_expect_tx(full_bar(s), C::kStage);
+          tma_load_2d(base + s * C::kStage, &map_p, full_bar(s), kb * BK, p0);
+          tma_load_2d(base + s * C::kStage + C::kTileP, &map_q, full_bar(s), kb * BK, q0);
+        }
       }
     }
   } else if (warp == 1) {
-    if (lane == 0 && num_kb > 0) {
+    if (lane == 0) {
       constexpr uint32_t idesc = instr_desc(BM, BN);
+      SegmentWalk walk(p);
+      uint32_t it = 0, seg = 0;
       bool ok = true;
-      for (int i = 0; i < num_kb && ok; ++i) {
-        const int s = i % C::kStages;
-        const uint32_t phase = (uint32_t)(i / C::kStages) & 1u;
-        ok = mbar_wait(full_bar(s), phase, p.status, 2);
+      while (ok && walk.next()) {
+        const uint32_t buf = seg & 1u;
+        // the epilogue must have read this accumulator out (its use two segments ago)
+        ok = mbar_wait(acc_empty(buf), ((seg >> 1) & 1u) ^ 1u, p.status, 4);
         if (!ok) break;
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        const uint64_t da = smem_desc(base + s * C::kStage);
-        const uint64_t db = smem_desc(base + s * C::kStage + C::kTileP);
+        const uint32_t tmem_acc = tmem_base + buf * BN;
+        for (int kb = walk.kb0; kb < walk.kb1; ++kb, ++it) {
+          const int s = it % C::kStages;
+          const uint32_t phase = (it / C::kStages) & 1u;
+          ok = mbar_wait(full_bar(s), phase, p.status, 2);
+          if (!ok) break;
+          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+          const uint64_t da = smem_desc(base + s * C::kStage);
+          const uint64_t db = smem_desc(base + s * C::kStage + C::kTileP);
 #pragma unroll
-        for (int k = 0; k < BK / UMMA_K; ++k)  // 32 bytes further along K inside the swizzle atom
-          umma(tmem_base, da + (uint64_t)(k * UMMA_K * 2 >> 4), db + (uint64_t)(k * UMMA_K * 2 >> 4), idesc,
-               (uint32_t)((i | k) != 0));
-        umma_commit(empty_bar(s));  // stage s may be refilled once these MMAs have read it
+          for (int k = 0; k < BK / UMMA_K; ++k)  // 32 bytes further along K inside the swizzle atom
+            umma(tmem_acc, da + (uint64_t)(k * UMMA_K * 2 >> 4), db + (uint64_t)(k * UMMA_K * 2 >> 4), idesc,
+                 (uint32_t)((kb > walk.kb0) | (k != 0)));
+          umma_commit(empty_bar(s));  // stage s may be refilled once these MMAs have read it
+        }
+        umma_commit(acc_full(buf));  // arrives when every MMA of this segment has completed
+        ++seg;
       }
-      umma_commit(acc_bar);  // arrives when every MMA issued above has completed
     }
   } else {
     // Epilogue: this warp owns TMEM lanes 32*(warp%4)..+31, one lane (P row) per thread.
     const int quad = warp & 3;
-    const int prow = p0 + quad * 32 + lane;
-    int ok_i = num_kb > 0;
-    if (ok_i && lane == 0) ok_i = mbar_wait(acc_bar, 0, p.status, 3) ? 1 : 0;  // one poller per warp
-    const bool ok = __shfl_sync(0xffffffffu, ok_i, 0) != 0;
-    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-    if (ok) {
+    SegmentWalk walk(p);
+    uint32_t seg = 0;
+    bool ok = true;
+    while (ok && walk.next()) {
+      const uint32_t buf = seg & 1u;
+      int ok_i = 1;
+      if (lane == 0) ok_i = mbar_wait(acc_full(buf), (seg >> 1) & 1u, p.status, 3) ? 1 : 0;  // one poller per warp
+      ok = __shfl_sync(0xffffffffu, ok_i, 0) != 0;
+      if (!ok) break;
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      const int p0 = (walk.tile % p.tiles_p) * BM, q0 = (walk.tile / p.tiles_p) * BN;
+      const int prow = p0 + quad * 32 + lane;
+      const bool whole = walk.kb0 == 0 && walk.kb1 == p.kb_per_tile;
+      float* slot = nullptr;
+      if (!whole) {
+        const long long total = (long long)p.num_tiles * p.kb_per_tile;
+        const int first = block_of(total, gridDim.x, (long long)walk.tile * p.kb_per_tile);
+        // slot layout follows the output's contiguous dimension: [lane][column] when lanes are
+        // tokens, [column][lane] when lanes are output columns (swapped operands)
+        slot = p.workspace + ((size_t)walk.tile * p.max_slots + (blockIdx.x - first)) * BM * BN;
+      }
       constexpr int kChunk = 16;
 #pragma unroll 1
       for (int c = 0; c < BN; c += kChunk) {
-        if (q0 + c >= p.q_rows) break;  // uniform: depends on the block and c only
+        if (q0 + c >= p.q_rows) break;  // uniform: depends on the segment and c only
         uint32_t raw[16];
-        tmem_ld16(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)c, raw);
+        tmem_ld16(tmem_base + ((uint32_t)(quad * 32) << 16) + buf * BN + (uint32_t)c, raw);
+        if (!whole) {  // partial sums; rows beyond the matrix hold zeros
+          const int row = quad * 32 + lane;
+          if (p.swap) {
+#pragma unroll
+            for (int j = 0; j < kChunk; ++j) slot[(size_t)(c + j) * BM + row] = __uint_as_float(raw[j]);
+          } else {
+#pragma unroll
+            for (int j = 0; j < kChunk; j += 4)
+              *reinterpret_cast<uint4*>(slot + (size_t)row * BN + c + j) = make_uint4(raw[j], raw[j + 1], raw[j + 2], raw[j + 3]);
+          }
+          continue;
+        }
         if (prow >= p.p_rows) continue;
         if (p.swap) {
           // lanes are output columns (weight rows), TMEM columns are tokens: out[token, prow]
 #pragma unroll
           for (int j = 0; j < kChunk; ++j) {
             const int tok = q0 + c + j;
-            if (tok >= p.q_rows) break;
-            const size_t at = (size_t)tok * p.ldo + prow;
-            float v = __uint_as_float(raw[j]);
-            if (p.epilogue == kStorePartial) {
-              ((float*)p.out)[(size_t)blockIdx.z * p.split_stride + at] = v;
-            } else if (p.epilogue == kStoreF32) {
-              ((float*)p.out)[at] = v;
-            } else {
-              if (p.epilogue == kStoreBf16Residual) v += __bfloat162float(((const __nv_bfloat16*)p.residual)[at]);
-              ((__nv_bfloat16*)p.out)[at] = __float2bfloat16_rn(v);
+            if (tok < p.q_rows) {
+              const size_t at = (size_t)tok * p.ldo + prow;
+              float v = __uint_as_float(raw[j]);
+              if (p.epilogue == kStoreF32) {
+                ((float*)p.out)[at] = v;
+              } else {
+                if (p.epilogue == kStoreBf16Residual) v += __bfloat162float(((const __nv_bfloat16*)p.residual)[at]);
+                ((__nv_bfloat16*)p.out)[at] = __float2bfloat16_rn(v);
+              }
             }
           }
         } else {
           // lanes are tokens, TMEM columns are output columns: out[prow, q0 + c + j], contiguous in j
           const size_t at = (size_t)prow * p.ldo + q0 + c;
           const int valid = min(kChunk, p.q_rows - (q0 + c));
-          if (p.epilogue == kStorePartial || p.epilogue == kStoreF32) {
-            float* o = (float*)p.out + (p.epilogue == kStorePartial ? (size_t)blockIdx.z * p.split_stride : 0) + at;
+          if (p.epilogue == kStoreF32) {
+            float* o = (float*)p.out + at;
             if (valid == kChunk && (((uintptr_t)o) & 15) == 0) {
 #pragma unroll
               for (int j = 0; j < kChunk; j += 4)
                 *reinterpret_cast<uint4*>(o + j) = make_uint4(raw[j], raw[j + 1], raw[j + 2], raw[j + 3]);
             } else {
-              for (int j = 0; j < valid; ++j) o[j] = __uint_as_float(raw[j]);
+#pragma unroll
+              for (int j = 0; j < kChunk; ++j)
+                if (j < valid) o[j] = __uint_as_float(raw[j]);
             }
           } else {
             __nv_bfloat16* o = (__nv_bfloat16*)p.out + at;
@@ -261,15 +367,23 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_cons
               *reinterpret_cast<uint4*>(o) = ov[0];
               *reinterpret_cast<uint4*>(o + 8) = ov[1];
             } else {
-              for (int j = 0; j < valid; ++j) {
-                float v = __uint_as_float(raw[j]);
-                if (res) v += __bfloat162float(res[j]);
-                o[j] = __float2bfloat16_rn(v);
-              }
+#pragma unroll
+              for (int j = 0; j < kChunk; ++j)
+                if (j < valid) {
+                  float v = __uint_as_float(raw[j]);
+                  if (res) v += __bfloat162float(res[j]);
+                  o[j] = __float2bfloat16_rn(v);
+                }
             }
           }
         }
       }
+      // this warp has read its lanes of the accumulator: hand the buffer back to the MMA warp
+      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+      __syncwarp();
+      if (lane == 0) mbar_arrive(acc_empty(buf));
+      ++seg;
+
     }
   }
 
@@ -281,16 +395,41 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_cons
   }
 }
 
-// out[m, n] = sum over splits of partial[s, m, n] (+ residual), rounded once.
-__global__ void splitk_reduce_kernel(void* __restrict__ out, const float* __restrict__ partial,
-                                     const __nv_bfloat16* __restrict__ residual, long long total,
-                                     int splits, int out_f32) {
-  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
-       i += (long long)gridDim.x * blockDim.x) {
-    float v = 0.f;
-    for (int s = 0; s < splits; ++s) v += partial[(size_t)s * total + i];
-    if (residual) v += __bfloat162float(residual[i]);
-    if (out_f32) ((float*)out)[i] = v; else ((__nv_bfloat16*)out)[i] = __float2bfloat16_rn(v);
+// Sums the workspace slots of every tile that was computed in parts, adds the residual and
+// stores in the output's orientation. grid = (tiles, pieces of the tile); each thread owns four
+// consecutive elements along the output's contiguous dimension. Tiles stored whole are skipped.
+template <int BN>
+__global__ void segment_reduce_kernel(const GemmParams p, int parts) {
+  const int tile = blockIdx.x;
+  const long long total = (long long)p.num_tiles * p.kb_per_tile;
+  const long long begin = (long long)tile * p.kb_per_tile;
+  const int first = block_of(total, parts, begin), last = block_of(total, parts, begin + p.kb_per_tile - 1);
+  const int slots = last - first + 1;
+  if (slots == 1) return;  // one block covered all of K and stored the tile itself
+  const int p0 = (tile % p.tiles_p) * BM, q0 = (tile / p.tiles_p) * BN;
+  const float* ws = p.workspace + (size_t)tile * p.max_slots * BM * BN;
+  const int i = (blockIdx.y * blockDim.x + threadIdx.x) * 4;
+  if (i >= BM * BN) return;
+  float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+  for (int s = 0; s < slots; ++s) {
+    const float4 a = *reinterpret_cast<const float4*>(ws + (size_t)s * BM * BN + i);
+    v.x += a.x; v.y += a.y; v.z += a.z; v.w += a.w;
+  }
+  const float e[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+  for (int k = 0; k < 4; ++k) {
+    // slot layout: [column][lane] when swapped, [lane][column] otherwise
+    const int row = p.swap ? (i + k) % BM : (i + k) / BN, col = p.swap ? (i + k) / BM : (i + k) % BN;
+    const int prow = p0 + row, qrow = q0 + col;
+    if (prow >= p.p_rows || qrow >= p.q_rows) continue;
+    const size_t at = p.swap ? (size_t)qrow * p.ldo + prow : (size_t)prow * p.ldo + qrow;
+    float o = e[k];
+    if (p.epilogue == kStoreF32) {
+      ((float*)p.out)[at] = o;
+    } else {
+      if (p.epilogue == kStoreBf16Residual) o += __bfloat162float(((const __nv_bfloat16*)p.residual)[at]);
+      ((__nv_bfloat16*)p.out)[at] = __float2bfloat16_rn(o);
+    }
   }
 }
 
@@ -325,18 +464,7 @@ int make_map(CUtensorMap* map, const void* ptr, int rows, int K, int box_rows) {
   return 0;
 }
 
-template <int BN>
-int launch(const CUtensorMap& mp, const CUtensorMap& mq, const GemmParams& p, dim3 grid, cudaStream_t stream) {
-  auto kern = gemm_tcgen05_kernel<BN>;
-  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Config<BN>::kSmem);
-  if (e != cudaSuccess) return asb::fail("gemm_tcgen05: shared memory %d: %s", Config<BN>::kSmem, cudaGetErrorString(e));
-  kern<<<grid, kThreads, Config<BN>::kSmem, stream>>>(mp, mq, p);
-  return asb::check_launch("gemm_tcgen05");
-}
-
-}  // namespace
-
-static int sm_count() {
+int sm_count() {
   static int count = 0;
   if (!count) {
     int device = 0;
@@ -347,47 +475,76 @@ static int sm_count() {
   return count;
 }
 
-// How the shape is run: operands swap at up to 64 tokens. One block runs per SM, so K is split
-// where that shortens the slowest SM's share of the weight stream by more than the float32
-// partial sums cost to write and read back; every split keeps at least four K blocks.
-static void plan(int M, int N, int K, int* swap, int* bn, int* splits, int* kb_per_split) {
-  *swap = M <= 64 ? 1 : 0;
-  const int total_kb = (K + BK - 1) / BK;
-  int best = 1;
-  if (*swap) {
-    *bn = M <= 16 ? 16 : (M <= 32 ? 32 : 64);
-    const int tiles = (N + BM - 1) / BM, sms = sm_count();
-    const double weight_bytes = 2.0 * N * K;
-    double best_cost = 0;
-    for (int s = 1; s <= 16 && total_kb / s >= 4; ++s) {
-      const int waves = (tiles * s + sms - 1) / sms;
-      // bytes the busiest SM streams, scaled to the whole device, plus the partials' round trip
-      double cost = weight_bytes * waves * sms / ((double)tiles * s);
-      if (s > 1) cost += 2.0 * s * M * N * 4.0;
-      if (s == 1 || cost < best_cost * 0.97) {
-        best_cost = cost;
-        best = s;
-      }
-    }
-  } else {
-    *bn = N <= 128 ? 128 : 256;
+struct Plan {
+  int swap, bn, tiles_p, tiles_q, kb_per_tile, stream, blocks, max_slots;
+  long long workspace;  // float32 elements
+};
+
+// How a shape is run. Operands swap at up to 64 tokens. One block runs per SM. Whole tiles are
+// dealt round-robin unless cutting the flattened K-block sequence into equal ranges shortens
+// the busiest SM's share of the operand stream by more than the partial sums cost to write and
+// read back.
+Plan make_plan(int M, int N, int K) {
+  Plan pl;
+  pl.swap = M <= 64 ? 1 : 0;
+  pl.bn = pl.swap ? (M <= 16 ? 16 : (M <= 32 ? 32 : 64)) : (N <= 128 ? 128 : 256);
+  const int p_rows = pl.swap ? N : M, q_rows = pl.swap ? M : N;
+  pl.tiles_p = (p_rows + BM - 1) / BM;
+  pl.tiles_q = (q_rows + pl.bn - 1) / pl.bn;
+  pl.kb_per_tile = (K + BK - 1) / BK;
+  const int tiles = pl.tiles_p * pl.tiles_q, sms = sm_count();
+  const long long total = (long long)tiles * pl.kb_per_tile;
+  // whole tiles: the busiest block runs ceil(tiles / blocks) tiles
+  const int whole_blocks = tiles < sms ? tiles : sms;
+  const double whole_cost = (double)((tiles + whole_blocks - 1) / whole_blocks) * pl.kb_per_tile;
+  // equal ranges: every block runs total / blocks K blocks (at least four), plus the partials
+  int stream_blocks = (int)(total / 4 < sms ? total / 4 : sms);
+  if (stream_blocks < 1) stream_blocks = 1;
+  const double per_block = (double)total / stream_blocks;
+  const double kb_bytes = (double)(BM + pl.bn) * BK * 2;             // operand bytes one K block brings
+  const double cut_tiles = stream_blocks < tiles ? stream_blocks : tiles;  // tiles a range boundary falls into
+  const double partial_bytes = 2.0 * 2.0 * cut_tiles * BM * pl.bn * 4;     // two slots each, written and read
+  const double stream_cost = per_block + partial_bytes / kb_bytes / stream_blocks;
+  pl.stream = pl.swap && stream_cost < whole_cost * 0.95 ? 1 : 0;  // partial tiles of many tokens are too large to pay
+  pl.blocks = pl.stream ? stream_blocks : whole_blocks;
+  pl.max_slots = 0;
+  pl.workspace = 0;
+  if (pl.stream) {
+    const long long shortest = total / pl.blocks;  // the shortest range
+    pl.max_slots = (int)((pl.kb_per_tile + shortest - 1) / shortest) + 1;
+    pl.workspace = (long long)tiles * pl.max_slots * BM * pl.bn;
   }
-  const int per = (total_kb + best - 1) / best;
-  *splits = (total_kb + per - 1) / per;  // no empty split
-  *kb_per_split = per;
+  return pl;
 }
 
-// Float32 workspace elements a call needs (0 when K is not split).
-extern "C" long long asb_gemm_tcgen05_workspace(int M, int N, int K, int* splits_out) {
-  int swap, bn, splits, per;
-  plan(M, N, K, &swap, &bn, &splits, &per);
-  if (splits_out) *splits_out = splits;
-  return splits > 1 ? (long long)splits * M * N : 0;
+template <int BN>
+int launch(const CUtensorMap& mp, const CUtensorMap& mq, const GemmParams& p, const Plan& pl, cudaStream_t stream) {
+  auto kern = gemm_tcgen05_kernel<BN>;
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Config<BN>::kSmem);
+  if (e != cudaSuccess) return asb::fail("gemm_tcgen05: shared memory %d: %s", Config<BN>::kSmem, cudaGetErrorString(e));
+  kern<<<pl.blocks, kThreads, Config<BN>::kSmem, stream>>>(mp, mq, p);
+  if (int rc = asb::check_launch("gemm_tcgen05")) return rc;
+  if (pl.stream) {
+    segment_reduce_kernel<BN><<<dim3(p.num_tiles, (BM * BN / 4 + 255) / 256), 256, 0, stream>>>(p, pl.blocks);
+    return asb::check_launch("gemm_tcgen05 segment_reduce");
+  }
+  return 0;
+}
+
+}  // namespace
+
+// Float32 workspace elements a call needs (0 when every tile is computed whole).
+extern "C" long long asb_gemm_tcgen05_workspace(int M, int N, int K, int* stream_out) {
+  if (M <= 0 || N <= 0 || K <= 0) return 0;
+  const Plan pl = make_plan(M, N, K);
+  if (stream_out) *stream_out = pl.stream;
+  return pl.workspace;
 }
 
 // out = x . w^T (+ residual). x [M, K] and w [N, K] bfloat16, contiguous, K a multiple of 8 and
 // both bases 16-byte aligned (TMA's rules). out bfloat16 [M, N], or float32 when out_f32.
-// workspace: float32, asb_gemm_tcgen05_workspace(M, N, K) elements (null if that is 0).
+// workspace: float32, asb_gemm_tcgen05_workspace(M, N, K) elements (null if that is 0); calls that
+// may overlap on the GPU need separate workspaces.
 // status: one int on the device; it stays 0 unless a pipeline wait ran out.
 extern "C" int asb_gemm_tcgen05(void* out, const void* x, const void* w, const void* residual, int M,
                                 int N, int K, int out_f32, float* workspace, int* status,
@@ -397,49 +554,32 @@ extern "C" int asb_gemm_tcgen05(void* out, const void* x, const void* w, const v
   if (((uintptr_t)x & 15) || ((uintptr_t)w & 15)) return asb::fail("gemm_tcgen05: operands must be 16-byte aligned");
   if (out_f32 && residual) return asb::fail("gemm_tcgen05: the float32 result form takes no residual");
   if (!status) return asb::fail("gemm_tcgen05: a status word is required");
-  int swap, bn, splits, per;
-  plan(M, N, K, &swap, &bn, &splits, &per);
-  if (splits > 1 && !workspace) return asb::fail("gemm_tcgen05: %d K splits need a workspace", splits);
+  const Plan pl = make_plan(M, N, K);
+  if (pl.workspace > 0 && !workspace) return asb::fail("gemm_tcgen05: this shape needs a workspace of %lld floats", pl.workspace);
 
   GemmParams p;
-  p.status = status;
-  p.K = K;
-  p.kb_per_split = per;
-  p.swap = swap;
-  p.ldo = N;
-  p.split_stride = (long long)M * N;
-  p.p_rows = swap ? N : M;
-  p.q_rows = swap ? M : N;
+  p.out = out;
   p.residual = residual;
-  if (splits > 1) {
-    p.out = workspace;
-    p.epilogue = kStorePartial;
-  } else {
-    p.out = out;
-    p.epilogue = out_f32 ? kStoreF32 : (residual ? kStoreBf16Residual : kStoreBf16);
-  }
+  p.workspace = workspace;
+  p.status = status;
+  p.swap = pl.swap;
+  p.ldo = N;
+  p.p_rows = pl.swap ? N : M;
+  p.q_rows = pl.swap ? M : N;
+  p.epilogue = out_f32 ? kStoreF32 : (residual ? kStoreBf16Residual : kStoreBf16);
+  p.tiles_p = pl.tiles_p;
+  p.num_tiles = pl.tiles_p * pl.tiles_q;
+  p.kb_per_tile = pl.kb_per_tile;
+  p.stream = pl.stream;
+  p.max_slots = pl.max_slots;
   alignas(64) CUtensorMap mp, mq;
-  if (int rc = make_map(&mp, swap ? w : x, p.p_rows, K, BM)) return rc;
-  if (int rc = make_map(&mq, swap ? x : w, p.q_rows, K, bn)) return rc;
-  dim3 grid((p.p_rows + BM - 1) / BM, (p.q_rows + bn - 1) / bn, splits);
-  if (grid.y > 65535 || grid.z > 65535) return asb::fail("gemm_tcgen05: grid too large");
-  int rc = 0;
-  switch (bn) {
-    case 16: rc = launch<16>(mp, mq, p, grid, stream); break;
-    case 32: rc = launch<32>(mp, mq, p, grid, stream); break;
-    case 64: rc = launch<64>(mp, mq, p, grid, stream); break;
-    case 128: rc = launch<128>(mp, mq, p, grid, stream); break;
-    default: rc = launch<256>(mp, mq, p, grid, stream); break;
+  if (int rc = make_map(&mp, pl.swap ? w : x, p.p_rows, K, BM)) return rc;
+  if (int rc = make_map(&mq, pl.swap ? x : w, p.q_rows, K, pl.bn)) return rc;
+  switch (pl.bn) {
+    case 16: return launch<16>(mp, mq, p, pl, stream);
+    case 32: return launch<32>(mp, mq, p, pl, stream);
+    case 64: return launch<64>(mp, mq, p, pl, stream);
+    case 128: return launch<128>(mp, mq, p, pl, stream);
+    default: return launch<256>(mp, mq, p, pl, stream);
   }
-  if (rc) return rc;
-  if (splits > 1) {
-    const long long total = (long long)M * N;
-    const int threads = 256;
-    long long blocks = (total + threads - 1) / threads;
-    if (blocks > 148 * 8) blocks = 148 * 8;
-    splitk_reduce_kernel<<<(unsigned)blocks, threads, 0, stream>>>(out, workspace, (const __nv_bfloat16*)residual,
-                                                                  total, splits, out_f32);
-    return asb::check_launch("splitk_reduce");
-  }
-  return 0;
 }

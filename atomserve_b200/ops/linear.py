@@ -1,13 +1,17 @@
 """y = x W^T (+ residual), weights in checkpoint layout [out_features, in_features].
 
 float32 operands run this package's CUDA-core kernel with float32 multiply-adds (no tensor-core
-mode of reduced precision). bfloat16 operands go to the vendor GEMM library through torch, as
-the reference engine does for its matrix products (atomserve/quant.py:89-91); the float32
-result form (`out_dtype=torch.float32`, for logits) asks the library for its float32
+mode of reduced precision). bfloat16 operands run this package's tcgen05 kernel (TMA operands,
+float32 accumulator in tensor memory; csrc/gemm_tcgen05.cu). The vendor GEMM library through
+torch, which is what the reference engine uses for its matrix products
+(atomserve/quant.py:89-91), stays selectable for comparison and takes the shapes the kernel
+refuses. The float32 result form (`out_dtype=torch.float32`, for logits) stores the float32
 accumulator, so logits are never rounded to bfloat16.
 """
 
 from __future__ import annotations
+
+import os
 
 import torch
 
@@ -22,6 +26,11 @@ def gemm_simt(x: torch.Tensor, w: torch.Tensor, residual: torch.Tensor | None, o
                               dtype_code(out), stream()))  # fmt: skip
     return out
 
+
+# Which bfloat16 GEMM serves: "tcgen05" (this package's kernel, the default) or "library" (the
+# vendor GEMM through torch), for comparison. Shapes the kernel refuses (K not a multiple of 8,
+# unaligned operands) go to the library either way.
+BACKEND = os.environ.get("ATOMSERVE_B200_GEMM", "tcgen05")
 
 _STATUS: dict[torch.device, torch.Tensor] = {}
 
@@ -42,6 +51,19 @@ def check_gemm_status(device: torch.device | str = "cuda") -> None:
         raise KernelLibraryError(f"gemm_tcgen05: a pipeline wait ran out (role {code}: 1 TMA, 2 MMA, 3 epilogue)")
 
 
+_WORKSPACE: dict[torch.device, torch.Tensor] = {}
+
+
+def gemm_workspace(device: torch.device, floats: int) -> torch.Tensor:
+    """One float32 buffer per device for the partial sums of tensor-core GEMM calls that cut K
+    (they run on one stream, one after another, so they can share it). Grown, never shrunk."""
+    buf = _WORKSPACE.get(device)
+    if buf is None or buf.numel() < floats:
+        buf = torch.zeros(max(floats, 1 << 22), device=device, dtype=torch.float32)
+        _WORKSPACE[device] = buf
+    return buf
+
+
 def gemm_tcgen05(x: torch.Tensor, w: torch.Tensor, residual: torch.Tensor | None, out_dtype: torch.dtype) -> torch.Tensor:
     """bfloat16 x [M, K] . w [N, K]^T on tcgen05 tensor cores (TMA operands, TMEM accumulator)."""
     import ctypes
@@ -49,10 +71,9 @@ def gemm_tcgen05(x: torch.Tensor, w: torch.Tensor, residual: torch.Tensor | None
     M, K = x.shape
     N = w.shape[0]
     out = torch.empty(M, N, device=x.device, dtype=out_dtype)
-    splits = ctypes.c_int()
     lib().asb_gemm_tcgen05_workspace.restype = ctypes.c_longlong
-    need = lib().asb_gemm_tcgen05_workspace(M, N, K, ctypes.byref(splits))
-    workspace = torch.empty(need, device=x.device, dtype=torch.float32) if need else None
+    need = lib().asb_gemm_tcgen05_workspace(M, N, K, None)
+    workspace = gemm_workspace(x.device, need) if need else None
     check(lib().asb_gemm_tcgen05(ptr(out), ptr(x), ptr(w), ptr(residual), M, N, K, int(out_dtype == torch.float32),
                                  ptr(workspace), ptr(gemm_status(x.device)), stream()))  # fmt: skip
     return out
@@ -80,9 +101,11 @@ def linear(
         if out_dtype != torch.float32:
             raise KernelLibraryError("linear: float32 operands give float32 results")
         return gemm_simt(x, w, residual, torch.float32)
+    if out_dtype == torch.float32 and residual is not None:
+        return gemm_simt(x, w, residual, torch.float32)
+    if BACKEND == "tcgen05" and tcgen05_supported(x, w):
+        return gemm_tcgen05(x, w, residual, out_dtype)
     if out_dtype == torch.float32:
-        if residual is not None:
-            return gemm_simt(x, w, residual, torch.float32)
         return torch.mm(x, w.t(), out_dtype=torch.float32)  # float32 accumulator, not rounded
     if residual is None:
         return torch.mm(x, w.t())

@@ -216,6 +216,59 @@ def time_prefill(engine, steps: int, warmup: int) -> float:
     return start.elapsed_time(end) / steps
 
 
+def time_gemms(which: str, tokens: list[int], steps: int) -> None:
+    """Device time of this package's tcgen05 GEMM and of the vendor library's on the model's
+    five weight shapes, replayed from a CUDA graph (no host time), rotating over several weight
+    copies so that no call finds its weights in L2. One JSON line per (shape, tokens)."""
+    import torch
+
+    from atomserve_b200.ops.linear import check_gemm_status, gemm_tcgen05
+
+    c = QWEN3_8B
+    qkv_rows = (c["num_attention_heads"] + 2 * c["num_key_value_heads"]) * c["head_dim"]
+    shapes = {
+        "qkv": (qkv_rows, c["hidden_size"]), "o": (c["hidden_size"], c["num_attention_heads"] * c["head_dim"]),
+        "gate_up": (2 * c["intermediate_size"], c["hidden_size"]), "down": (c["hidden_size"], c["intermediate_size"]),
+        "lm_head": (c["vocab_size"], c["hidden_size"]),
+    }  # fmt: skip
+
+    def graph_time(fn, n):
+        for i in range(3):
+            fn(i)
+        torch.cuda.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            for i in range(n):
+                fn(i)
+        g.replay()
+        torch.cuda.synchronize()
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        g.replay()
+        end.record()
+        torch.cuda.synchronize()
+        return start.elapsed_time(end) / n * 1000
+
+    for name, (N, K) in shapes.items():
+        if which not in ("all", name):
+            continue
+        copies = 2 if name == "lm_head" else 6
+        ws = [(torch.randn(N, K, device="cuda") * 0.02).bfloat16() for _ in range(copies)]
+        for M in tokens:
+            if name == "lm_head" and M > 256:
+                continue
+            x = torch.randn(M, K, device="cuda").bfloat16()
+            dt = torch.float32 if name == "lm_head" else torch.bfloat16
+            library = graph_time(lambda i: torch.mm(x, ws[i % copies].t(), out_dtype=dt) if dt == torch.float32
+                                 else torch.mm(x, ws[i % copies].t()), steps)  # fmt: skip
+            mine = graph_time(lambda i: gemm_tcgen05(x, ws[i % copies], None, dt), steps)
+            check_gemm_status()
+            print(json.dumps({"gemm": name, "tokens": M, "N": N, "K": K, "tcgen05_us": round(mine, 1),
+                              "library_us": round(library, 1), "tcgen05_tbs": round(N * K * 2 / mine / 1e6, 2),
+                              "tcgen05_tflops": round(2 * M * N * K / mine / 1e6, 1)}))  # fmt: skip
+        del ws
+
+
 def main() -> int:
     parser = argparse.ArgumentParser()
     parser.add_argument("--gpus", type=int, default=1)
@@ -225,7 +278,9 @@ def main() -> int:
                         help="fewer layers than the model has (same layer sizes), where time or memory needs it")  # fmt: skip
     parser.add_argument("--batch", type=int, default=8)
     parser.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    parser.add_argument("--only", choices=["decode", "prefill"], help="time just this (for profiling small cases)")
+    parser.add_argument("--only", choices=["decode", "prefill", "gemm"], help="time just this (for profiling small cases)")
+    parser.add_argument("--gemm-shape", default="all", help="with --only gemm: qkv, o, gate_up, down, lm_head or all")
+    parser.add_argument("--gemm-tokens", default="1,8,64,2048", help="with --only gemm: token counts, comma-separated")
     args = parser.parse_args()
     if args.impl == "reference":
         print(json.dumps({"impl": "reference", "unavailable":
@@ -243,6 +298,9 @@ def main() -> int:
 
     require_device()
     pk = peaks()
+    if args.only == "gemm":
+        time_gemms(args.gemm_shape, [int(t) for t in args.gemm_tokens.split(",")], max(args.steps // 4, 4))
+        return 0
     config, model, engine = build_engine(args.layers, max_seqs=64)
     if args.only == "decode":
         ms, launches, ctx, e2e = time_decode(engine, args.batch, args.steps, warmup)
