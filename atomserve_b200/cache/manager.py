@@ -20,6 +20,7 @@ manager, which keeps the groups in step: a reservation succeeds in every group o
 
 from __future__ import annotations
 
+import itertools
 from dataclasses import dataclass, field
 
 import torch
@@ -36,6 +37,8 @@ class RequestCache:
     block_tables: list[list[int]]
     state_slot: int = -1
     block_hashes: list[bytes] = field(default_factory=list)  # of full, computed pages (prefix cache)
+    uid: int = field(default_factory=itertools.count().__next__)  # never reused, unlike id()
+    generation: int = 0  # bumped whenever the tables are emptied: copies of them are then stale
 
     @property
     def block_table(self) -> list[int]:
@@ -164,6 +167,7 @@ class CacheManager:
             if held:
                 g.allocator.free(held)
             table.clear()
+        rc.generation += 1
         rc.block_hashes.clear()
         if rc.state_slot >= 0:
             self.state.give_back(rc.state_slot)

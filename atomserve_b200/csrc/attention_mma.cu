@@ -8,7 +8,7 @@
 //            writes (max, sum, accumulator) for the reduction kernel of attention_simt.cu.
 //            Serves every request that brings at most kShortRows tokens in the step; each of
 //            those tokens is its own row with its own context length.
-//   prefill  one block per (request, tile of query tokens, kv head): 64 rows = (token, head)
+//   prefill  one block per (request, tile of query tokens, kv head): 128 rows = (token, head)
 //            pairs, sixteen per warp, all key tiles up to the tile's last position, causal and
 //            window masks from absolute positions. Serves the longer portions.
 //
@@ -42,7 +42,7 @@ struct MmaParams {
   float* part_acc;           // [T, H, NP, HD]
   int T, R, H, KV, bs, table_width;
   int G, GC, HC;             // heads per kv head, heads per block (<= 16), chunks per kv head
-  int QT;                    // prefill: tokens per 64-row tile
+  int QT;                    // prefill: tokens per 128-row tile
   int window, PS, NP;
   int all_single;            // every request brings exactly one token: request = row
   float scale;
@@ -78,6 +78,11 @@ __device__ __forceinline__ void mma_bf16(float (&d)[4], const uint32_t (&a)[4], 
       : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
       : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
 __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
   __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
   return *reinterpret_cast<uint32_t*>(&v);
@@ -90,11 +95,11 @@ __device__ __forceinline__ uint32_t tile_offset(int row, int chunk) {
 }
 
 // Copy keys [kt0, kt0 + 64) of one kv head into a tile; rows outside [key_lo, key_hi) are zero.
-template <int HD>
+template <int HD, int NT = kThreads>
 __device__ __forceinline__ void load_kv_tile(uint32_t k_tile, uint32_t v_tile, const MmaParams& p,
                                              const int* table, int kvh, int kt0, int key_lo, int key_hi) {
-  constexpr int kChunks = HD / 8;                    // 16-byte chunks per row
-  constexpr int kRowsPerPass = kThreads / kChunks;   // rows covered by one pass of the block
+  constexpr int kChunks = HD / 8;              // 16-byte chunks per row
+  constexpr int kRowsPerPass = NT / kChunks;   // rows covered by one pass of the block
   const int chunk = threadIdx.x % kChunks;
   const int row0 = threadIdx.x / kChunks;
 #pragma unroll
@@ -128,6 +133,89 @@ __device__ __forceinline__ void qk_16keys(float (&s)[2][4], const uint32_t (&qf)
     ldmatrix_x4(b, k_tile + tile_offset<HD>(krow, kc * 2 + kchunk));
     mma_bf16(s[0], qf[kc], b[0], b[1]);
     mma_bf16(s[1], qf[kc], b[2], b[3]);
+  }
+#pragma unroll
+  for (int j = 0; j < 2; ++j)
+#pragma unroll
+    for (int e = 0; e < 4; ++e) s[j][e] *= scale;
+}
+
+// One warp: scores of its 16 rows against all 64 keys of a tile. The eight accumulators advance
+// together along the head dimension, so eight independent MMA chains are in flight.
+template <int HD>
+__device__ __forceinline__ void qk_64keys(float (&s)[kKeyTile / 8][4], const uint32_t (&qf)[HD / 16][4],
+                                          uint32_t k_tile, int lane, float scale) {
+#pragma unroll
+  for (int j = 0; j < kKeyTile / 8; ++j)
+#pragma unroll
+    for (int e = 0; e < 4; ++e) s[j][e] = 0.f;
+  const int krow = (lane & 7) + ((lane >> 4) << 3);
+  const int kchunk = (lane >> 3) & 1;
+#pragma unroll
+  for (int kc = 0; kc < HD / 16; ++kc) {
+#pragma unroll
+    for (int sub = 0; sub < kKeyTile / 16; ++sub) {
+      uint32_t b[4];
+      ldmatrix_x4(b, k_tile + tile_offset<HD>(sub * 16 + krow, kc * 2 + kchunk));
+      mma_bf16(s[sub * 2], qf[kc], b[0], b[1]);
+      mma_bf16(s[sub * 2 + 1], qf[kc], b[2], b[3]);
+    }
+  }
+#pragma unroll
+  for (int j = 0; j < kKeyTile / 8; ++j)
+#pragma unroll
+    for (int e = 0; e < 4; ++e) s[j][e] *= scale;
+}
+
+// The same with the Q fragments read from shared memory as they are needed, which frees the
+// HD/4 registers that holding them costs (the prefill kernel runs two blocks per SM that way).
+template <int HD>
+__device__ __forceinline__ void qk_64keys_smem_q(float (&s)[kKeyTile / 8][4], uint32_t q_tile, int q_row0,
+                                                 uint32_t k_tile, int lane, float scale) {
+#pragma unroll
+  for (int j = 0; j < kKeyTile / 8; ++j)
+#pragma unroll
+    for (int e = 0; e < 4; ++e) s[j][e] = 0.f;
+  const int krow = (lane & 7) + ((lane >> 4) << 3);
+  const int kchunk = (lane >> 3) & 1;
+  const int qrow = q_row0 + (lane & 7) + (((lane >> 3) & 1) << 3);
+  const int qchunk = lane >> 4;
+#pragma unroll
+  for (int kc = 0; kc < HD / 16; ++kc) {
+    uint32_t a[4];
+    ldmatrix_x4(a, q_tile + tile_offset<HD>(qrow, kc * 2 + qchunk));
+#pragma unroll
+    for (int sub = 0; sub < kKeyTile / 16; ++sub) {
+      uint32_t b[4];
+      ldmatrix_x4(b, k_tile + tile_offset<HD>(sub * 16 + krow, kc * 2 + kchunk));
+      mma_bf16(s[sub * 2], a, b[0], b[1]);
+      mma_bf16(s[sub * 2 + 1], a, b[2], b[3]);
+    }
+  }
+#pragma unroll
+  for (int j = 0; j < kKeyTile / 8; ++j)
+#pragma unroll
+    for (int e = 0; e < 4; ++e) s[j][e] *= scale;
+}
+
+template <int HD>
+__device__ __forceinline__ void qk_16keys_smem_q(float (&s)[2][4], uint32_t q_tile, int q_row0, uint32_t k_tile,
+                                                 int key0, int lane, float scale) {
+#pragma unroll
+  for (int j = 0; j < 2; ++j)
+#pragma unroll
+    for (int e = 0; e < 4; ++e) s[j][e] = 0.f;
+  const int krow = key0 + (lane & 7) + ((lane >> 4) << 3);
+  const int kchunk = (lane >> 3) & 1;
+  const int qrow = q_row0 + (lane & 7) + (((lane >> 3) & 1) << 3);
+  const int qchunk = lane >> 4;
+#pragma unroll
+  for (int kc = 0; kc < HD / 16; ++kc) {
+    uint32_t a[4], b[4];
+    ldmatrix_x4(a, q_tile + tile_offset<HD>(qrow, kc * 2 + qchunk));
+    ldmatrix_x4(b, k_tile + tile_offset<HD>(krow, kc * 2 + kchunk));
+    mma_bf16(s[0], a, b[0], b[1]);
+    mma_bf16(s[1], a, b[2], b[3]);
   }
 #pragma unroll
   for (int j = 0; j < 2; ++j)
@@ -342,15 +430,18 @@ decode_attention_kernel(const MmaParams p) {
 
 // ---- prefill -----------------------------------------------------------------------------------
 
+constexpr int kPrefillThreads = 256;  // eight warps of sixteen rows
+constexpr int kPrefillRows = 128;
+
 template <int HD>
-__global__ void __launch_bounds__(kThreads)
+__global__ void __launch_bounds__(kPrefillThreads, 2)
 prefill_attention_kernel(const MmaParams p) {
   extern __shared__ __align__(128) unsigned char smem_raw[];
   constexpr int kTileBytes = kKeyTile * HD * 2;
   const uint32_t smem = smem_u32(smem_raw);
   auto k_stage = [&](int i) { return smem + (uint32_t)(i & 1) * kTileBytes; };
   auto v_stage = [&](int i) { return smem + (uint32_t)(2 + (i & 1)) * kTileBytes; };
-  const uint32_t q_tile = smem + 4 * kTileBytes;  // 64 rows
+  const uint32_t q_tile = smem + 4 * kTileBytes;  // 128 rows
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   // Which request and tile of its tokens? Only requests with more than kShortRows tokens count.
@@ -359,7 +450,10 @@ prefill_attention_kernel(const MmaParams p) {
     q_len = p.req_q_start[r + 1] - p.req_q_start[r];
     if (q_len <= kShortRows) continue;
     const int tiles = (q_len + p.QT - 1) / p.QT;
-    if (tile < tiles) break;
+    if (tile < tiles) {
+      tile = tiles - 1 - tile;  // late tiles see the most keys: start them first
+      break;
+    }
     tile -= tiles;
   }
   if (r >= p.R) return;
@@ -378,7 +472,7 @@ prefill_attention_kernel(const MmaParams p) {
 
   {
     constexpr int kChunks = HD / 8;
-    for (int i = threadIdx.x; i < 64 * kChunks; i += kThreads) {
+    for (int i = threadIdx.x; i < kPrefillRows * kChunks; i += kPrefillThreads) {
       const int rr = i / kChunks, c = i % kChunks;
       uint4 v = make_uint4(0, 0, 0, 0);
       if (rr < num_rows) {
@@ -410,74 +504,104 @@ prefill_attention_kernel(const MmaParams p) {
   const int warp_first = warp * 16, warp_last = min(warp * 16 + 15, num_rows - 1);
   const int warp_hi = warp_first < num_rows ? pos0 + warp_last / gc + 1 : 0;
   const int warp_lo = p.window > 0 ? max(0, pos0 + warp_first / gc - p.window + 1) : 0;
+  const int warp_min_pos = pos0 + warp_first / gc;            // position of the warp's first row
+  const int warp_max_pos = warp_hi - 1;                       // and of its last real row
+  const bool warp_full = warp_first + 15 < num_rows;          // no padding rows in this warp
 
   const int kt_begin = (key_lo / kKeyTile) * kKeyTile;
   const int num_tiles = (key_hi - kt_begin + kKeyTile - 1) / kKeyTile;
-  load_kv_tile<HD>(k_stage(0), v_stage(0), p, table, kvh, kt_begin, key_lo, key_hi);
+  load_kv_tile<HD, kPrefillThreads>(k_stage(0), v_stage(0), p, table, kvh, kt_begin, key_lo, key_hi);
   cp_async_commit();
-  __syncthreads();
-  uint32_t qf[HD / 16][4];
-  load_q_frags<HD>(qf, q_tile, warp * 16, lane);
+  __syncthreads();  // the Q tile is in shared memory; fragments are read from it as needed
 
   for (int it = 0; it < num_tiles; ++it) {
     const int kt0 = kt_begin + it * kKeyTile;
     if (it + 1 < num_tiles)
-      load_kv_tile<HD>(k_stage(it + 1), v_stage(it + 1), p, table, kvh, kt0 + kKeyTile, key_lo, key_hi);
+      load_kv_tile<HD, kPrefillThreads>(k_stage(it + 1), v_stage(it + 1), p, table, kvh, kt0 + kKeyTile, key_lo, key_hi);
     cp_async_commit();
     cp_async_wait<1>();
     __syncthreads();
 
     if (kt0 < warp_hi && kt0 + kKeyTile > warp_lo) {
+      // Scores of this warp's 16 rows against all 64 keys of the tile, in units of log2(e) so that
+      // the exponentials are bare ex2 instructions; 16-key groups no row can see are skipped.
+      float s[kKeyTile / 8][4];
+      bool live[kKeyTile / 16];
+      const bool all_live = kt0 + kKeyTile <= warp_hi && kt0 >= warp_lo;  // uniform in the warp
+      if (all_live) {
+#pragma unroll
+        for (int sub = 0; sub < kKeyTile / 16; ++sub) live[sub] = true;
+        qk_64keys_smem_q<HD>(s, q_tile, warp * 16, k_stage(it), lane, p.scale * 1.4426950408889634f);
+      } else
 #pragma unroll
       for (int sub = 0; sub < kKeyTile / 16; ++sub) {
-        const int key0 = sub * 16;
-        if (kt0 + key0 >= warp_hi || kt0 + key0 + 16 <= warp_lo) continue;  // uniform in the warp
-        float s[2][4];
-        qk_16keys<HD>(s, qf, k_stage(it), key0, lane, p.scale);
-        float rmax[2] = {-INFINITY, -INFINITY};
-#pragma unroll
-        for (int j = 0; j < 2; ++j)
+        live[sub] = kt0 + sub * 16 < warp_hi && kt0 + sub * 16 + 16 > warp_lo;  // uniform in the warp
+        if (live[sub]) {
+          float part[2][4];
+          qk_16keys_smem_q<HD>(part, q_tile, warp * 16, k_stage(it), sub * 16, lane, p.scale * 1.4426950408889634f);
 #pragma unroll
           for (int e = 0; e < 4; ++e) {
-            const int key = kt0 + key0 + j * 8 + (lane & 3) * 2 + (e & 1);
+            s[sub * 2][e] = part[0][e];
+            s[sub * 2 + 1][e] = part[1][e];
+          }
+        } else {
+#pragma unroll
+          for (int e = 0; e < 4; ++e) s[sub * 2][e] = s[sub * 2 + 1][e] = -INFINITY;
+        }
+      }
+      // Masks are needed only where the tile touches a row's own position, the window's edge or
+      // the ends of the key range; tiles strictly inside every row's view skip them.
+      const bool inside = warp_full && kt0 + kKeyTile <= warp_min_pos + 1 && kt0 >= key_lo && kt0 + kKeyTile <= key_hi &&
+                          (p.window <= 0 || kt0 > warp_max_pos - p.window);
+      float rmax[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+      for (int j = 0; j < kKeyTile / 8; ++j)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          if (!inside) {
+            const int key = kt0 + j * 8 + (lane & 3) * 2 + (e & 1);
             const int qp = qpos[e >> 1];
             const bool visible = key <= qp && key >= key_lo && (p.window <= 0 || key > qp - p.window);
             if (!visible) s[j][e] = -INFINITY;
-            rmax[e >> 1] = fmaxf(rmax[e >> 1], s[j][e]);
           }
-        float corr[2], rsum[2] = {0.f, 0.f}, m_use[2];
+          rmax[e >> 1] = fmaxf(rmax[e >> 1], s[j][e]);
+        }
+      float corr[2], rsum[2] = {0.f, 0.f}, m_use[2];
 #pragma unroll
-        for (int h = 0; h < 2; ++h) {
-          rmax[h] = fmaxf(rmax[h], __shfl_xor_sync(0xffffffffu, rmax[h], 1));
-          rmax[h] = fmaxf(rmax[h], __shfl_xor_sync(0xffffffffu, rmax[h], 2));
-          const float m_new = fmaxf(m[h], rmax[h]);
-          // a row that has seen nothing yet keeps max -inf: use 0 in the exponent to avoid inf - inf
-          m_use[h] = m_new == -INFINITY ? 0.f : m_new;
-          corr[h] = __expf(m[h] - m_use[h]);
-          m[h] = m_new;
+      for (int h = 0; h < 2; ++h) {
+        rmax[h] = fmaxf(rmax[h], __shfl_xor_sync(0xffffffffu, rmax[h], 1));
+        rmax[h] = fmaxf(rmax[h], __shfl_xor_sync(0xffffffffu, rmax[h], 2));
+        const float m_new = fmaxf(m[h], rmax[h]);
+        // a row that has seen nothing yet keeps max -inf: use 0 in the exponent to avoid inf - inf
+        m_use[h] = m_new == -INFINITY ? 0.f : m_new;
+        corr[h] = fast_exp2(m[h] - m_use[h]);
+        m[h] = m_new;
+      }
+#pragma unroll
+      for (int j = 0; j < kKeyTile / 8; ++j)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const float pe = fast_exp2(s[j][e] - m_use[e >> 1]);
+          s[j][e] = pe;
+          rsum[e >> 1] += pe;
         }
 #pragma unroll
-        for (int j = 0; j < 2; ++j)
+      for (int h = 0; h < 2; ++h) {
+        rsum[h] += __shfl_xor_sync(0xffffffffu, rsum[h], 1);
+        rsum[h] += __shfl_xor_sync(0xffffffffu, rsum[h], 2);
+        l[h] = l[h] * corr[h] + rsum[h];
+      }
 #pragma unroll
-          for (int e = 0; e < 4; ++e) {
-            const float pe = __expf(s[j][e] - m_use[e >> 1]);
-            s[j][e] = pe;
-            rsum[e >> 1] += pe;
-          }
+      for (int i = 0; i < HD / 8; ++i) {
+        acc[i][0] *= corr[0]; acc[i][1] *= corr[0];
+        acc[i][2] *= corr[1]; acc[i][3] *= corr[1];
+      }
 #pragma unroll
-        for (int h = 0; h < 2; ++h) {
-          rsum[h] += __shfl_xor_sync(0xffffffffu, rsum[h], 1);
-          rsum[h] += __shfl_xor_sync(0xffffffffu, rsum[h], 2);
-          l[h] = l[h] * corr[h] + rsum[h];
-        }
-#pragma unroll
-        for (int i = 0; i < HD / 8; ++i) {
-          acc[i][0] *= corr[0]; acc[i][1] *= corr[0];
-          acc[i][2] *= corr[1]; acc[i][3] *= corr[1];
-        }
-        const uint32_t pf[4] = {pack_bf16(s[0][0], s[0][1]), pack_bf16(s[0][2], s[0][3]),
-                                pack_bf16(s[1][0], s[1][1]), pack_bf16(s[1][2], s[1][3])};
-        pv_16keys<HD>(acc, pf, v_stage(it), key0, lane);
+      for (int sub = 0; sub < kKeyTile / 16; ++sub) {
+        if (!live[sub]) continue;
+        const uint32_t pf[4] = {pack_bf16(s[sub * 2][0], s[sub * 2][1]), pack_bf16(s[sub * 2][2], s[sub * 2][3]),
+                                pack_bf16(s[sub * 2 + 1][0], s[sub * 2 + 1][1]), pack_bf16(s[sub * 2 + 1][2], s[sub * 2 + 1][3])};
+        pv_16keys<HD>(acc, pf, v_stage(it), sub * 16, lane);
       }
     }
     __syncthreads();
@@ -512,12 +636,12 @@ int launch_mma(const MmaParams& p, int run_decode, int run_prefill, cudaStream_t
     if (int rc = asb::check_launch("decode_attention")) return rc;
   }
   if (run_prefill) {
-    const int smem = 4 * kTileBytes + 64 * HD * 2;
+    const int smem = 4 * kTileBytes + kPrefillRows * HD * 2;
     auto kern = prefill_attention_kernel<HD>;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) return asb::fail("prefill_attention: %s", cudaGetErrorString(e));
     dim3 grid((p.T + p.QT - 1) / p.QT + p.R, p.KV * p.HC, 1);
-    kern<<<grid, kThreads, smem, stream>>>(p);
+    kern<<<grid, kPrefillThreads, smem, stream>>>(p);
     if (int rc = asb::check_launch("prefill_attention")) return rc;
   }
   return 0;
@@ -532,10 +656,10 @@ extern "C" int asb_attention_mma_supported(int hd, int group) {
 
 // Rows of requests with at most 8 new tokens go through the decode kernel (`run_decode`), longer
 // portions through the prefill kernel (`run_prefill`); the caller says which kinds the step
-// holds. Partitions (PS, NP) apply to the decode kernel only; with NP > 1 the caller runs the
-// reduction over the scratch afterwards (asb_attention_reduce), and the prefill kernel's rows
-// must not be in the same launch pair unless NP == 1 or the reduction skips them: the scratch
-// then has to hold a full entry for every row, so mixed steps use NP == 1.
+// holds. Partitions (PS, NP) apply to the decode kernel only, so steps that also hold longer
+// portions use NP == 1. With NP > 1 every block writes (max, sum, accumulator) to the scratch
+// and the caller runs asb_attention_reduce over it afterwards. (Letting the last block to arrive
+// merge the partitions inside this kernel was measured and was slower than the second launch.)
 extern "C" int asb_paged_attention_mma(void* out, const void* q, const void* k_cache,
                                        const void* v_cache, const int* block_tables,
                                        const int* req_q_start, const int* req_pos_start,
@@ -560,7 +684,7 @@ extern "C" int asb_paged_attention_mma(void* out, const void* q, const void* k_c
   p.G = H / KV;
   p.GC = p.G < 16 ? p.G : 16;
   p.HC = (p.G + p.GC - 1) / p.GC;
-  p.QT = 64 / p.GC;
+  p.QT = kPrefillRows / p.GC;
   if (p.KV * p.HC > 65535) return asb::fail("paged_attention_mma: too many head chunks");
   p.window = window; p.PS = PS; p.NP = NP; p.all_single = all_single; p.scale = scale;
   if (hd == 64) return launch_mma<64>(p, run_decode, run_prefill, stream);

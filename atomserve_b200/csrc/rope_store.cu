@@ -80,10 +80,10 @@ __global__ void qk_norm_rope_store_kernel(
 // Vector form for head sizes 32, 64, 128, 256 with the whole head rotated: each lane holds EPT
 // consecutive elements, lanes 0-15 the first half of the head and lanes 16-31 the second, so a
 // rotate-half partner is one shuffle away and nothing passes through shared memory. A warp
-// takes kHeadsPerWarp heads of one token and computes the token's sines and cosines once.
-constexpr int kHeadsPerWarp = 4;
-
-template <typename T, int EPT>
+// takes kHeadsPerWarp heads of one token and computes the token's sines and cosines once: four
+// heads when there are many tokens, one when there are few (decoding), where spreading the
+// heads over more warps matters more than saving the trigonometry.
+template <typename T, int EPT, int kHeadsPerWarp>
 __global__ void qk_norm_rope_store_vec_kernel(
     T* __restrict__ q_out, T* __restrict__ k_cache, T* __restrict__ v_cache,
     const T* __restrict__ qkv, const float* __restrict__ q_gain, const float* __restrict__ k_gain,
@@ -156,10 +156,16 @@ template <typename T, int EPT>
 void launch_vec(T* q_out, T* k_cache, T* v_cache, const T* qkv, const float* q_gain,
                 const float* k_gain, const float* inv_freq, const int* positions, const int* slots,
                 int num_tokens, int H, int KV, int block_size, float eps, cudaStream_t stream) {
-  const int heads_per_block = kWarps * kHeadsPerWarp;
-  dim3 grid(num_tokens, (H + 2 * KV + heads_per_block - 1) / heads_per_block);
-  qk_norm_rope_store_vec_kernel<T, EPT><<<grid, kWarps * 32, 0, stream>>>(
-      q_out, k_cache, v_cache, qkv, q_gain, k_gain, inv_freq, positions, slots, H, KV, block_size, eps);
+  if (num_tokens >= 256) {
+    const int heads_per_block = kWarps * 4;
+    dim3 grid(num_tokens, (H + 2 * KV + heads_per_block - 1) / heads_per_block);
+    qk_norm_rope_store_vec_kernel<T, EPT, 4><<<grid, kWarps * 32, 0, stream>>>(
+        q_out, k_cache, v_cache, qkv, q_gain, k_gain, inv_freq, positions, slots, H, KV, block_size, eps);
+  } else {
+    dim3 grid(num_tokens, (H + 2 * KV + kWarps - 1) / kWarps);
+    qk_norm_rope_store_vec_kernel<T, EPT, 1><<<grid, kWarps * 32, 0, stream>>>(
+        q_out, k_cache, v_cache, qkv, q_gain, k_gain, inv_freq, positions, slots, H, KV, block_size, eps);
+  }
 }
 
 }  // namespace

@@ -74,6 +74,8 @@ class ModelRunner:
         self.use_graphs = cuda_graphs and self.device.type == "cuda" and not cache.entry_state
         self._copy_done: torch.cuda.Event | None = None
         self._graphs: dict[tuple, tuple] = {}
+        # request uid -> (generation, per group a numpy copy of its block table, extended as it grows)
+        self._tables: dict[int, tuple[int, list[np.ndarray]]] = {}
         self._host: torch.Tensor | None = None
         self._dev: torch.Tensor | None = None
         self.num_launches_hint = 0
@@ -98,9 +100,25 @@ class ModelRunner:
             for g, table in zip(self.cache.groups, r.cache.block_tables):
                 if (r.start + n) > len(table) * bs:
                     raise ValueError(f"block table holds {len(table) * bs} slots, the row needs {r.start + n}")
-                first = self.cache.first_needed_block(g, r.start)
-                if any(b < 0 for b in table[first : -(-(r.start + n) // bs)]):
-                    raise ValueError("a page the row still reads has been released")
+                if g.window is not None:  # only windows release pages before a request ends
+                    first = self.cache.first_needed_block(g, r.start)
+                    if any(b < 0 for b in table[first : -(-(r.start + n) // bs)]):
+                        raise ValueError("a page the row still reads has been released")
+
+    def _table_array(self, rc: RequestCache, g: int) -> np.ndarray:
+        """The request's block table of group g as int32, kept between steps and extended by the
+        pages added since (entries a window released keep their old page id: never read)."""
+        entry = self._tables.get(rc.uid)
+        if entry is None or entry[0] != rc.generation:  # new, or freed and started again
+            if len(self._tables) > 4096:
+                self._tables.clear()
+            entry = self._tables[rc.uid] = (rc.generation, [np.zeros(0, dtype=np.int32) for _ in rc.block_tables])
+        cached = entry[1]
+        table, have = rc.block_tables[g], cached[g]
+        if len(table) > len(have):
+            have = np.concatenate([have, np.asarray(table[len(have) :], dtype=np.int32)])
+        cached[g] = have
+        return have
 
     def _layout(self, T: int, R: int, W: list[int], B: int) -> _Packed:
         lay = _Packed()
@@ -125,16 +143,23 @@ class ModelRunner:
         return self._host, self._dev
 
     def prepare(self, rows: list[Row], pad_requests: int | None = None, pad_width: int | None = None):
-        """Pack the rows; returns (ctx, per-group (slots, tables), layout key)."""
+        """Pack the rows; returns (ctx, per-group (slots, tables), layout key).
+
+        `pad_requests` (decode-only steps) appends dummy single-token requests up to that count:
+        token 0 at position 0, nothing stored (slot -1), an all-zero block table, and a wanted
+        row each, so that a few captured graph shapes serve every batch size. Their logits are
+        computed and dropped by the caller."""
         self.validate(rows)
         bs = self.block_size
-        R = len(rows)
-        T = sum(len(r.tokens) for r in rows)
+        real = len(rows)
+        pad = max(0, (pad_requests or 0) - real)
+        R = real + pad
+        T = sum(len(r.tokens) for r in rows) + pad
         widths = []
         for g in range(len(self.cache.groups)):
             w = max(-(-(r.start + len(r.tokens)) // bs) for r in rows)
             widths.append(pad_width if pad_width is not None else w)
-        B = sum(len(r.want) for r in rows)
+        B = sum(len(r.want) for r in rows) + pad
         lay = self._layout(T, R, widths, B)
         host, dev = self._buffers(lay.size)
         if self._copy_done is not None:
@@ -154,19 +179,29 @@ class ModelRunner:
                 b += 1
             flat += n
             max_context = max(max_context, r.start + n)
+        for i in range(real, R):  # padding requests
+            tok[flat], pos[flat], qs[i], ps[i], ss[i], lr[b] = 0, 0, flat, 0, 0, flat
+            flat += 1
+            b += 1
         qs[R] = flat
         for g, width in enumerate(widths):
             slots, tables = hv[f"slots{g}"].numpy(), hv[f"tables{g}"].numpy().reshape(R, width)
             flat = 0
             for i, r in enumerate(rows):
-                table = r.cache.block_tables[g]
+                table = self._table_array(r.cache, g)
                 n = len(r.tokens)
                 used = min(len(table), width)
                 tables[i, :used] = table[:used]
                 tables[i, used:] = 0
-                p = np.arange(r.start, r.start + n)
-                slots[flat : flat + n] = np.asarray(table, dtype=np.int64)[p // bs] * bs + p % bs
+                if n == 1:
+                    slots[flat] = int(table[r.start // bs]) * bs + r.start % bs
+                else:
+                    p = np.arange(r.start, r.start + n)
+                    slots[flat : flat + n] = table[p // bs].astype(np.int64) * bs + p % bs
                 flat += n
+            if pad:
+                tables[real:] = 0
+                slots[flat : flat + pad] = -1
         dev[: lay.size].copy_(host[: lay.size], non_blocking=True)
         if self.device.type == "cuda":
             self._copy_done = torch.cuda.Event()
@@ -176,8 +211,8 @@ class ModelRunner:
             num_tokens=T, num_requests=R, token_ids=dv["token_ids"], positions=dv["positions"],
             req_q_start=dv["req_q_start"], req_pos_start=dv["req_pos_start"],
             state_slots=dv["state_slots"], logits_rows=dv["logits_rows"], max_context=max_context,
-            host_q_lens=[len(r.tokens) for r in rows], host_pos_start=[r.start for r in rows],
-            host_state_slots=[r.cache.state_slot for r in rows],
+            host_q_lens=[len(r.tokens) for r in rows] + [1] * pad, host_pos_start=[r.start for r in rows] + [0] * pad,
+            host_state_slots=[r.cache.state_slot for r in rows] + [0] * pad,
         )  # fmt: skip
         groups = [(dv[f"slots{g}"], dv[f"tables{g}"].view(R, w)) for g, w in enumerate(widths)]
         return ctx, groups, (T, R, tuple(widths), B)
@@ -201,16 +236,25 @@ class ModelRunner:
         self._bind(groups)
         return self.model.forward(ctx, self.views)
 
+    GRAPH_BATCHES = (1, 2, 4, 8, 12, 16, 24, 32, 48, 64, 96, 128, 192, 256)
+
     def _step_graph(self, rows: list[Row]) -> torch.Tensor:
         """Decode-only step through a captured graph. The graph is keyed by everything that
-        fixes kernel shapes and buffer offsets: tokens, table width (rounded up to a bucket),
-        wanted rows, and the bucket of the longest context (which sets the key partitions)."""
+        fixes kernel shapes and buffer offsets: requests (rounded up to a bucket and padded with
+        dummy requests when every row wants its logits, as in generation), table width (rounded
+        up to a power of two), wanted rows, and the bucket of the longest context (which sets
+        the key partitions). The returned logits are a view of the graph's output buffer: read
+        them before the next step."""
         bs = self.block_size
         need_w = max(-(-(r.start + 1) // bs) for r in rows)
         pad_w = 16
         while pad_w < need_w:
             pad_w *= 2
-        ctx, groups, key = self.prepare(rows, pad_width=pad_w)
+        wanted = sum(len(r.want) for r in rows)
+        pad_r = None
+        if wanted == len(rows) and len(rows) <= self.GRAPH_BATCHES[-1]:
+            pad_r = next(b for b in self.GRAPH_BATCHES if b >= len(rows))
+        ctx, groups, key = self.prepare(rows, pad_requests=pad_r, pad_width=pad_w)
         ctx_bucket = 256
         while ctx_bucket < ctx.max_context:
             ctx_bucket *= 2
@@ -231,7 +275,7 @@ class ModelRunner:
         graph, out, launches = entry
         graph.replay()
         LAUNCHES[0] += launches  # the replay launched what the capture recorded
-        return out
+        return out[:wanted]
 
 
 def rows_for(seqs, num_new_tokens: list[int]) -> list[Row]:

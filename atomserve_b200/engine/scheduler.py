@@ -133,7 +133,7 @@ class Scheduler:
     def _finish_reason(self, seq: Sequence, token: int) -> str | None:
         if token in self.eos_token_ids and not seq.params.ignore_eos:
             return "stop"
-        if len(seq.output_ids) >= seq.params.max_tokens:
+        if seq.num_tokens - seq.num_prompt_tokens >= seq.params.max_tokens:
             return "length"
         if seq.num_tokens >= self.config.max_model_len:
             return "length"

@@ -50,7 +50,7 @@ class Sampler:
             [[s.params.temperature for s in seqs], [s.params.top_p for s in seqs]], dtype=torch.float32
         )
         top_k = torch.tensor([s.params.top_k for s in seqs], dtype=torch.int32)
-        keys = torch.tensor([[self.seed_of(s) for s in seqs], [len(s.output_ids) for s in seqs]], dtype=torch.int64)
+        keys = torch.tensor([[self.seed_of(s) for s in seqs], [s.num_tokens - s.num_prompt_tokens for s in seqs]], dtype=torch.int64)
         floats, top_k, keys = (t.to(self.device, non_blocking=True) for t in (floats, top_k, keys))
         out = ops.sample_rows(logits, floats[0], top_k, floats[1], keys[0], keys[1])
         assert out.shape[0] == n
