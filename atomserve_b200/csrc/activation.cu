@@ -8,6 +8,8 @@ namespace {
 template <typename T>
 __global__ void silu_mul_kernel(T* __restrict__ out, const T* __restrict__ gate_up, int inter,
                                 long long total) {
+  asb::pdl_wait();  // the stream's previous kernel has completed (programmatic dependent launch)
+  asb::pdl_launch_dependents();
   for (long long idx = blockIdx.x * (long long)blockDim.x + threadIdx.x; idx < total;
        idx += (long long)gridDim.x * blockDim.x) {
     const long long t = idx / inter;
@@ -21,6 +23,8 @@ __global__ void silu_mul_kernel(T* __restrict__ out, const T* __restrict__ gate_
 template <typename T, int VEC>
 __global__ void silu_mul_vec_kernel(T* __restrict__ out, const T* __restrict__ gate_up, int inter,
                                     long long total_vecs) {
+  asb::pdl_wait();  // the stream's previous kernel has completed (programmatic dependent launch)
+  asb::pdl_launch_dependents();
   const int vecs_per_row = inter / VEC;
   for (long long idx = blockIdx.x * (long long)blockDim.x + threadIdx.x; idx < total_vecs;
        idx += (long long)gridDim.x * blockDim.x) {
@@ -49,12 +53,12 @@ int launch(void* out, const void* gate_up, int num_tokens, int inter, cudaStream
   if (inter % VEC == 0 && aligned) {
     const long long total = (long long)num_tokens * (inter / VEC);
     const long long blocks = (total + threads - 1) / threads;
-    silu_mul_vec_kernel<T, VEC><<<(unsigned)(blocks < 148 * 32 ? blocks : 148 * 32), threads, 0, stream>>>(
+    asb::launch(silu_mul_vec_kernel<T, VEC>, (unsigned)(blocks < 148 * 32 ? blocks : 148 * 32), threads, 0, stream, 
         (T*)out, (const T*)gate_up, inter, total);
   } else {
     const long long total = (long long)num_tokens * inter;
     const long long blocks = (total + threads - 1) / threads;
-    silu_mul_kernel<T><<<(unsigned)(blocks < 148 * 32 ? blocks : 148 * 32), threads, 0, stream>>>(
+    asb::launch(silu_mul_kernel<T>, (unsigned)(blocks < 148 * 32 ? blocks : 148 * 32), threads, 0, stream, 
         (T*)out, (const T*)gate_up, inter, total);
   }
   return asb::check_launch("silu_mul");

@@ -261,6 +261,8 @@ __device__ __forceinline__ int find_request(const int* req_q_start, int R, int r
 template <int HD>
 __global__ void __launch_bounds__(kThreads)
 decode_attention_kernel(const MmaParams p) {
+  asb::pdl_wait();  // the stream's previous kernel has completed (programmatic dependent launch)
+  asb::pdl_launch_dependents();
   extern __shared__ __align__(128) unsigned char smem_raw[];
   constexpr int kTileBytes = kKeyTile * HD * 2;
   // [K stage 0][K stage 1][V stage 0][V stage 1][Q 16 rows]; the merge reuses the K/V stages
@@ -436,6 +438,8 @@ constexpr int kPrefillRows = 128;
 template <int HD>
 __global__ void __launch_bounds__(kPrefillThreads, 2)
 prefill_attention_kernel(const MmaParams p) {
+  asb::pdl_wait();  // the stream's previous kernel has completed (programmatic dependent launch)
+  asb::pdl_launch_dependents();
   extern __shared__ __align__(128) unsigned char smem_raw[];
   constexpr int kTileBytes = kKeyTile * HD * 2;
   const uint32_t smem = smem_u32(smem_raw);
@@ -632,7 +636,7 @@ int launch_mma(const MmaParams& p, int run_decode, int run_prefill, cudaStream_t
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) return asb::fail("decode_attention: %s", cudaGetErrorString(e));
     dim3 grid(p.T, p.KV * p.HC, p.NP);
-    kern<<<grid, kThreads, smem, stream>>>(p);
+    asb::launch(kern, grid, kThreads, smem, stream, p);
     if (int rc = asb::check_launch("decode_attention")) return rc;
   }
   if (run_prefill) {
@@ -641,7 +645,7 @@ int launch_mma(const MmaParams& p, int run_decode, int run_prefill, cudaStream_t
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) return asb::fail("prefill_attention: %s", cudaGetErrorString(e));
     dim3 grid((p.T + p.QT - 1) / p.QT + p.R, p.KV * p.HC, 1);
-    kern<<<grid, kPrefillThreads, smem, stream>>>(p);
+    asb::launch(kern, grid, kPrefillThreads, smem, stream, p);
     if (int rc = asb::check_launch("prefill_attention")) return rc;
   }
   return 0;

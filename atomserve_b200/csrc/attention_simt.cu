@@ -51,6 +51,8 @@ struct AttentionParams {
 template <typename T, int EPL>
 __global__ void __launch_bounds__(kWarps * 32)
 paged_attention_kernel(const AttentionParams p) {
+  asb::pdl_wait();  // the stream's previous kernel has completed (programmatic dependent launch)
+  asb::pdl_launch_dependents();
   extern __shared__ float smem[];
   const int hd = p.hd;
   const int kstride = hd | 1;  // odd stride: lanes reading one column of 32 keys hit 32 banks
@@ -200,6 +202,8 @@ template <typename T>
 __global__ void attention_reduce_kernel(T* __restrict__ out, const float* __restrict__ part_m,
                                         const float* __restrict__ part_l,
                                         const float* __restrict__ part_acc, int NP, int hd) {
+  asb::pdl_wait();  // the stream's previous kernel has completed (programmatic dependent launch)
+  asb::pdl_launch_dependents();
   const size_t row = blockIdx.x;
   const float* pm = part_m + row * NP;
   const float* pl = part_l + row * NP;
@@ -228,7 +232,7 @@ int launch(const AttentionParams& p, int num_tokens, cudaStream_t stream) {
     auto kern = paged_attention_kernel<T, E>;                                                   \
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
     if (e != cudaSuccess) return asb::fail("paged_attention: shared memory %zu: %s", smem, cudaGetErrorString(e)); \
-    kern<<<grid, kWarps * 32, smem, stream>>>(p);                                               \
+    asb::launch(kern, grid, kWarps * 32, smem, stream, p);                                               \
     break;                                                                                      \
   }
   switch (epl) {
@@ -248,7 +252,7 @@ int launch(const AttentionParams& p, int num_tokens, cudaStream_t stream) {
   if (p.NP > 1) {
     int threads = 32;
     while (threads < p.hd && threads < 256) threads <<= 1;
-    attention_reduce_kernel<T><<<num_tokens * p.H, threads, 0, stream>>>(
+    asb::launch(attention_reduce_kernel<T>, num_tokens * p.H, threads, 0, stream, 
         (T*)p.out, p.part_m, p.part_l, p.part_acc, p.NP, p.hd);
     return asb::check_launch("attention_reduce");
   }
@@ -265,7 +269,7 @@ extern "C" int asb_attention_reduce(void* out, const float* part_m, const float*
   int threads = 32;
   while (threads < hd && threads < 256) threads <<= 1;
   ASB_DISPATCH_DTYPE(dtype, T,
-                     attention_reduce_kernel<T><<<rows, threads, 0, stream>>>(
+                     asb::launch(attention_reduce_kernel<T>, rows, threads, 0, stream, 
                          (T*)out, part_m, part_l, part_acc, NP, hd));
   return asb::check_launch("attention_reduce");
 }

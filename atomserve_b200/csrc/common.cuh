@@ -12,6 +12,7 @@
 
 #include <cstdarg>
 #include <cstdio>
+#include <utility>
 
 namespace asb {
 
@@ -20,6 +21,34 @@ enum DType : int { kFloat32 = 0, kBFloat16 = 1 };
 char* error_buffer();
 int fail(const char* fmt, ...);
 int check_launch(const char* what);
+
+// Programmatic dependent launch. Every kernel of this library begins with pdl_wait(): when the
+// launch carries the programmatic-serialization attribute, the grid may be scheduled while its
+// predecessor in the stream is still running, and pdl_wait() is where it stops until that
+// predecessor has completed and its writes are visible; what a kernel does before pdl_wait()
+// (barrier set-up, tensor-memory allocation, loads of weights, which no kernel writes) overlaps the
+// predecessor's tail. Without the attribute the instruction does nothing. pdl_enabled() is the
+// library-wide switch (asb_set_pdl).
+bool pdl_enabled();
+
+template <typename... KArgs, typename... Args>
+inline void launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                   Args&&... args) {
+  cudaLaunchConfig_t config = {};
+  config.gridDim = grid;
+  config.blockDim = block;
+  config.dynamicSmemBytes = smem;
+  config.stream = stream;
+  cudaLaunchAttribute attribute[1];
+  attribute[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attribute[0].val.programmaticStreamSerializationAllowed = 1;
+  config.attrs = attribute;
+  config.numAttrs = pdl_enabled() ? 1 : 0;
+  cudaLaunchKernelEx(&config, kernel, std::forward<Args>(args)...);
+}
+
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
 template <typename T>
 __device__ __forceinline__ float to_float(T v);

@@ -7,6 +7,8 @@ template <typename T>
 __global__ void embedding_kernel(T* __restrict__ out, const T* __restrict__ table,
                                  const int* __restrict__ ids, int width, int vocab,
                                  int* __restrict__ status) {
+  asb::pdl_wait();  // the stream's previous kernel has completed (programmatic dependent launch)
+  asb::pdl_launch_dependents();
   const int t = blockIdx.x;
   const int id = ids[t];
   if (id < 0 || id >= vocab) {  // refuse rather than read outside the table
@@ -34,7 +36,7 @@ extern "C" int asb_embedding(void* out, const void* table, const int* ids, int n
   if (num_tokens == 0) return 0;
   const int threads = width >= 2048 ? 256 : 128;
   ASB_DISPATCH_DTYPE(dtype, T,
-                     embedding_kernel<T><<<num_tokens, threads, 0, stream>>>(
+                     asb::launch(embedding_kernel<T>, num_tokens, threads, 0, stream, 
                          (T*)out, (const T*)table, ids, width, vocab, status));
   return asb::check_launch("embedding");
 }

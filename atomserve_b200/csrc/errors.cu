@@ -22,7 +22,16 @@ int check_launch(const char* what) {
   return 0;
 }
 
+static bool g_pdl = false;
+bool pdl_enabled() { return g_pdl; }
+void set_pdl(bool on) { g_pdl = on; }
+
 }  // namespace asb
+
+namespace asb { void set_pdl(bool on); }
+
+// Switch programmatic dependent launch on or off for every later launch of this library.
+extern "C" void asb_set_pdl(int on) { asb::set_pdl(on != 0); }
 
 extern "C" const char* asb_last_error() { return asb::error_buffer(); }
 

@@ -18,6 +18,8 @@ template <typename TIn, typename TOut>
 __global__ void __launch_bounds__(256)
 gemm_simt_kernel(TOut* __restrict__ out, const TIn* __restrict__ x, const TIn* __restrict__ w,
                  const TOut* __restrict__ residual, int M, int N, int K) {
+  asb::pdl_wait();  // the stream's previous kernel has completed (programmatic dependent launch)
+  asb::pdl_launch_dependents();
   __shared__ float xs[BK][BM + 4];
   __shared__ float ws[BK][BN + 4];
   const int tid = threadIdx.x;
@@ -82,14 +84,14 @@ extern "C" int asb_gemm_simt(void* out, const void* x, const void* w, const void
   dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM);
   if (grid.y > 65535) return asb::fail("gemm_simt: M = %d exceeds the grid", M);
   if (in_dtype == asb::kFloat32 && out_dtype == asb::kFloat32) {
-    gemm_simt_kernel<float, float><<<grid, 256, 0, stream>>>(
+    asb::launch(gemm_simt_kernel<float, float>, grid, 256, 0, stream, 
         (float*)out, (const float*)x, (const float*)w, (const float*)residual, M, N, K);
   } else if (in_dtype == asb::kBFloat16 && out_dtype == asb::kBFloat16) {
-    gemm_simt_kernel<__nv_bfloat16, __nv_bfloat16><<<grid, 256, 0, stream>>>(
+    asb::launch(gemm_simt_kernel<__nv_bfloat16, __nv_bfloat16>, grid, 256, 0, stream, 
         (__nv_bfloat16*)out, (const __nv_bfloat16*)x, (const __nv_bfloat16*)w,
         (const __nv_bfloat16*)residual, M, N, K);
   } else if (in_dtype == asb::kBFloat16 && out_dtype == asb::kFloat32) {
-    gemm_simt_kernel<__nv_bfloat16, float><<<grid, 256, 0, stream>>>(
+    asb::launch(gemm_simt_kernel<__nv_bfloat16, float>, grid, 256, 0, stream, 
         (float*)out, (const __nv_bfloat16*)x, (const __nv_bfloat16*)w, (const float*)residual, M,
         N, K);
   } else {

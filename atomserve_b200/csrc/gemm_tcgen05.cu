@@ -222,9 +222,29 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_cons
   __syncthreads();
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
   const uint32_t tmem_base = *tmem_slot;
+  // Everything above touched only this block's shared and tensor memory: with a programmatic
+  // dependent launch it ran while the stream's previous kernel was finishing. Each role calls
+  // pdl_wait() before it first reads that kernel's output; the TMA warp first fills the pipeline
+  // with the weight operand, which no kernel writes.
 
   if (warp == 0) {
     if (lane == 0) {
+      // The weights are operand P when swapped, Q otherwise. Before waiting for the previous
+      // kernel, fill the first kStages stages with the weight half; the activation half follows.
+      {
+        SegmentWalk ahead(p);
+        uint32_t it = 0;
+        while (it < (uint32_t)C::kStages && ahead.next()) {
+          const int p0 = (ahead.tile % p.tiles_p) * BM, q0 = (ahead.tile / p.tiles_p) * BN;
+          for (int kb = ahead.kb0; kb < ahead.kb1 && it < (uint32_t)C::kStages; ++kb, ++it) {
+            mbar_expect_tx(full_bar(it), C::kStage);
+            if (p.swap) tma_load_2d(base + it * C::kStage, &map_p, full_bar(it), kb * BK, p0);
+            else tma_load_2d(base + it * C::kStage + C::kTileP, &map_q, full_bar(it), kb * BK, q0);
+          }
+        }
+      }
+      asb::pdl_wait();
+      asb::pdl_launch_dependents();
       SegmentWalk walk(p);
       uint32_t it = 0;  // K blocks loaded so far by this block, across segments
       bool ok = true;
@@ -232,6 +252,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_cons
         const int p0 = (walk.tile % p.tiles_p) * BM, q0 = (walk.tile / p.tiles_p) * BN;
         for (int kb = walk.kb0; kb < walk.kb1; ++kb, ++it) {
           const int s = it % C::kStages;
+          if (it < (uint32_t)C::kStages) {  // the weight half is already on its way
+            if (p.swap) tma_load_2d(base + s * C::kStage + C::kTileP, &map_q, full_bar(s), kb * BK, q0);
+            else tma_load_2d(base + s * C::kStage, &map_p, full_bar(s), kb * BK, p0);
+            continue;
+          }
           const uint32_t phase = (it / C::kStages) & 1u;
           ok = mbar_wait(empty_bar(s), phase ^ 1u, p.status, 1);
           if (!ok) break;
@@ -242,6 +267,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_cons
       }
     }
   } else if (warp == 1) {
+    asb::pdl_wait();
     if (lane == 0) {
       constexpr uint32_t idesc = instr_desc(BM, BN);
       SegmentWalk walk(p);
@@ -274,6 +300,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_cons
     }
   } else {
     // Epilogue: this warp owns TMEM lanes 32*(warp%4)..+31, one lane (P row) per thread.
+    asb::pdl_wait();  // it reads the residual and writes where earlier kernels may still be reading
     const int quad = warp & 3;
     SegmentWalk walk(p);
     uint32_t seg = 0;
@@ -400,6 +427,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_cons
 // consecutive elements along the output's contiguous dimension. Tiles stored whole are skipped.
 template <int BN>
 __global__ void segment_reduce_kernel(const GemmParams p, int parts) {
+  asb::pdl_wait();  // the stream's previous kernel has completed (programmatic dependent launch)
+  asb::pdl_launch_dependents();
   const int tile = blockIdx.x;
   const long long total = (long long)p.num_tiles * p.kb_per_tile;
   const long long begin = (long long)tile * p.kb_per_tile;
@@ -522,10 +551,10 @@ int launch(const CUtensorMap& mp, const CUtensorMap& mq, const GemmParams& p, co
   auto kern = gemm_tcgen05_kernel<BN>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Config<BN>::kSmem);
   if (e != cudaSuccess) return asb::fail("gemm_tcgen05: shared memory %d: %s", Config<BN>::kSmem, cudaGetErrorString(e));
-  kern<<<pl.blocks, kThreads, Config<BN>::kSmem, stream>>>(mp, mq, p);
+  asb::launch(kern, pl.blocks, kThreads, Config<BN>::kSmem, stream, mp, mq, p);
   if (int rc = asb::check_launch("gemm_tcgen05")) return rc;
   if (pl.stream) {
-    segment_reduce_kernel<BN><<<dim3(p.num_tiles, (BM * BN / 4 + 255) / 256), 256, 0, stream>>>(p, pl.blocks);
+    asb::launch(segment_reduce_kernel<BN>, dim3(p.num_tiles, (BM * BN / 4 + 255) / 256), 256, 0, stream, p, pl.blocks);
     return asb::check_launch("gemm_tcgen05 segment_reduce");
   }
   return 0;

@@ -13,6 +13,8 @@ template <typename T>
 __global__ void rmsnorm_kernel(T* __restrict__ out, const T* __restrict__ x,
                                const float* __restrict__ gain, const int* __restrict__ rows,
                                int width, float eps) {
+  asb::pdl_wait();  // the stream's previous kernel has completed (programmatic dependent launch)
+  asb::pdl_launch_dependents();
   __shared__ float scratch[32];
   const int r = blockIdx.x;
   const T* src = x + (size_t)(rows ? rows[r] : r) * width;
@@ -34,6 +36,8 @@ template <typename T, int VEC>
 __global__ void rmsnorm_vec_kernel(T* __restrict__ out, const T* __restrict__ x,
                                    const float* __restrict__ gain, const int* __restrict__ rows,
                                    int width, float eps) {
+  asb::pdl_wait();  // the stream's previous kernel has completed (programmatic dependent launch)
+  asb::pdl_launch_dependents();
   __shared__ float scratch[32];
   const int r = blockIdx.x;
   const T* src = x + (size_t)(rows ? rows[r] : r) * width;
@@ -74,11 +78,11 @@ int launch(void* out, const void* x, const float* gain, const int* rows, int num
   const bool aligned = ((uintptr_t)out % 16 == 0) && ((uintptr_t)x % 16 == 0) && ((uintptr_t)gain % 16 == 0);
   if (width % VEC == 0 && width / VEC <= 1024 && aligned) {
     const int threads = ((width / VEC) + 31) / 32 * 32;
-    rmsnorm_vec_kernel<T, VEC><<<num_rows, threads, 0, stream>>>((T*)out, (const T*)x, gain, rows, width, eps);
+    asb::launch(rmsnorm_vec_kernel<T, VEC>, num_rows, threads, 0, stream, (T*)out, (const T*)x, gain, rows, width, eps);
   } else {
     int threads = 32;
     while (threads < 1024 && threads * 4 < width) threads <<= 1;
-    rmsnorm_kernel<T><<<num_rows, threads, 0, stream>>>((T*)out, (const T*)x, gain, rows, width, eps);
+    asb::launch(rmsnorm_kernel<T>, num_rows, threads, 0, stream, (T*)out, (const T*)x, gain, rows, width, eps);
   }
   return asb::check_launch("rmsnorm");
 }

@@ -26,6 +26,8 @@ __global__ void qk_norm_rope_store_kernel(
     const float* __restrict__ inv_freq, const int* __restrict__ positions,
     const int* __restrict__ slots, int H, int KV, int hd, int rotary_dim, int block_size,
     float eps) {
+  asb::pdl_wait();  // the stream's previous kernel has completed (programmatic dependent launch)
+  asb::pdl_launch_dependents();
   __shared__ float stage[kWarps][kMaxHeadDim];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int head = blockIdx.y * kWarps + warp;
@@ -89,6 +91,8 @@ __global__ void qk_norm_rope_store_vec_kernel(
     const T* __restrict__ qkv, const float* __restrict__ q_gain, const float* __restrict__ k_gain,
     const float* __restrict__ inv_freq, const int* __restrict__ positions,
     const int* __restrict__ slots, int H, int KV, int block_size, float eps) {
+  asb::pdl_wait();  // the stream's previous kernel has completed (programmatic dependent launch)
+  asb::pdl_launch_dependents();
   constexpr int hd = EPT * 32;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int t = blockIdx.x;
@@ -159,11 +163,11 @@ void launch_vec(T* q_out, T* k_cache, T* v_cache, const T* qkv, const float* q_g
   if (num_tokens >= 256) {
     const int heads_per_block = kWarps * 4;
     dim3 grid(num_tokens, (H + 2 * KV + heads_per_block - 1) / heads_per_block);
-    qk_norm_rope_store_vec_kernel<T, EPT, 4><<<grid, kWarps * 32, 0, stream>>>(
+    asb::launch(qk_norm_rope_store_vec_kernel<T, EPT, 4>, grid, kWarps * 32, 0, stream, 
         q_out, k_cache, v_cache, qkv, q_gain, k_gain, inv_freq, positions, slots, H, KV, block_size, eps);
   } else {
     dim3 grid(num_tokens, (H + 2 * KV + kWarps - 1) / kWarps);
-    qk_norm_rope_store_vec_kernel<T, EPT, 1><<<grid, kWarps * 32, 0, stream>>>(
+    asb::launch(qk_norm_rope_store_vec_kernel<T, EPT, 1>, grid, kWarps * 32, 0, stream, 
         q_out, k_cache, v_cache, qkv, q_gain, k_gain, inv_freq, positions, slots, H, KV, block_size, eps);
   }
 }
@@ -199,7 +203,7 @@ extern "C" int asb_qk_norm_rope_store(void* q_out, void* k_cache, void* v_cache,
   }
   dim3 grid(num_tokens, (H + 2 * KV + kWarps - 1) / kWarps);
   ASB_DISPATCH_DTYPE(dtype, T,
-                     qk_norm_rope_store_kernel<T><<<grid, kWarps * 32, 0, stream>>>(
+                     asb::launch(qk_norm_rope_store_kernel<T>, grid, kWarps * 32, 0, stream, 
                          (T*)q_out, (T*)k_cache, (T*)v_cache, (const T*)qkv, q_gain, k_gain,
                          inv_freq, positions, slots, H, KV, hd, rotary_dim, block_size, eps));
   return asb::check_launch("qk_norm_rope_store");

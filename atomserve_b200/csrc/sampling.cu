@@ -230,6 +230,8 @@ sample_rows_kernel(int* __restrict__ out, const float* __restrict__ logits, int 
                    const float* __restrict__ temperature, const int* __restrict__ top_k,
                    const float* __restrict__ top_p, const unsigned long long* __restrict__ seed,
                    const unsigned long long* __restrict__ counter) {
+  asb::pdl_wait();  // the stream's previous kernel has completed (programmatic dependent launch)
+  asb::pdl_launch_dependents();
   __shared__ Scratch s;
   const int b = blockIdx.x;
   RowView row{logits + (size_t)b * V, nullptr, V};
@@ -355,6 +357,8 @@ sample_rows_kernel(int* __restrict__ out, const float* __restrict__ logits, int 
 }
 
 __global__ void argmax_rows_kernel(int* __restrict__ out, const float* __restrict__ logits, int V) {
+  asb::pdl_wait();  // the stream's previous kernel has completed (programmatic dependent launch)
+  asb::pdl_launch_dependents();
   __shared__ Scratch s;
   RowView row{logits + (size_t)blockIdx.x * V, nullptr, V};
   const int best = row_argmax(row, s, nullptr);
@@ -364,6 +368,8 @@ __global__ void argmax_rows_kernel(int* __restrict__ out, const float* __restric
 __global__ void presence_penalty_kernel(float* __restrict__ logits, const int* __restrict__ rows,
                                         const int* __restrict__ tokens,
                                         const float* __restrict__ amounts, int n, int V) {
+  asb::pdl_wait();  // the stream's previous kernel has completed (programmatic dependent launch)
+  asb::pdl_launch_dependents();
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
   if (i < n && tokens[i] >= 0 && tokens[i] < V) logits[(size_t)rows[i] * V + tokens[i]] -= amounts[i];
 }
@@ -372,7 +378,7 @@ __global__ void presence_penalty_kernel(float* __restrict__ logits, const int* _
 
 extern "C" int asb_argmax_rows(int* out, const float* logits, int B, int V, cudaStream_t stream) {
   if (B == 0) return 0;
-  argmax_rows_kernel<<<B, kThreads, 0, stream>>>(out, logits, V);
+  asb::launch(argmax_rows_kernel, B, kThreads, 0, stream, out, logits, V);
   return asb::check_launch("argmax_rows");
 }
 
@@ -380,7 +386,7 @@ extern "C" int asb_argmax_rows(int* out, const float* logits, int B, int V, cuda
 extern "C" int asb_presence_penalty(float* logits, const int* rows, const int* tokens,
                                     const float* amounts, int n, int V, cudaStream_t stream) {
   if (n == 0) return 0;
-  presence_penalty_kernel<<<(n + 255) / 256, 256, 0, stream>>>(logits, rows, tokens, amounts, n, V);
+  asb::launch(presence_penalty_kernel, (n + 255) / 256, 256, 0, stream, logits, rows, tokens, amounts, n, V);
   return asb::check_launch("presence_penalty");
 }
 
@@ -390,6 +396,6 @@ extern "C" int asb_sample_rows(int* out, const float* logits, int B, int V,
                                cudaStream_t stream) {
   if (B == 0) return 0;
   if (V < 1) return asb::fail("sample_rows: vocabulary %d", V);
-  sample_rows_kernel<<<B, kThreads, 0, stream>>>(out, logits, V, temperature, top_k, top_p, seed, counter);
+  asb::launch(sample_rows_kernel, B, kThreads, 0, stream, out, logits, V, temperature, top_k, top_p, seed, counter);
   return asb::check_launch("sample_rows");
 }

@@ -8,6 +8,7 @@ it was compiled for, the first operation raises `KernelLibraryError`.
 from __future__ import annotations
 
 import ctypes
+import os
 import threading
 from ctypes import c_float, c_int, c_void_p
 
@@ -60,6 +61,10 @@ def lib() -> ctypes.CDLL:
                 f"the CUDA kernel library could not be built or loaded: {error}"
             ) from error
         handle.asb_last_error.restype = ctypes.c_char_p
+        handle.asb_set_pdl.argtypes = [c_int]
+        handle.asb_set_pdl.restype = None
+        # programmatic dependent launch: kernels are scheduled while their predecessor drains
+        handle.asb_set_pdl(int(os.environ.get("ATOMSERVE_B200_PDL", "1") != "0"))
         handle.asb_attention_tile_shape.argtypes = [c_int, c_void_p, c_void_p]
         handle.asb_attention_tile_shape.restype = None
         for name, argtypes in _SIGNATURES.items():
