@@ -1,0 +1,372 @@
+// Paged grouped-query attention for prompt portions on the fifth-generation tensor cores:
+// bfloat16, head size 128, both products (Q K^T and P V) issued as tcgen05.mma with the scores
+// and the output accumulator in tensor memory, operands brought in by TMA straight from the
+// cache pages. It serves the same requests as the mma.sync prefill kernel of attention_mma.cu
+// (portions of more than 8 tokens) where its shape rules hold; the math is the same: causal and
+// window masks from absolute positions, softmax in float32, one rounding of the output
+// (atomserve/model.py:199-232).
+//
+// One block per (request, tile of QT query tokens, kv head). Its 128 rows are the (token, head)
+// pairs of the tile, QT = 128 / G tokens times the G query heads of the kv head, loaded as one
+// 3-D TMA box of q [T, H, hd]. Keys are visited in tiles of 128 at absolute multiples of 128.
+//
+//   warp 0     TMA: the Q tile once, then per key tile the pages of K and of V named by the
+//              block table, each page as two boxes (the two 64-element halves of the head).
+//   warp 1     MMA: S[b] = Q K^T into score buffer b = tile & 1 (two buffers, so the next tile's
+//              scores are computed while this tile's softmax runs), then O += P V once the
+//              softmax has written P. V is consumed as an MN-major operand: its rows in shared
+//              memory are keys, exactly as the pages hold them.
+//   warps 2-5  softmax: thread r owns row r (a TMEM lane), so row maxima and sums need no
+//              shuffles. It reads its scores twice (maximum, then exponentials), rescales its
+//              row of O in tensor memory when the maximum moved, writes P as bfloat16 into shared
+//              memory in the swizzled K-major layout, and at the end stores O / sum.
+//
+// Shared memory: Q 32 KB, two stages of (K 32 KB + V 32 KB), P 32 KB. Tensor memory: two score
+// buffers and the output accumulator, 128 columns each. All barrier waits are bounded; a wait
+// that runs out sets *status and the roles wind down to the final barrier.
+#include "tcgen05.cuh"
+
+namespace {
+
+using namespace asb::t5;
+
+constexpr int kThreads = 192;
+constexpr int HD = 128;
+constexpr int kRows = 128;
+constexpr int kKeys = 128;
+constexpr int kBlockBytes = 128 * 64 * 2;       // one [128 rows][64 elements] swizzled block: 16 KB
+constexpr int kTileBytes = 2 * kBlockBytes;     // 32 KB: the two halves of the head (or of the keys, for P)
+constexpr int kStageBytes = 2 * kTileBytes;     // K and V
+constexpr int kStages = 2;
+constexpr int kSmem = kTileBytes /*Q*/ + kStages * kStageBytes + kTileBytes /*P*/ + 1024 + 256;
+constexpr uint32_t kTmemCols = 512;
+constexpr int kShortRows = 8;
+
+struct AttnParams {
+  __nv_bfloat16* out;        // [T, H, HD]
+  const int* block_tables;   // [R, table_width]
+  const int* req_q_start;    // [R + 1]
+  const int* req_pos_start;  // [R]
+  int* status;
+  int T, R, H, KV, bs, table_width;
+  int G, QT;                 // query heads per kv head, tokens per tile (128 / G)
+  int window;
+  float scale_log2;          // softmax scale times log2(e)
+};
+
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+__global__ void __launch_bounds__(kThreads, 1)
+prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                                 const __grid_constant__ CUtensorMap map_v, const AttnParams p) {
+  extern __shared__ unsigned char smem_raw[];
+  const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  unsigned char* aligned = smem_raw + (base - smem_u32(smem_raw));
+  const uint32_t q_smem = base;
+  auto k_smem = [&](int s) { return base + kTileBytes + (uint32_t)s * kStageBytes; };
+  auto v_smem = [&](int s) { return base + kTileBytes + (uint32_t)s * kStageBytes + kTileBytes; };
+  const uint32_t p_smem = base + kTileBytes + kStages * kStageBytes;
+  unsigned char* p_ptr = aligned + kTileBytes + kStages * kStageBytes;
+  const uint32_t bars = p_smem + kTileBytes;
+  const uint32_t q_full = bars;
+  auto kv_full = [&](int s) { return bars + 8u * (1 + s); };
+  auto kv_empty = [&](int s) { return bars + 8u * (3 + s); };
+  auto s_full = [&](int b) { return bars + 8u * (5 + b); };
+  const uint32_t p_full = bars + 8u * 7;
+  const uint32_t pv_done = bars + 8u * 8;
+  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(aligned + 2 * kTileBytes + kStages * kStageBytes + 8 * 9);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  // Which request and tile of its tokens? Only requests with more than kShortRows tokens count.
+  int tile = blockIdx.x, r = 0, q_len = 0;
+  for (; r < p.R; ++r) {
+    q_len = p.req_q_start[r + 1] - p.req_q_start[r];
+    if (q_len <= kShortRows) continue;
+    const int tiles = (q_len + p.QT - 1) / p.QT;
+    if (tile < tiles) {
+      tile = tiles - 1 - tile;  // late tiles see the most keys: start them first
+      break;
+    }
+    tile -= tiles;
+  }
+  if (r >= p.R) return;  // the whole block leaves before any barrier or allocation
+  const int q0 = tile * p.QT;
+  const int nq = min(p.QT, q_len - q0);
+  const int row0 = p.req_q_start[r] + q0;
+  const int pos0 = p.req_pos_start[r] + q0;
+  const int kvh = blockIdx.y;
+  const int head0 = kvh * p.G;
+  const int* table = p.block_tables + (size_t)r * p.table_width;
+  const int key_lo = p.window > 0 ? max(0, pos0 - p.window + 1) : 0;
+  const int key_hi = pos0 + nq;  // exclusive
+  const int kt_begin = (key_lo / kKeys) * kKeys;
+  const int num_tiles = (key_hi - kt_begin + kKeys - 1) / kKeys;
+
+  if (threadIdx.x == 0) {
+    mbar_init(q_full, 1);
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(kv_full(s), 1);
+      mbar_init(kv_empty(s), 1);
+      mbar_init(s_full(s), 1);
+    }
+    mbar_init(p_full, 4);  // one arrival per softmax warp
+    mbar_init(pv_done, 1);
+    mbar_init_fence();
+  }
+  if (warp == 1) tmem_alloc(smem_u32((const void*)tmem_slot), kTmemCols);
+  fence_before_sync();
+  __syncthreads();
+  fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+  auto tmem_s = [&](int j) { return tmem_base + (uint32_t)(j & 1) * 128u; };  // two score buffers
+  const uint32_t tmem_o = tmem_base + 256;
+  asb::pdl_wait();
+  asb::pdl_launch_dependents();
+
+  if (warp == 0) {
+    if (lane == 0) {
+      mbar_expect_tx(q_full, kTileBytes);
+      tma_load_3d(q_smem, &map_q, q_full, 0, head0, row0);
+      tma_load_3d(q_smem + kBlockBytes, &map_q, q_full, 64, head0, row0);
+      const int pages_per_tile = kKeys / p.bs;
+      const int last_page = (key_hi - 1) / p.bs;  // the last page this request certainly holds
+      bool ok = true;
+      for (int j = 0; j < num_tiles && ok; ++j) {
+        const int s = j & 1;
+        ok = mbar_wait(kv_empty(s), (((uint32_t)j >> 1) & 1u) ^ 1u, p.status, 11);
+        if (!ok) break;
+        mbar_expect_tx(kv_full(s), kStageBytes);
+        const int first_page = (kt_begin + j * kKeys) / p.bs;
+        for (int i = 0; i < pages_per_tile; ++i) {
+          // pages beyond the request's end, or released by the window, are masked out anyway:
+          // read a page the request holds, so that shared memory never holds non-finite values
+          int page = min(first_page + i, last_page);
+          int blk = table[page];
+          if (blk < 0) blk = table[last_page];
+          const int y = (blk * p.KV + kvh) * p.bs;
+          const uint32_t off = (uint32_t)(i * p.bs) * 128u;
+          tma_load_2d(k_smem(s) + off, &map_k, kv_full(s), 0, y);
+          tma_load_2d(k_smem(s) + kBlockBytes + off, &map_k, kv_full(s), 64, y);
+          tma_load_2d(v_smem(s) + off, &map_v, kv_full(s), 0, y);
+          tma_load_2d(v_smem(s) + kBlockBytes + off, &map_v, kv_full(s), 64, y);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      constexpr uint32_t idesc_qk = instr_desc_bf16(kRows, kKeys, false);
+      constexpr uint32_t idesc_pv = instr_desc_bf16(kRows, HD, true);
+      auto issue_qk = [&](int j) {
+        const int s = j & 1;
+#pragma unroll
+        for (int ks = 0; ks < HD / 16; ++ks) {  // 16 head elements per MMA: 32 bytes along the swizzled row
+          const uint32_t off = (uint32_t)(ks / 4) * kBlockBytes + (uint32_t)(ks % 4) * 32u;
+          umma_bf16(tmem_s(j), desc_k_major(q_smem + off, 1024), desc_k_major(k_smem(s) + off, 1024), idesc_qk,
+                    (uint32_t)(ks != 0));
+        }
+        umma_commit(s_full(j & 1));
+      };
+      bool ok = mbar_wait(q_full, 0, p.status, 12);
+      if (ok) ok = mbar_wait(kv_full(0), 0, p.status, 13);
+      if (ok) {
+        fence_after_sync();
+        issue_qk(0);
+      }
+      for (int j = 0; j < num_tiles && ok; ++j) {
+        if (j + 1 < num_tiles) {
+          ok = mbar_wait(kv_full((j + 1) & 1), ((uint32_t)(j + 1) >> 1) & 1u, p.status, 14);
+          if (!ok) break;
+          fence_after_sync();
+          issue_qk(j + 1);
+        }
+        ok = mbar_wait(p_full, (uint32_t)j & 1u, p.status, 15);
+        if (!ok) break;
+        fence_after_sync();
+        const int s = j & 1;
+#pragma unroll
+        for (int ks = 0; ks < kKeys / 16; ++ks) {  // 16 keys per MMA
+          const uint64_t a = desc_k_major(p_smem + (uint32_t)(ks / 4) * kBlockBytes + (uint32_t)(ks % 4) * 32u, 1024);
+          // V: rows are keys (128 bytes each), 8-key groups 1024 bytes apart, head halves 16 KB apart
+          const uint64_t b = desc_mn_major(v_smem(s) + (uint32_t)ks * 2048u, kBlockBytes, 1024);
+          umma_bf16(tmem_o, a, b, idesc_pv, (uint32_t)((j | ks) != 0));
+        }
+        umma_commit(pv_done);
+        umma_commit(kv_empty(s));
+      }
+    }
+  } else {
+    // Softmax and epilogue: thread `row` of the block owns TMEM lane `row`.
+    const int quad = warp & 3;
+    const int row = quad * 32 + lane;
+    const int qi = row / p.G;
+    const bool real = qi < nq;
+    const int pos = real ? pos0 + qi : -1;  // padding rows see nothing
+    const int row_lo = p.window > 0 ? max(key_lo, pos - p.window + 1) : key_lo;
+    const uint32_t lane_addr = (uint32_t)(quad * 32) << 16;
+    float m = -INFINITY, l = 0.f;
+    bool ok = true;
+    for (int j = 0; j < num_tiles && ok; ++j) {
+      const int kt0 = kt_begin + j * kKeys;
+      int ok_i = 1;
+      if (lane == 0) ok_i = mbar_wait(s_full(j & 1), ((uint32_t)j >> 1) & 1u, p.status, 16) ? 1 : 0;
+      ok = __shfl_sync(0xffffffffu, ok_i, 0) != 0;
+      if (!ok) break;
+      fence_after_sync();
+      // pass 1: the row's maximum over this tile
+      float tile_max = -INFINITY;
+#pragma unroll 1
+      for (int c = 0; c < kKeys; c += 32) {
+        uint32_t raw[32];
+        tmem_ld32(tmem_s(j) + lane_addr + (uint32_t)c, raw);
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          const int key = kt0 + c + i;
+          const float sc = (key <= pos && key >= row_lo) ? __uint_as_float(raw[i]) * p.scale_log2 : -INFINITY;
+          tile_max = fmaxf(tile_max, sc);
+        }
+      }
+      const float m_new = fmaxf(m, tile_max);
+      const float m_use = m_new == -INFINITY ? 0.f : m_new;  // a row that has seen nothing yet
+      const float corr = fast_exp2(m - m_use);
+      m = m_new;
+      l *= corr;
+      if (j > 0) {
+        // the previous P V must have completed before O is rescaled and P overwritten
+        if (lane == 0) ok_i = mbar_wait(pv_done, (uint32_t)(j - 1) & 1u, p.status, 17) ? 1 : 0;
+        ok = __shfl_sync(0xffffffffu, ok_i, 0) != 0;
+        if (!ok) break;
+        fence_after_sync();
+        if (__any_sync(0xffffffffu, corr != 1.f)) {
+#pragma unroll 1
+          for (int c = 0; c < HD; c += 32) {
+            uint32_t raw[32];
+            tmem_ld32(tmem_o + lane_addr + (uint32_t)c, raw);
+#pragma unroll
+            for (int i = 0; i < 32; ++i) raw[i] = __float_as_uint(__uint_as_float(raw[i]) * corr);
+            tmem_st32(tmem_o + lane_addr + (uint32_t)c, raw);
+          }
+          tmem_st_wait();
+        }
+      }
+      // pass 2: probabilities, their sum, and P as bfloat16 in the swizzled K-major layout
+#pragma unroll 1
+      for (int c = 0; c < kKeys; c += 32) {
+        uint32_t raw[32];
+        tmem_ld32(tmem_s(j) + lane_addr + (uint32_t)c, raw);
+        uint32_t packed[16];
+#pragma unroll
+        for (int i = 0; i < 32; i += 2) {
+          const int key = kt0 + c + i;
+          const float a = (key <= pos && key >= row_lo) ? fast_exp2(__uint_as_float(raw[i]) * p.scale_log2 - m_use) : 0.f;
+          const float b = (key + 1 <= pos && key + 1 >= row_lo) ? fast_exp2(__uint_as_float(raw[i + 1]) * p.scale_log2 - m_use) : 0.f;
+          l += a + b;
+          __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
+          packed[i >> 1] = *reinterpret_cast<uint32_t*>(&v);
+        }
+        // keys c..c+31 of this row: four 16-byte chunks of block c / 64
+        unsigned char* dst = p_ptr + (c / 64) * kBlockBytes + row * 128;
+#pragma unroll
+        for (int q4 = 0; q4 < 4; ++q4) {
+          const int chunk = ((c % 64) / 8 + q4) ^ (row & 7);
+          *reinterpret_cast<uint4*>(dst + chunk * 16) = make_uint4(packed[q4 * 4], packed[q4 * 4 + 1], packed[q4 * 4 + 2], packed[q4 * 4 + 3]);
+        }
+      }
+      fence_async_smem();   // P is read by the tensor cores
+      fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(p_full);
+    }
+    // epilogue: O / sum, rounded once
+    if (ok) {
+      int ok_i = 1;
+      if (lane == 0) ok_i = mbar_wait(pv_done, (uint32_t)(num_tiles - 1) & 1u, p.status, 18) ? 1 : 0;
+      ok = __shfl_sync(0xffffffffu, ok_i, 0) != 0;
+    }
+    if (ok) {
+      fence_after_sync();
+      const float inv = real ? 1.f / l : 0.f;
+      __nv_bfloat16* o = p.out + ((size_t)(row0 + qi) * p.H + head0 + (row - qi * p.G)) * HD;
+#pragma unroll 1
+      for (int c = 0; c < HD; c += 32) {
+        uint32_t raw[32];
+        tmem_ld32(tmem_o + lane_addr + (uint32_t)c, raw);
+        if (real) {
+          uint4 v[4];
+          __nv_bfloat162* h2 = reinterpret_cast<__nv_bfloat162*>(v);
+#pragma unroll
+          for (int i = 0; i < 32; i += 2)
+            h2[i >> 1] = __floats2bfloat162_rn(__uint_as_float(raw[i]) * inv, __uint_as_float(raw[i + 1]) * inv);
+#pragma unroll
+          for (int q4 = 0; q4 < 4; ++q4) *reinterpret_cast<uint4*>(o + c + q4 * 8) = v[q4];
+        }
+      }
+    }
+  }
+
+  fence_before_sync();
+  __syncthreads();
+  if (warp == 1) {
+    fence_after_sync();
+    tmem_dealloc(tmem_base, kTmemCols);
+  }
+}
+
+}  // namespace
+
+// 1 if the tcgen05 prefill kernel serves this shape: head size 128, a power-of-two group of at
+// most 16 query heads per kv head, pages of 8 to 128 tokens (a power of two).
+extern "C" int asb_attention_tcgen05_supported(int hd, int group, int block_size) {
+  const bool pow2_group = group >= 1 && group <= 16 && (group & (group - 1)) == 0;
+  const bool pow2_page = block_size >= 8 && block_size <= 128 && (block_size & (block_size - 1)) == 0;
+  return hd == 128 && pow2_group && pow2_page ? 1 : 0;
+}
+
+// Attention for every request that brings more than 8 tokens in this step (others are left
+// untouched for the decode kernel). q, out: [T, H, 128] bfloat16; caches [num_blocks, KV, bs, 128].
+extern "C" int asb_prefill_attention_tcgen05(void* out, const void* q, const void* k_cache, const void* v_cache,
+                                             const int* block_tables, const int* req_q_start,
+                                             const int* req_pos_start, int num_tokens, int R, int H, int KV,
+                                             int hd, int bs, int num_blocks, int table_width, int window,
+                                             float scale, int* status, cudaStream_t stream) {
+  if (num_tokens == 0 || R == 0) return 0;
+  if (KV < 1 || H % KV) return asb::fail("prefill_attention_tcgen05: %d heads over %d kv heads", H, KV);
+  if (!asb_attention_tcgen05_supported(hd, H / KV, bs))
+    return asb::fail("prefill_attention_tcgen05: head_dim %d, group %d, page %d are not served", hd, H / KV, bs);
+  if (!status) return asb::fail("prefill_attention_tcgen05: a status word is required");
+  AttnParams p;
+  p.out = (__nv_bfloat16*)out;
+  p.block_tables = block_tables; p.req_q_start = req_q_start; p.req_pos_start = req_pos_start;
+  p.status = status;
+  p.T = num_tokens; p.R = R; p.H = H; p.KV = KV; p.bs = bs; p.table_width = table_width;
+  p.G = H / KV;
+  p.QT = kRows / p.G;
+  p.window = window;
+  p.scale_log2 = scale * 1.4426950408889634f;
+
+  alignas(64) CUtensorMap mq, mk, mv;
+  {
+    const cuuint64_t dims[3] = {(cuuint64_t)HD, (cuuint64_t)H, (cuuint64_t)num_tokens};
+    const cuuint64_t strides[2] = {(cuuint64_t)HD * 2, (cuuint64_t)H * HD * 2};
+    const cuuint32_t box[3] = {64, (cuuint32_t)p.G, (cuuint32_t)p.QT};
+    if (int rc = make_bf16_map(&mq, q, 3, dims, strides, box)) return rc;
+  }
+  {
+    const cuuint64_t dims[2] = {(cuuint64_t)HD, (cuuint64_t)num_blocks * KV * bs};
+    const cuuint64_t strides[1] = {(cuuint64_t)HD * 2};
+    const cuuint32_t box[2] = {64, (cuuint32_t)bs};
+    if (int rc = make_bf16_map(&mk, k_cache, 2, dims, strides, box)) return rc;
+    if (int rc = make_bf16_map(&mv, v_cache, 2, dims, strides, box)) return rc;
+  }
+  auto kern = prefill_attention_tcgen05_kernel;
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem);
+  if (e != cudaSuccess) return asb::fail("prefill_attention_tcgen05: shared memory %d: %s", kSmem, cudaGetErrorString(e));
+  dim3 grid((num_tokens + p.QT - 1) / p.QT + R, KV);
+  if (grid.y > 65535) return asb::fail("prefill_attention_tcgen05: too many kv heads");
+  asb::launch(kern, grid, kThreads, kSmem, stream, mq, mk, mv, p);
+  return asb::check_launch("prefill_attention_tcgen05");
+}

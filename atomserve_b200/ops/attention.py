@@ -3,6 +3,7 @@
 from __future__ import annotations
 
 import ctypes
+import os
 
 import torch
 
@@ -12,6 +13,11 @@ KEY_TILE = 32
 TARGET_BLOCKS = 296  # two blocks for each of the 148 SMs before the key range is split
 SHORT_ROWS = 8  # requests with at most this many new tokens run row by row in the decode kernel
 DECODE_TARGET_BLOCKS = 592  # four resident decode blocks per SM keep the HBM stream busy
+
+
+# Which kernel serves prompt portions in bfloat16 with head size 128: "tcgen05" (scores and output
+# in tensor memory; the default where its shape rules hold) or "mma" (the mma.sync kernel).
+PREFILL_KERNEL = os.environ.get("ATOMSERVE_B200_PREFILL_ATTENTION", "tcgen05")
 
 
 def attention_tile_shape(group: int) -> tuple[int, int]:
@@ -126,6 +132,22 @@ def _paged_attention_mma(q, out, k_cache, v_cache, block_tables, req_q_start, re
         has_long = any(n > SHORT_ROWS for n in host_q_lens)
         all_single = all(n == 1 for n in host_q_lens)
         short_rows = sum(n for n in host_q_lens if n <= SHORT_ROWS)
+    if has_long and PREFILL_KERNEL == "tcgen05" and lib().asb_attention_tcgen05_supported(hd, H // KV, bs):
+        from atomserve_b200.ops.linear import gemm_status
+
+        check(lib().asb_prefill_attention_tcgen05(
+            ptr(out), ptr(q), ptr(k_cache), ptr(v_cache), ptr(block_tables), ptr(req_q_start), ptr(req_pos_start),
+            T, num_requests, H, KV, hd, bs, k_cache.shape[0], block_tables.shape[1], win, float(scale),
+            ptr(gemm_status(q.device)), stream()))  # fmt: skip
+        if not has_short:
+            return out
+        # what is left for the decode kernel: the short rows, unpartitioned (the reduction over
+        # partitions covers every row of the step, and the long rows have no partial results)
+        check(lib().asb_paged_attention_mma(
+            ptr(out), ptr(q), ptr(k_cache), ptr(v_cache), ptr(block_tables), ptr(req_q_start),
+            ptr(req_pos_start), None, None, None, T, num_requests, H, KV, hd, bs,
+            block_tables.shape[1], win, 1 << 30, 1, float(scale), 1, 0, 0, stream()))  # fmt: skip
+        return out
     ps, np_ = 1 << 30, 1
     if has_short and not has_long:
         ps, np_ = partitions or plan_decode_partitions(short_rows, KV, H // KV, max_context, win)

@@ -372,3 +372,42 @@ def test_gemm_tcgen05(ops, M, N, K):
     if M > 1:
         again = gemm_tcgen05(x, w, None, torch.float32)
         assert torch.equal(again, full)
+
+
+TCGEN05_ATTN_CASES = [
+    # H, KV, bs, ctx_lens, q_lens, window
+    (4, 1, 16, [200], [200], None),
+    (32, 8, 16, [700, 33, 2100], [1, 33, 300], None),
+    (8, 8, 8, [130, 500], [130, 260], None),
+    (16, 8, 32, [640, 129, 77], [129, 129, 9], None),
+    (16, 2, 64, [1000], [333], 200),
+    (16, 1, 128, [300, 150], [100, 150], 64),
+    (8, 2, 16, [2048], [2048], None),
+]
+
+
+@pytest.mark.parametrize("case", TCGEN05_ATTN_CASES)
+def test_prefill_attention_tcgen05(ops, case):
+    """The tcgen05 prefill kernel (scores and output in tensor memory, V as an MN-major operand,
+    pages fetched by TMA) against the plain attention, and against the mma.sync kernel it
+    replaces; prompt portions with a cached prefix, several requests, windows, every group size
+    and page size it serves."""
+    from atomserve_b200.ops import attention as attn
+    from atomserve_b200.ops.linear import check_gemm_status
+
+    H, KV, bs, ctx_lens, q_lens, window = case
+    hd = 128
+    dev, dense, qs = paged_setup(ctx_lens, q_lens, H, KV, hd, bs, torch.bfloat16, seed=H + bs)
+    ref = attention_reference(qs, dense, ctx_lens, q_lens, window)
+    common = dict(num_requests=len(ctx_lens), max_context=max(ctx_lens), window=window, scale=hd**-0.5, host_q_lens=q_lens)
+    assert attn.lib().asb_attention_tcgen05_supported(hd, H // KV, bs)
+    results = {}
+    for kernel in ("tcgen05", "mma"):
+        attn.PREFILL_KERNEL = kernel
+        try:
+            results[kernel] = ops.paged_attention(**dev, **common).float().cpu()
+        finally:
+            attn.PREFILL_KERNEL = "tcgen05"
+    check_gemm_status()
+    assert torch.allclose(results["tcgen05"], ref, atol=2e-2, rtol=2e-2), float((results["tcgen05"] - ref).abs().max())
+    assert torch.allclose(results["mma"], ref, atol=2e-2, rtol=2e-2)
