@@ -8,7 +8,7 @@
 //
 // One block per (request, tile of QT query tokens, kv head). Its 128 rows are the (token, head)
 // pairs of the tile, QT = 128 / G tokens times the G query heads of the kv head, loaded as one
-// 3-D TMA box of q [T, H, hd]. Keys are visited in tiles of 128 at absolute multiples of 128.
+// 3-D TMA box of q [T, H, hd]. Keys are visited in tiles of 64 at absolute multiples of 64.
 //
 //   warp 0     TMA: the Q tile once, then per key tile the pages of K and of V named by the
 //              block table, each page as two boxes (the two 64-element halves of the head).
@@ -17,12 +17,15 @@
 //              softmax has written P. V is consumed as an MN-major operand: its rows in shared
 //              memory are keys, exactly as the pages hold them.
 //   warps 2-5  softmax: thread r owns row r (a TMEM lane), so row maxima and sums need no
-//              shuffles. It reads its scores twice (maximum, then exponentials), rescales its
-//              row of O in tensor memory when the maximum moved, writes P as bfloat16 into shared
-//              memory in the swizzled K-major layout, and at the end stores O / sum.
+//              shuffles. It reads its scores once, rescales its row of O in tensor memory only when
+//              the maximum moved by more than a factor of 256, writes P as bfloat16 into one of two
+//              shared-memory buffers in the swizzled K-major layout, and at the end stores O / sum.
+//              With two P buffers it waits for the previous P V only when it has to rescale, so
+//              softmax and tensor cores work on different tiles at the same time.
 //
-// Shared memory: Q 32 KB, two stages of (K 32 KB + V 32 KB), P 32 KB. Tensor memory: two score
-// buffers and the output accumulator, 128 columns each. All barrier waits are bounded; a wait
+// Shared memory: Q 32 KB, five stages of (K 16 KB + V 16 KB), so that loads run several tiles
+// ahead of their use (a TMA load takes longer than a tile's arithmetic), P 2 x 16 KB. Tensor memory:
+// two score buffers of 64 columns and the output accumulator of 128. All barrier waits are bounded; a wait
 // that runs out sets *status and the roles wind down to the final barrier.
 #include "tcgen05.cuh"
 
@@ -33,13 +36,16 @@ using namespace asb::t5;
 constexpr int kThreads = 192;
 constexpr int HD = 128;
 constexpr int kRows = 128;
-constexpr int kKeys = 128;
-constexpr int kBlockBytes = 128 * 64 * 2;       // one [128 rows][64 elements] swizzled block: 16 KB
-constexpr int kTileBytes = 2 * kBlockBytes;     // 32 KB: the two halves of the head (or of the keys, for P)
-constexpr int kStageBytes = 2 * kTileBytes;     // K and V
-constexpr int kStages = 2;
-constexpr int kSmem = kTileBytes /*Q*/ + kStages * kStageBytes + kTileBytes /*P*/ + 1024 + 256;
-constexpr uint32_t kTmemCols = 512;
+constexpr int kKeys = 64;                         // keys per tile
+constexpr int kBlockBytes = kRows * 64 * 2;       // one [128 rows][64 elements] swizzled block: 16 KB
+constexpr int kQBytes = 2 * kBlockBytes;          // Q: the two 64-element halves of the head
+constexpr int kKVBlockBytes = kKeys * 64 * 2;     // one [kKeys rows][64 elements] block: 8 KB
+constexpr int kKVBytes = 2 * kKVBlockBytes;       // K or V of a tile: two halves of the head
+constexpr int kStageBytes = 2 * kKVBytes;         // K and V
+constexpr int kStages = 5;                        // K/V tiles in flight: TMA latency is several tiles long
+constexpr int kPBytes = (kKeys / 64) * kBlockBytes;  // one P buffer: [128 rows][kKeys] in blocks of 64 keys
+constexpr int kSmem = kQBytes + kStages * kStageBytes + 2 * kPBytes + 1024;  // two P buffers
+constexpr uint32_t kTmemCols = 256;               // two score buffers of kKeys columns, 128 of output
 constexpr int kShortRows = 8;
 
 struct AttnParams {
@@ -67,20 +73,25 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   unsigned char* aligned = smem_raw + (base - smem_u32(smem_raw));
   const uint32_t q_smem = base;
-  auto k_smem = [&](int s) { return base + kTileBytes + (uint32_t)s * kStageBytes; };
-  auto v_smem = [&](int s) { return base + kTileBytes + (uint32_t)s * kStageBytes + kTileBytes; };
-  const uint32_t p_smem = base + kTileBytes + kStages * kStageBytes;
-  unsigned char* p_ptr = aligned + kTileBytes + kStages * kStageBytes;
-  const uint32_t bars = p_smem + kTileBytes;
+  auto k_smem = [&](int s) { return base + kQBytes + (uint32_t)s * kStageBytes; };
+  auto v_smem = [&](int s) { return base + kQBytes + (uint32_t)s * kStageBytes + kKVBytes; };
+  const uint32_t p_smem = base + kQBytes + kStages * kStageBytes;
+  unsigned char* p_ptr = aligned + kQBytes + kStages * kStageBytes;
+  const uint32_t bars = p_smem + 2 * kPBytes;
   const uint32_t q_full = bars;
   auto kv_full = [&](int s) { return bars + 8u * (1 + s); };
-  auto kv_empty = [&](int s) { return bars + 8u * (3 + s); };
-  auto s_full = [&](int b) { return bars + 8u * (5 + b); };
-  const uint32_t p_full = bars + 8u * 7;
-  const uint32_t pv_done = bars + 8u * 8;
-  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(aligned + 2 * kTileBytes + kStages * kStageBytes + 8 * 9);
+  auto kv_empty = [&](int s) { return bars + 8u * (1 + kStages + s); };
+  auto s_full = [&](int b) { return bars + 8u * (1 + 2 * kStages + b); };
+  const uint32_t p_full = bars + 8u * (3 + 2 * kStages);
+  auto pv_done = [&](int b) { return bars + 8u * (4 + 2 * kStages + b); };  // one per P buffer
+  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(aligned + kQBytes + kStages * kStageBytes + 2 * kPBytes + 8 * (6 + 2 * kStages));
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  // The 1 KB beyond the tiles holds the alignment padding and, after it, the barriers.
+  if (base - smem_u32(smem_raw) > 1024 - 8 * (7 + 2 * kStages)) {
+    if (threadIdx.x == 0) atomicExch(p.status, 19);
+    return;
+  }
 
   // Which request and tile of its tokens? Only requests with more than kShortRows tokens count.
   int tile = blockIdx.x, r = 0, q_len = 0;
@@ -112,10 +123,12 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
     for (int s = 0; s < kStages; ++s) {
       mbar_init(kv_full(s), 1);
       mbar_init(kv_empty(s), 1);
-      mbar_init(s_full(s), 1);
     }
+    mbar_init(s_full(0), 1);
+    mbar_init(s_full(1), 1);
     mbar_init(p_full, 4);  // one arrival per softmax warp
-    mbar_init(pv_done, 1);
+    mbar_init(pv_done(0), 1);
+    mbar_init(pv_done(1), 1);
     mbar_init_fence();
   }
   if (warp == 1) tmem_alloc(smem_u32((const void*)tmem_slot), kTmemCols);
@@ -123,37 +136,50 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
   __syncthreads();
   fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
-  auto tmem_s = [&](int j) { return tmem_base + (uint32_t)(j & 1) * 128u; };  // two score buffers
-  const uint32_t tmem_o = tmem_base + 256;
+  auto tmem_s = [&](int j) { return tmem_base + (uint32_t)(j & 1) * kKeys; };  // two score buffers
+  const uint32_t tmem_o = tmem_base + 2 * kKeys;
   asb::pdl_wait();
   asb::pdl_launch_dependents();
 
   if (warp == 0) {
+    // The whole warp looks up the pages of a key tile (one page per lane, the loads in flight
+    // together); lane 0 waits for the stage and issues the TMA loads.
     if (lane == 0) {
-      mbar_expect_tx(q_full, kTileBytes);
+      mbar_expect_tx(q_full, kQBytes);
       tma_load_3d(q_smem, &map_q, q_full, 0, head0, row0);
       tma_load_3d(q_smem + kBlockBytes, &map_q, q_full, 64, head0, row0);
-      const int pages_per_tile = kKeys / p.bs;
-      const int last_page = (key_hi - 1) / p.bs;  // the last page this request certainly holds
-      bool ok = true;
-      for (int j = 0; j < num_tiles && ok; ++j) {
-        const int s = j & 1;
-        ok = mbar_wait(kv_empty(s), (((uint32_t)j >> 1) & 1u) ^ 1u, p.status, 11);
-        if (!ok) break;
-        mbar_expect_tx(kv_full(s), kStageBytes);
-        const int first_page = (kt_begin + j * kKeys) / p.bs;
-        for (int i = 0; i < pages_per_tile; ++i) {
-          // pages beyond the request's end, or released by the window, are masked out anyway:
-          // read a page the request holds, so that shared memory never holds non-finite values
-          int page = min(first_page + i, last_page);
-          int blk = table[page];
-          if (blk < 0) blk = table[last_page];
-          const int y = (blk * p.KV + kvh) * p.bs;
-          const uint32_t off = (uint32_t)(i * p.bs) * 128u;
+    }
+    const int box_rows = min(p.bs, kKeys);        // rows one TMA box brings (the tensor maps' box)
+    const int boxes_per_tile = kKeys / box_rows;  // at most 8
+    const int last_page = (key_hi - 1) / p.bs;    // the last page this request certainly holds
+    const int fallback = table[last_page];
+    bool ok = true;
+    for (int j = 0; j < num_tiles; ++j) {
+      const int s = j % kStages;
+      // pages beyond the request's end, or released by the window, are masked out anyway: read a
+      // page the request holds, so that shared memory never holds non-finite values
+      int row_y = 0;
+      if (lane < boxes_per_tile) {
+        const int key = kt_begin + j * kKeys + lane * box_rows;
+        int blk = table[min(key / p.bs, last_page)];
+        if (blk < 0) blk = fallback;
+        row_y = (blk * p.KV + kvh) * p.bs + key % p.bs;
+      }
+      int ok_i = 1;
+      if (lane == 0) {
+        ok_i = mbar_wait(kv_empty(s), (((uint32_t)j / kStages) & 1u) ^ 1u, p.status, 11) ? 1 : 0;
+        if (ok_i) mbar_expect_tx(kv_full(s), kStageBytes);
+      }
+      ok = __shfl_sync(0xffffffffu, ok_i, 0) != 0;
+      if (!ok) break;
+      for (int i = 0; i < boxes_per_tile; ++i) {
+        const int y = __shfl_sync(0xffffffffu, row_y, i);
+        if (lane == 0) {
+          const uint32_t off = (uint32_t)(i * box_rows) * 128u;
           tma_load_2d(k_smem(s) + off, &map_k, kv_full(s), 0, y);
-          tma_load_2d(k_smem(s) + kBlockBytes + off, &map_k, kv_full(s), 64, y);
+          tma_load_2d(k_smem(s) + kKVBlockBytes + off, &map_k, kv_full(s), 64, y);
           tma_load_2d(v_smem(s) + off, &map_v, kv_full(s), 0, y);
-          tma_load_2d(v_smem(s) + kBlockBytes + off, &map_v, kv_full(s), 64, y);
+          tma_load_2d(v_smem(s) + kKVBlockBytes + off, &map_v, kv_full(s), 64, y);
         }
       }
     }
@@ -162,11 +188,12 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
       constexpr uint32_t idesc_qk = instr_desc_bf16(kRows, kKeys, false);
       constexpr uint32_t idesc_pv = instr_desc_bf16(kRows, HD, true);
       auto issue_qk = [&](int j) {
-        const int s = j & 1;
+        const int s = j % kStages;
 #pragma unroll
         for (int ks = 0; ks < HD / 16; ++ks) {  // 16 head elements per MMA: 32 bytes along the swizzled row
-          const uint32_t off = (uint32_t)(ks / 4) * kBlockBytes + (uint32_t)(ks % 4) * 32u;
-          umma_bf16(tmem_s(j), desc_k_major(q_smem + off, 1024), desc_k_major(k_smem(s) + off, 1024), idesc_qk,
+          const uint32_t in_row = (uint32_t)(ks % 4) * 32u;
+          umma_bf16(tmem_s(j), desc_k_major(q_smem + (uint32_t)(ks / 4) * kBlockBytes + in_row, 1024),
+                    desc_k_major(k_smem(s) + (uint32_t)(ks / 4) * kKVBlockBytes + in_row, 1024), idesc_qk,
                     (uint32_t)(ks != 0));
         }
         umma_commit(s_full(j & 1));
@@ -179,7 +206,7 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
       }
       for (int j = 0; j < num_tiles && ok; ++j) {
         if (j + 1 < num_tiles) {
-          ok = mbar_wait(kv_full((j + 1) & 1), ((uint32_t)(j + 1) >> 1) & 1u, p.status, 14);
+          ok = mbar_wait(kv_full((j + 1) % kStages), ((uint32_t)(j + 1) / kStages) & 1u, p.status, 14);
           if (!ok) break;
           fence_after_sync();
           issue_qk(j + 1);
@@ -187,15 +214,15 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
         ok = mbar_wait(p_full, (uint32_t)j & 1u, p.status, 15);
         if (!ok) break;
         fence_after_sync();
-        const int s = j & 1;
+        const int s = j % kStages;
 #pragma unroll
         for (int ks = 0; ks < kKeys / 16; ++ks) {  // 16 keys per MMA
-          const uint64_t a = desc_k_major(p_smem + (uint32_t)(ks / 4) * kBlockBytes + (uint32_t)(ks % 4) * 32u, 1024);
-          // V: rows are keys (128 bytes each), 8-key groups 1024 bytes apart, head halves 16 KB apart
-          const uint64_t b = desc_mn_major(v_smem(s) + (uint32_t)ks * 2048u, kBlockBytes, 1024);
+          const uint64_t a = desc_k_major(p_smem + (uint32_t)(j & 1) * kPBytes + (uint32_t)(ks / 4) * kBlockBytes + (uint32_t)(ks % 4) * 32u, 1024);
+          // V: rows are keys (128 bytes each), 8-key groups 1024 bytes apart, head halves one block apart
+          const uint64_t b = desc_mn_major(v_smem(s) + (uint32_t)ks * 2048u, kKVBlockBytes, 1024);
           umma_bf16(tmem_o, a, b, idesc_pv, (uint32_t)((j | ks) != 0));
         }
-        umma_commit(pv_done);
+        umma_commit(pv_done(j & 1));
         umma_commit(kv_empty(s));
       }
     }
@@ -208,6 +235,7 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
     const int pos = real ? pos0 + qi : -1;  // padding rows see nothing
     const int row_lo = p.window > 0 ? max(key_lo, pos - p.window + 1) : key_lo;
     const uint32_t lane_addr = (uint32_t)(quad * 32) << 16;
+    const bool real_block = nq * p.G == kRows;  // no padding rows in this block
     float m = -INFINITY, l = 0.f;
     bool ok = true;
     for (int j = 0; j < num_tiles && ok; ++j) {
@@ -217,64 +245,80 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
       ok = __shfl_sync(0xffffffffu, ok_i, 0) != 0;
       if (!ok) break;
       fence_after_sync();
-      // pass 1: the row's maximum over this tile
-      float tile_max = -INFINITY;
-#pragma unroll 1
-      for (int c = 0; c < kKeys; c += 32) {
-        uint32_t raw[32];
-        tmem_ld32(tmem_s(j) + lane_addr + (uint32_t)c, raw);
+      // The row's 128 raw scores, read from tensor memory once (four loads in flight, one wait)
+      // and kept in registers. Tiles strictly inside every row's view (below the diagonal,
+      // inside the window) need no mask.
+      const bool inside = kt0 + kKeys <= pos0 + 1 && kt0 >= key_lo && real_block &&
+                          (p.window <= 0 || kt0 > pos0 + nq - 1 - p.window);
+      uint32_t raw[kKeys];
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          const int key = kt0 + c + i;
-          const float sc = (key <= pos && key >= row_lo) ? __uint_as_float(raw[i]) * p.scale_log2 : -INFINITY;
-          tile_max = fmaxf(tile_max, sc);
+      for (int c = 0; c < kKeys; c += 32) tmem_ld32_nowait(tmem_s(j) + lane_addr + (uint32_t)c, raw + c);
+      tmem_ld_wait();
+      float raw_max = -INFINITY;
+      if (inside) {
+#pragma unroll
+        for (int i = 0; i < kKeys; ++i) raw_max = fmaxf(raw_max, __uint_as_float(raw[i]));
+      } else {
+#pragma unroll
+        for (int i = 0; i < kKeys; ++i) {
+          const int key = kt0 + i;
+          if (!(key <= pos && key >= row_lo)) raw[i] = 0xff800000u;  // -inf
+          raw_max = fmaxf(raw_max, __uint_as_float(raw[i]));
         }
       }
-      const float m_new = fmaxf(m, tile_max);
-      const float m_use = m_new == -INFINITY ? 0.f : m_new;  // a row that has seen nothing yet
-      const float corr = fast_exp2(m - m_use);
-      m = m_new;
-      l *= corr;
-      if (j > 0) {
-        // the previous P V must have completed before O is rescaled and P overwritten
-        if (lane == 0) ok_i = mbar_wait(pv_done, (uint32_t)(j - 1) & 1u, p.status, 17) ? 1 : 0;
+      const float tile_max = raw_max * p.scale_log2;  // the scale is positive
+      // The running maximum moves only when the new one exceeds it by more than 8 (a factor of
+      // 256 in the probabilities, harmless in float32 sums and bfloat16 operands); otherwise the
+      // older maximum stays and neither the sum nor the accumulator needs rescaling.
+      float corr = 1.f;
+      if (tile_max > m + 8.f || m == -INFINITY) {
+        const float m_new = fmaxf(m, tile_max);
+        const float m_ref = m_new == -INFINITY ? 0.f : m_new;  // a row that has seen nothing yet
+        corr = fast_exp2(m - m_ref);  // 0 when m was -inf
+        m = m_new;
+        l *= corr;
+      }
+      const float m_use = m == -INFINITY ? 0.f : m;
+      if (j > 0 && __any_sync(0xffffffffu, corr != 1.f)) {
+        // rescale this row of O: the previous P V (tile j - 1) must have completed
+        if (lane == 0) ok_i = mbar_wait(pv_done((j - 1) & 1), ((uint32_t)(j - 1) >> 1) & 1u, p.status, 17) ? 1 : 0;
         ok = __shfl_sync(0xffffffffu, ok_i, 0) != 0;
         if (!ok) break;
         fence_after_sync();
-        if (__any_sync(0xffffffffu, corr != 1.f)) {
 #pragma unroll 1
-          for (int c = 0; c < HD; c += 32) {
-            uint32_t raw[32];
-            tmem_ld32(tmem_o + lane_addr + (uint32_t)c, raw);
+        for (int c = 0; c < HD; c += 32) {
+          uint32_t oraw[32];
+          tmem_ld32(tmem_o + lane_addr + (uint32_t)c, oraw);
 #pragma unroll
-            for (int i = 0; i < 32; ++i) raw[i] = __float_as_uint(__uint_as_float(raw[i]) * corr);
-            tmem_st32(tmem_o + lane_addr + (uint32_t)c, raw);
-          }
-          tmem_st_wait();
+          for (int i = 0; i < 32; ++i) oraw[i] = __float_as_uint(__uint_as_float(oraw[i]) * corr);
+          tmem_st32(tmem_o + lane_addr + (uint32_t)c, oraw);
         }
+        tmem_st_wait();
       }
-      // pass 2: probabilities, their sum, and P as bfloat16 in the swizzled K-major layout
-#pragma unroll 1
-      for (int c = 0; c < kKeys; c += 32) {
-        uint32_t raw[32];
-        tmem_ld32(tmem_s(j) + lane_addr + (uint32_t)c, raw);
-        uint32_t packed[16];
+      if (j > 1) {
+        // this tile's P buffer was last read by the P V of tile j - 2
+        if (lane == 0) ok_i = mbar_wait(pv_done(j & 1), ((uint32_t)(j - 2) >> 1) & 1u, p.status, 20) ? 1 : 0;
+        ok = __shfl_sync(0xffffffffu, ok_i, 0) != 0;
+        if (!ok) break;
+      }
+      // probabilities exp2(score * scale - max), their sum, and P as bfloat16 in the swizzled
+      // K-major layout (a masked score is -inf and gives 0)
+      const float neg_m = -m_use;
 #pragma unroll
-        for (int i = 0; i < 32; i += 2) {
-          const int key = kt0 + c + i;
-          const float a = (key <= pos && key >= row_lo) ? fast_exp2(__uint_as_float(raw[i]) * p.scale_log2 - m_use) : 0.f;
-          const float b = (key + 1 <= pos && key + 1 >= row_lo) ? fast_exp2(__uint_as_float(raw[i + 1]) * p.scale_log2 - m_use) : 0.f;
+      for (int c = 0; c < kKeys; c += 8) {
+        uint32_t packed[4];
+#pragma unroll
+        for (int i = 0; i < 8; i += 2) {
+          const float a = fast_exp2(fmaf(__uint_as_float(raw[c + i]), p.scale_log2, neg_m));
+          const float b = fast_exp2(fmaf(__uint_as_float(raw[c + i + 1]), p.scale_log2, neg_m));
           l += a + b;
           __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
           packed[i >> 1] = *reinterpret_cast<uint32_t*>(&v);
         }
-        // keys c..c+31 of this row: four 16-byte chunks of block c / 64
-        unsigned char* dst = p_ptr + (c / 64) * kBlockBytes + row * 128;
-#pragma unroll
-        for (int q4 = 0; q4 < 4; ++q4) {
-          const int chunk = ((c % 64) / 8 + q4) ^ (row & 7);
-          *reinterpret_cast<uint4*>(dst + chunk * 16) = make_uint4(packed[q4 * 4], packed[q4 * 4 + 1], packed[q4 * 4 + 2], packed[q4 * 4 + 3]);
-        }
+        // keys c..c+7 of this row: one 16-byte chunk of block c / 64
+        const int chunk = ((c % 64) / 8) ^ (row & 7);
+        *reinterpret_cast<uint4*>(p_ptr + (j & 1) * kPBytes + (c / 64) * kBlockBytes + row * 128 + chunk * 16) =
+            make_uint4(packed[0], packed[1], packed[2], packed[3]);
       }
       fence_async_smem();   // P is read by the tensor cores
       fence_before_sync();
@@ -284,7 +328,7 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
     // epilogue: O / sum, rounded once
     if (ok) {
       int ok_i = 1;
-      if (lane == 0) ok_i = mbar_wait(pv_done, (uint32_t)(num_tiles - 1) & 1u, p.status, 18) ? 1 : 0;
+      if (lane == 0) ok_i = mbar_wait(pv_done((num_tiles - 1) & 1), ((uint32_t)(num_tiles - 1) >> 1) & 1u, p.status, 18) ? 1 : 0;
       ok = __shfl_sync(0xffffffffu, ok_i, 0) != 0;
     }
     if (ok) {
@@ -319,10 +363,10 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
 }  // namespace
 
 // 1 if the tcgen05 prefill kernel serves this shape: head size 128, a power-of-two group of at
-// most 16 query heads per kv head, pages of 8 to 128 tokens (a power of two).
+// most 16 query heads per kv head, pages of 8 to 256 tokens (a power of two).
 extern "C" int asb_attention_tcgen05_supported(int hd, int group, int block_size) {
   const bool pow2_group = group >= 1 && group <= 16 && (group & (group - 1)) == 0;
-  const bool pow2_page = block_size >= 8 && block_size <= 128 && (block_size & (block_size - 1)) == 0;
+  const bool pow2_page = block_size >= 8 && block_size <= 256 && (block_size & (block_size - 1)) == 0;
   return hd == 128 && pow2_group && pow2_page ? 1 : 0;
 }
 
@@ -358,7 +402,7 @@ extern "C" int asb_prefill_attention_tcgen05(void* out, const void* q, const voi
   {
     const cuuint64_t dims[2] = {(cuuint64_t)HD, (cuuint64_t)num_blocks * KV * bs};
     const cuuint64_t strides[1] = {(cuuint64_t)HD * 2};
-    const cuuint32_t box[2] = {64, (cuuint32_t)bs};
+    const cuuint32_t box[2] = {64, (cuuint32_t)(bs < kKeys ? bs : kKeys)};
     if (int rc = make_bf16_map(&mk, k_cache, 2, dims, strides, box)) return rc;
     if (int rc = make_bf16_map(&mv, v_cache, 2, dims, strides, box)) return rc;
   }
