@@ -15,7 +15,7 @@ from tiny_configs import TINY
 
 pytestmark = pytest.mark.gpu
 DTYPES = ["float32", "bfloat16"]
-LENGTHS = {"a": [5, 17, 33, 70], "b": [1, 9, 24, 40, 75], "c": [3, 50, 90, 41]}
+LENGTHS = {"a": [5, 17, 33, 70], "b": [1, 9, 24, 40, 75], "c": [3, 50, 90, 41], "d": [45, 200, 9, 330]}
 
 
 @pytest.fixture(scope="module")
@@ -68,20 +68,20 @@ def check(got, oracle, dtype, what):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("name", ["a", "b", "c"])
+@pytest.mark.parametrize("name", ["a", "b", "c", "d"])
 def test_each_request_alone_and_whole(models, name, dtype):
     cfg, bs, folder, ps, oracle = models[name]
-    rp = replayer(folder, dtype, bs, 128)
+    rp = replayer(folder, dtype, bs, max(-(-len(p) // 64) * 64 for p in ps))
     for i, (p, ref) in enumerate(zip(ps, oracle)):
         logits = rp.step([dict(id=i, tokens=p, want=list(range(len(p))))], end=[i])
         check(logits, ref, dtype, f"{name} request {i} whole")
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("name", ["a", "b", "c"])
+@pytest.mark.parametrize("name", ["a", "b", "c", "d"])
 def test_prefill_then_last_32_one_by_one(models, name, dtype):
     cfg, bs, folder, ps, oracle = models[name]
-    rp = replayer(folder, dtype, bs, 128)
+    rp = replayer(folder, dtype, bs, max(-(-len(p) // 64) * 64 for p in ps))
     for i, (p, ref) in enumerate(zip(ps, oracle)):
         head = max(len(p) - 32, 0)
         got = []
@@ -94,10 +94,10 @@ def test_prefill_then_last_32_one_by_one(models, name, dtype):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("name", ["a", "b", "c"])
+@pytest.mark.parametrize("name", ["a", "b", "c", "d"])
 def test_portions_of_changing_size(models, name, dtype):
     cfg, bs, folder, ps, oracle = models[name]
-    rp = replayer(folder, dtype, bs, 128)
+    rp = replayer(folder, dtype, bs, max(-(-len(p) // 64) * 64 for p in ps))
     sizes = [2, 7, 3, 16, 2, 17, 5, 31, 2, 9]
     for i, (p, ref) in enumerate(zip(ps, oracle)):
         at, k = 0, i
@@ -134,7 +134,7 @@ def mixed_trace(ps, rng, max_live=4):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("name", ["a", "b", "c"])
+@pytest.mark.parametrize("name", ["a", "b", "c", "d"])
 def test_mixed_requests_reusing_pages(models, name, dtype):
     """Up to four live requests, portions beside single tokens, in a pool so small that pages
     freed by finished requests are taken again by later ones; every request appears three times,
@@ -159,7 +159,7 @@ def test_mixed_requests_reusing_pages(models, name, dtype):
 @pytest.mark.parametrize("dtype", DTYPES)
 def test_long_decoding(models, dtype):
     """300 tokens one by one (across many pages and, for config c, far beyond its window)."""
-    for name in ("b", "c"):
+    for name in ("b", "c", "d"):
         cfg, bs, folder, _, _ = models[name]
         w = checkpoint(cfg, seed=21)
         p = prompts(cfg, [300], seed=9)[0]

@@ -27,4 +27,17 @@ TINY_C = dict(
 )  # fmt: skip
 BLOCK_SIZE_C = 16
 
-TINY = {"a": (TINY_A, BLOCK_SIZE_A), "b": (TINY_B, BLOCK_SIZE_B), "c": (TINY_C, BLOCK_SIZE_C)}
+# Head size 128 with four query heads per kv head, as the served models have it: the shapes that
+# run the tensor-core kernels (tcgen05 GEMM and prefill attention, mma.sync decode attention).
+TINY_D = dict(
+    architectures=["Qwen3ForCausalLM"], vocab_size=640, hidden_size=256, intermediate_size=704,
+    num_hidden_layers=2, num_attention_heads=8, num_key_value_heads=2, head_dim=128,
+    rms_norm_eps=1e-6, rope_theta=1000000.0, tie_word_embeddings=False,
+    max_position_embeddings=4096, hidden_act="silu",
+)  # fmt: skip
+BLOCK_SIZE_D = 16
+
+TINY = {
+    "a": (TINY_A, BLOCK_SIZE_A), "b": (TINY_B, BLOCK_SIZE_B), "c": (TINY_C, BLOCK_SIZE_C),
+    "d": (TINY_D, BLOCK_SIZE_D),
+}  # fmt: skip
