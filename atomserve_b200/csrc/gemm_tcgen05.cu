@@ -42,7 +42,7 @@ constexpr int BK = 64;    // K elements per stage: 128 bytes, one swizzle atom
 constexpr int UMMA_K = 16;
 constexpr uint32_t kMaxPolls = 1u << 24;
 
-enum Epilogue : int { kStoreBf16 = 0, kStoreBf16Residual = 1, kStoreF32 = 2, kStorePartial = 3 };
+enum Epilogue : int { kStoreBf16 = 0, kStoreBf16Residual = 1, kStoreF32 = 2, kStoreSwiGLU = 4 };
 
 struct GemmParams {
   void* out;             // bf16 or f32 [M, N]
@@ -52,7 +52,7 @@ struct GemmParams {
   int p_rows, q_rows;    // rows of P and Q (M and N, or N and M when swapped)
   int ldo;               // row stride of out (N)
   int swap;              // 1: P = w (lanes are output columns), Q = x
-  int epilogue;          // for whole segments: kStoreBf16 / kStoreBf16Residual / kStoreF32
+  int epilogue;          // kStoreBf16 / kStoreBf16Residual / kStoreF32 / kStoreSwiGLU (out is [M, N / 2])
   int tiles_p, num_tiles;  // tile t -> (t % tiles_p, t / tiles_p)
   int kb_per_tile;       // K blocks of BK per tile
   int stream;            // 0: whole tiles round-robin; 1: equal contiguous ranges of K blocks
@@ -181,6 +181,9 @@ struct Config {
   static constexpr int kTmemCols = 2 * BN < 32 ? 32 : 2 * BN;   // two accumulators
   static constexpr int kSmem = kStages * kStage + 1024 /* alignment slack */ + 256 /* barriers */;
 };
+
+// SwiGLU on a (gate, up) pair of float32 sums (atomserve/kernels.py:437-449).
+__device__ __forceinline__ float swiglu(float gate, float up) { return gate / (1.f + __expf(-gate)) * up; }
 
 __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
@@ -341,6 +344,36 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_cons
           }
           continue;
         }
+        if (p.epilogue == kStoreSwiGLU) {
+          // weight rows alternate gate, up: output column n / 2 = silu(sum[n]) * sum[n + 1]
+          if (p.swap) {
+            // lanes are weight rows: the up sum sits in the next lane
+#pragma unroll
+            for (int j = 0; j < kChunk; ++j) {
+              const float up = __shfl_down_sync(0xffffffffu, __uint_as_float(raw[j]), 1);
+              const int tok = q0 + c + j;
+              if ((lane & 1) == 0 && prow < p.p_rows && tok < p.q_rows)
+                ((__nv_bfloat16*)p.out)[(size_t)tok * (p.ldo / 2) + prow / 2] = __float2bfloat16_rn(swiglu(__uint_as_float(raw[j]), up));
+            }
+          } else if (prow < p.p_rows) {
+            // columns are weight rows: this thread holds eight (gate, up) pairs of its token
+            __nv_bfloat16* o = (__nv_bfloat16*)p.out + (size_t)prow * (p.ldo / 2) + (q0 + c) / 2;
+            const int valid = min(kChunk, p.q_rows - (q0 + c)) / 2;
+            uint4 packed;
+            __nv_bfloat16* ob = reinterpret_cast<__nv_bfloat16*>(&packed);
+#pragma unroll
+            for (int j = 0; j < kChunk / 2; ++j)
+              ob[j] = __float2bfloat16_rn(swiglu(__uint_as_float(raw[2 * j]), __uint_as_float(raw[2 * j + 1])));
+            if (valid == kChunk / 2 && (((uintptr_t)o) & 15) == 0) {
+              *reinterpret_cast<uint4*>(o) = packed;
+            } else {
+#pragma unroll
+              for (int j = 0; j < kChunk / 2; ++j)
+                if (j < valid) o[j] = ob[j];
+            }
+          }
+          continue;
+        }
         if (prow >= p.p_rows) continue;
         if (p.swap) {
           // lanes are output columns (weight rows), TMEM columns are tokens: out[token, prow]
@@ -445,6 +478,19 @@ __global__ void segment_reduce_kernel(const GemmParams p, int parts) {
     v.x += a.x; v.y += a.y; v.z += a.z; v.w += a.w;
   }
   const float e[4] = {v.x, v.y, v.z, v.w};
+  if (p.epilogue == kStoreSwiGLU) {
+    // the four sums are two (gate, up) pairs along the weight-row dimension, which is the slot's
+    // contiguous one in both layouts
+#pragma unroll
+    for (int k = 0; k < 4; k += 2) {
+      const int row = p.swap ? (i + k) % BM : (i + k) / BN, col = p.swap ? (i + k) / BM : (i + k) % BN;
+      const int prow = p0 + row, qrow = q0 + col;
+      if (prow >= p.p_rows || qrow >= p.q_rows) continue;
+      const size_t at = p.swap ? (size_t)qrow * (p.ldo / 2) + prow / 2 : (size_t)prow * (p.ldo / 2) + qrow / 2;
+      ((__nv_bfloat16*)p.out)[at] = __float2bfloat16_rn(swiglu(e[k], e[k + 1]));
+    }
+    return;
+  }
 #pragma unroll
   for (int k = 0; k < 4; ++k) {
     // slot layout: [column][lane] when swapped, [lane][column] otherwise
@@ -573,13 +619,18 @@ extern "C" long long asb_gemm_tcgen05_workspace(int M, int N, int K, int* stream
 }
 
 // out = x . w^T (+ residual). x [M, K] and w [N, K] bfloat16, contiguous, K a multiple of 8 and
-// both bases 16-byte aligned (TMA's rules). out bfloat16 [M, N], or float32 when out_f32.
+// both bases 16-byte aligned (TMA's rules). out bfloat16 [M, N], float32, or [M, N / 2] by mode.
 // workspace: float32, asb_gemm_tcgen05_workspace(M, N, K) elements (null if that is 0); calls that
 // may overlap on the GPU need separate workspaces.
 // status: one int on the device; it stays 0 unless a pipeline wait ran out.
+// mode 0: out bfloat16 (+ residual); 1: out float32; 2: SwiGLU: the rows of w alternate gate and
+// up (row 2i gate_i, row 2i + 1 up_i) and out is bfloat16 [M, N / 2] = silu(gate) * up.
 extern "C" int asb_gemm_tcgen05(void* out, const void* x, const void* w, const void* residual, int M,
-                                int N, int K, int out_f32, float* workspace, int* status,
+                                int N, int K, int mode, float* workspace, int* status,
                                 cudaStream_t stream) {
+  const int out_f32 = mode == 1;
+  if (mode < 0 || mode > 2) return asb::fail("gemm_tcgen05: unknown mode %d", mode);
+  if (mode == 2 && (residual || N % 2)) return asb::fail("gemm_tcgen05: the SwiGLU form takes no residual and an even N");
   if (M == 0 || N == 0) return 0;
   if (K < 8 || K % 8) return asb::fail("gemm_tcgen05: K = %d must be a positive multiple of 8 (16-byte TMA rows)", K);
   if (((uintptr_t)x & 15) || ((uintptr_t)w & 15)) return asb::fail("gemm_tcgen05: operands must be 16-byte aligned");
@@ -597,7 +648,7 @@ extern "C" int asb_gemm_tcgen05(void* out, const void* x, const void* w, const v
   p.ldo = N;
   p.p_rows = pl.swap ? N : M;
   p.q_rows = pl.swap ? M : N;
-  p.epilogue = out_f32 ? kStoreF32 : (residual ? kStoreBf16Residual : kStoreBf16);
+  p.epilogue = mode == 2 ? kStoreSwiGLU : (out_f32 ? kStoreF32 : (residual ? kStoreBf16Residual : kStoreBf16));
   p.tiles_p = pl.tiles_p;
   p.num_tiles = pl.tiles_p * pl.tiles_q;
   p.kb_per_tile = pl.kb_per_tile;

@@ -5,7 +5,7 @@ tensors the serving kernels; nothing here computes on the CPU."""
 from atomserve_b200.ops.attention import attention_tile_shape, paged_attention
 from atomserve_b200.ops.elementwise import embedding, qk_norm_rope_store, rms_norm, rotary, silu_mul
 from atomserve_b200.ops.library import KernelLibraryError, require_device
-from atomserve_b200.ops.linear import linear
+from atomserve_b200.ops.linear import interleave_gate_up, linear, linear_swiglu, swiglu_fusable
 from atomserve_b200.ops.sampling import argmax_rows, presence_penalty, sample_rows
 
 __all__ = [
@@ -13,7 +13,9 @@ __all__ = [
     "argmax_rows",
     "attention_tile_shape",
     "embedding",
+    "interleave_gate_up",
     "linear",
+    "linear_swiglu",
     "paged_attention",
     "presence_penalty",
     "qk_norm_rope_store",
@@ -22,4 +24,5 @@ __all__ = [
     "rotary",
     "sample_rows",
     "silu_mul",
+    "swiglu_fusable",
 ]

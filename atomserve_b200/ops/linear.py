@@ -64,23 +64,46 @@ def gemm_workspace(device: torch.device, floats: int) -> torch.Tensor:
     return buf
 
 
-def gemm_tcgen05(x: torch.Tensor, w: torch.Tensor, residual: torch.Tensor | None, out_dtype: torch.dtype) -> torch.Tensor:
-    """bfloat16 x [M, K] . w [N, K]^T on tcgen05 tensor cores (TMA operands, TMEM accumulator)."""
+def gemm_tcgen05(x: torch.Tensor, w: torch.Tensor, residual: torch.Tensor | None, out_dtype: torch.dtype,
+                 swiglu: bool = False) -> torch.Tensor:  # fmt: skip
+    """bfloat16 x [M, K] . w [N, K]^T on tcgen05 tensor cores (TMA operands, TMEM accumulator).
+    swiglu: the rows of w alternate gate and up; returns silu(gate) * up, [M, N / 2]."""
     import ctypes
 
     M, K = x.shape
     N = w.shape[0]
-    out = torch.empty(M, N, device=x.device, dtype=out_dtype)
+    out = torch.empty(M, N // 2 if swiglu else N, device=x.device, dtype=out_dtype)
     lib().asb_gemm_tcgen05_workspace.restype = ctypes.c_longlong
     need = lib().asb_gemm_tcgen05_workspace(M, N, K, None)
     workspace = gemm_workspace(x.device, need) if need else None
-    check(lib().asb_gemm_tcgen05(ptr(out), ptr(x), ptr(w), ptr(residual), M, N, K, int(out_dtype == torch.float32),
+    check(lib().asb_gemm_tcgen05(ptr(out), ptr(x), ptr(w), ptr(residual), M, N, K, 2 if swiglu else int(out_dtype == torch.float32),
                                  ptr(workspace), ptr(gemm_status(x.device)), stream()))  # fmt: skip
     return out
 
 
 def tcgen05_supported(x: torch.Tensor, w: torch.Tensor) -> bool:
     return x.dtype == torch.bfloat16 and x.shape[1] % 8 == 0 and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0
+
+
+def interleave_gate_up(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
+    """[I, K] gate and up matrices as one [2I, K] matrix whose rows alternate gate_i, up_i: the
+    layout `linear_swiglu` multiplies with, so that a (gate, up) pair lands in one output tile."""
+    return torch.stack([gate, up], dim=1).reshape(2 * gate.shape[0], gate.shape[1]).contiguous()
+
+
+def swiglu_fusable(w: torch.Tensor) -> bool:
+    """Whether x . w^T with this weight can run the fused SwiGLU form of the tensor-core GEMM."""
+    return BACKEND == "tcgen05" and w.dtype == torch.bfloat16 and w.shape[1] % 8 == 0 and w.data_ptr() % 16 == 0
+
+
+def linear_swiglu(x: torch.Tensor, w_interleaved: torch.Tensor) -> torch.Tensor:
+    """silu(x . gate^T) * (x . up^T) in one kernel: the products accumulate in float32 in tensor
+    memory and the activation is applied to those sums before the one rounding to bfloat16
+    (the unfused path rounds the two products first, atomserve/model.py:354-359)."""
+    require_cuda(x, w_interleaved)
+    if x.dtype != torch.bfloat16 or not swiglu_fusable(w_interleaved) or not x.is_contiguous() or x.data_ptr() % 16:
+        raise KernelLibraryError("linear_swiglu takes contiguous bfloat16 operands with K a multiple of 8")
+    return gemm_tcgen05(x, w_interleaved, None, torch.bfloat16, swiglu=True)
 
 
 def linear(

@@ -14,6 +14,7 @@ class SwiGLU(FeedForward):
     def __init__(self, hidden_size: int, prefix: str, intermediate_size: int):
         self.hidden_size, self.prefix, self.intermediate_size = hidden_size, prefix, intermediate_size
         self.gate_up_proj = self.down_proj = None
+        self.fused = False
 
     def tensor_specs(self) -> list[TensorSpec]:
         p, d, i = self.prefix, self.hidden_size, self.intermediate_size
@@ -25,12 +26,21 @@ class SwiGLU(FeedForward):
 
     def load(self, tensors: dict[str, torch.Tensor]) -> None:
         p = self.prefix
-        # gate rows first, then up rows (atomserve/loader.py:121)
-        self.gate_up_proj = torch.cat([tensors[p + "gate_proj.weight"], tensors[p + "up_proj.weight"]]).contiguous()
+        gate, up = tensors[p + "gate_proj.weight"], tensors[p + "up_proj.weight"]
+        self.fused = gate.is_cuda and ops.swiglu_fusable(gate)
+        if self.fused:
+            # rows alternate gate_i, up_i: the tensor-core GEMM applies SiLU * up in its epilogue
+            self.gate_up_proj = ops.interleave_gate_up(gate, up)
+        else:
+            # gate rows first, then up rows (atomserve/loader.py:121)
+            self.gate_up_proj = torch.cat([gate, up]).contiguous()
         self.down_proj = tensors[p + "down_proj.weight"]
 
     def forward(self, h: torch.Tensor, residual: torch.Tensor, ctx: StepContext) -> torch.Tensor:
-        hidden = ops.silu_mul(ops.linear(h, self.gate_up_proj))
+        if self.fused:
+            hidden = ops.linear_swiglu(h, self.gate_up_proj)
+        else:
+            hidden = ops.silu_mul(ops.linear(h, self.gate_up_proj))
         return ops.linear(hidden, self.down_proj, residual)
 
 

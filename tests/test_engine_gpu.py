@@ -388,7 +388,11 @@ def test_full_width_layers_bfloat16_against_float32():
             reference = random_model(config, seed=3, dtype="bfloat16", device="cuda")
             for blk, ref in zip(model.blocks, reference.blocks):
                 blk.mixer.qkv_proj, blk.mixer.o_proj = ref.mixer.qkv_proj.float(), ref.mixer.o_proj.float()
-                blk.feed_forward.gate_up_proj, blk.feed_forward.down_proj = ref.feed_forward.gate_up_proj.float(), ref.feed_forward.down_proj.float()
+                gate_up = ref.feed_forward.gate_up_proj.float()
+                if ref.feed_forward.fused:  # rows alternate gate, up there; the float32 path stacks them
+                    pairs = gate_up.view(-1, 2, gate_up.shape[1])
+                    gate_up = torch.cat([pairs[:, 0], pairs[:, 1]]).contiguous()
+                blk.feed_forward.gate_up_proj, blk.feed_forward.down_proj = gate_up, ref.feed_forward.down_proj.float()
             model.embedding.table, model.head.weight = reference.embedding.table.float(), reference.head.weight.float()
             del reference
         runs = {}

@@ -411,3 +411,23 @@ def test_prefill_attention_tcgen05(ops, case):
     check_gemm_status()
     assert torch.allclose(results["tcgen05"], ref, atol=2e-2, rtol=2e-2), float((results["tcgen05"] - ref).abs().max())
     assert torch.allclose(results["mma"], ref, atol=2e-2, rtol=2e-2)
+
+
+@pytest.mark.parametrize("M,I,K", [(1, 64, 64), (5, 200, 72), (16, 1024, 512), (40, 352, 256), (64, 12288, 4096),
+                                   (100, 176, 80), (300, 704, 256), (2048, 512, 512)])  # fmt: skip
+def test_gemm_tcgen05_swiglu(ops, M, I, K):
+    """silu(x gate^T) * (x up^T) from the GEMM's own epilogue (and, where K is cut, from the
+    reduction of its partial sums) against float64."""
+    from atomserve_b200.ops.linear import check_gemm_status
+
+    g = torch.Generator().manual_seed(M + I + K)
+    x = torch.randn(M, K, generator=g).bfloat16().cuda()
+    gate = (torch.randn(I, K, generator=g) / math.sqrt(K) * 2).bfloat16().cuda()
+    up = (torch.randn(I, K, generator=g) / math.sqrt(K) * 2).bfloat16().cuda()
+    w = ops.interleave_gate_up(gate, up)
+    assert torch.equal(w[0::2], gate) and torch.equal(w[1::2], up)
+    out = ops.linear_swiglu(x, w)
+    check_gemm_status()
+    gs, us = x.double().cpu() @ gate.double().cpu().T, x.double().cpu() @ up.double().cpu().T
+    ref = gs / (1 + torch.exp(-gs)) * us
+    assert out.shape == (M, I) and torch.allclose(out.double().cpu(), ref, atol=2e-2, rtol=2e-2)
