@@ -243,5 +243,5 @@ def create_engine(
         model.cache_requirements(), engine_config.block_size, engine_config.num_blocks,
         engine_config.max_num_seqs, model.dtype, model.device,
     )  # fmt: skip
-    runner = ModelRunner(model, cache, engine_config.max_num_batched_tokens, engine_config.cuda_graphs)
+    runner = ModelRunner(model, cache, engine_config.cuda_graphs)
     return Engine(runner, Scheduler(engine_config, cache, eos_token_ids), Sampler(model.device, sampler_seed))

@@ -63,8 +63,7 @@ class _Packed:
 
 
 class ModelRunner:
-    def __init__(self, model: DecoderModel, cache: CacheManager, max_batched_tokens: int = 8192,
-                 cuda_graphs: bool = True):  # fmt: skip
+    def __init__(self, model: DecoderModel, cache: CacheManager, cuda_graphs: bool = True):
         self.model, self.cache = model, cache
         self.device = model.device
         self.block_size = cache.block_size
@@ -78,7 +77,7 @@ class ModelRunner:
         self._tables: dict[int, tuple[int, list[np.ndarray]]] = {}
         self._host: torch.Tensor | None = None
         self._dev: torch.Tensor | None = None
-        self.num_launches_hint = 0
+        self.last_upload_bytes = 0  # size of the last step's packed host-to-device copy
 
     # ---- building the batch ---------------------------------------------------------------------
 
@@ -203,6 +202,7 @@ class ModelRunner:
                 tables[real:] = 0
                 slots[flat : flat + pad] = -1
         dev[: lay.size].copy_(host[: lay.size], non_blocking=True)
+        self.last_upload_bytes = lay.size * 4
         if self.device.type == "cuda":
             self._copy_done = torch.cuda.Event()
             self._copy_done.record()

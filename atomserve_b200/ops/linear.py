@@ -11,6 +11,7 @@ accumulator, so logits are never rounded to bfloat16.
 
 from __future__ import annotations
 
+import ctypes
 import os
 
 import torch
@@ -64,17 +65,21 @@ def gemm_workspace(device: torch.device, floats: int) -> torch.Tensor:
     return buf
 
 
+_WORKSPACE_FLOATS: dict[tuple[int, int, int], int] = {}
+
+
 def gemm_tcgen05(x: torch.Tensor, w: torch.Tensor, residual: torch.Tensor | None, out_dtype: torch.dtype,
                  swiglu: bool = False) -> torch.Tensor:  # fmt: skip
     """bfloat16 x [M, K] . w [N, K]^T on tcgen05 tensor cores (TMA operands, TMEM accumulator).
     swiglu: the rows of w alternate gate and up; returns silu(gate) * up, [M, N / 2]."""
-    import ctypes
-
     M, K = x.shape
     N = w.shape[0]
     out = torch.empty(M, N // 2 if swiglu else N, device=x.device, dtype=out_dtype)
-    lib().asb_gemm_tcgen05_workspace.restype = ctypes.c_longlong
-    need = lib().asb_gemm_tcgen05_workspace(M, N, K, None)
+    need = _WORKSPACE_FLOATS.get((M, N, K))
+    if need is None:
+        query = lib().asb_gemm_tcgen05_workspace
+        query.restype = ctypes.c_longlong
+        need = _WORKSPACE_FLOATS[(M, N, K)] = query(M, N, K, None)
     workspace = gemm_workspace(x.device, need) if need else None
     check(lib().asb_gemm_tcgen05(ptr(out), ptr(x), ptr(w), ptr(residual), M, N, K, 2 if swiglu else int(out_dtype == torch.float32),
                                  ptr(workspace), ptr(gemm_status(x.device)), stream()))  # fmt: skip

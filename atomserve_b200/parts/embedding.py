@@ -27,12 +27,6 @@ class TokenEmbedding(Part):
     def forward(self, token_ids: torch.Tensor) -> torch.Tensor:
         return ops.embedding(token_ids, self.table, self.status)
 
-    def check_ids(self) -> None:
-        """Raise if any id given since the last check lay outside the table (one device read)."""
-        if int(self.status.item()):
-            self.status.zero_()
-            raise ValueError(f"a token id outside [0, {self.vocab_size}) was given to the model")
-
 
 class LMHead(Part):
     def __init__(self, hidden_size: int, prefix: str, vocab_size: int, tied: bool):

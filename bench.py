@@ -187,11 +187,12 @@ def time_decode(engine, batch: int, steps: int, warmup: int):
     torch.cuda.synchronize()
     e2e_s = time.perf_counter() - t0
     e2e_tokens = engine.num_generated_tokens - before
+    upload_bytes = runner.last_upload_bytes  # the packed int32 buffer of a decode step
     while engine.step():
         pass
     for h in handles:
         list(h)
-    return device_ms, launches, mid_context, e2e_tokens / e2e_s
+    return device_ms, launches, mid_context, e2e_tokens / e2e_s, upload_bytes
 
 
 def time_prefill(engine, steps: int, warmup: int) -> float:
@@ -303,7 +304,7 @@ def main() -> int:
         return 0
     config, model, engine = build_engine(args.layers, max_seqs=64)
     if args.only == "decode":
-        ms, launches, ctx, e2e = time_decode(engine, args.batch, args.steps, warmup)
+        ms, launches, ctx, e2e, _ = time_decode(engine, args.batch, args.steps, warmup)
         print(json.dumps({"only": "decode", "batch": args.batch, "layers": args.layers, "ms_per_step": round(ms, 4),
                           "e2e_tokens_per_s": round(e2e, 1), "gpu_launches": launches}))  # fmt: skip
         return 0
@@ -312,10 +313,10 @@ def main() -> int:
         print(json.dumps({"only": "prefill", "layers": args.layers, "tokens": PROMPT_TOKENS, "ms": round(ms, 3)}))
         return 0
     with ClockSampler() as clocks:
-        device_ms, launches, ctx, e2e = time_decode(engine, args.batch, args.steps, warmup)
+        device_ms, launches, ctx, e2e, upload_bytes = time_decode(engine, args.batch, args.steps, warmup)
     points = {}
     for b in (1, 64):
-        ms, _, _, e = time_decode(engine, b, max(args.steps // 2, 8), 3)
+        ms, _, _, e, _ = time_decode(engine, b, max(args.steps // 2, 8), 3)
         points[f"decode_b{b}"] = round(b * 1000.0 / ms, 1)
         points[f"decode_b{b}_e2e"] = round(e, 1)
     prefill_ms = time_prefill(engine, steps=5, warmup=3)
@@ -343,7 +344,7 @@ def main() -> int:
             "global_batch": args.batch, "seq_len": CONTEXT, "prompt_tokens": PROMPT_TOKENS, "block_size": BLOCK_SIZE,
             "parallelism": "single-gpu", "l2": "weights read per step exceed L2; no flush needed", "sampling": "greedy",
         },
-        "e2e": {"value": round(e2e, 1), "unit": "tokens/s", "h2d_bytes_per_step": 4 * (6 * args.batch + 8 + 2 * args.batch * (CONTEXT // BLOCK_SIZE)),
+        "e2e": {"value": round(e2e, 1), "unit": "tokens/s", "h2d_bytes_per_step": upload_bytes,
                 "d2h_bytes_per_step": 4 * args.batch},
         "gpu_launches": launches * 1,
         "prefill": {"value": round(PROMPT_TOKENS * 1000.0 / prefill_ms, 1), "tokens": PROMPT_TOKENS, "ms": round(prefill_ms, 3),
