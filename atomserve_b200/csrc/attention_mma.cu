@@ -95,23 +95,36 @@ __device__ __forceinline__ uint32_t tile_offset(int row, int chunk) {
 }
 
 // Copy keys [kt0, kt0 + 64) of one kv head into a tile; rows outside [key_lo, key_hi) are zero.
+// A thread copies one 16-byte chunk column of a run of consecutive keys, so that when a run lies
+// inside one page (pages of at least that many tokens, a power of two) it looks the page up once.
 template <int HD, int NT = kThreads>
 __device__ __forceinline__ void load_kv_tile(uint32_t k_tile, uint32_t v_tile, const MmaParams& p,
                                              const int* table, int kvh, int kt0, int key_lo, int key_hi) {
-  constexpr int kChunks = HD / 8;              // 16-byte chunks per row
-  constexpr int kRowsPerPass = NT / kChunks;   // rows covered by one pass of the block
+  constexpr int kChunks = HD / 8;                        // 16-byte chunks per row
+  constexpr int kRun = kKeyTile / (NT / kChunks);        // consecutive keys per thread
   const int chunk = threadIdx.x % kChunks;
-  const int row0 = threadIdx.x / kChunks;
+  const int run0 = (threadIdx.x / kChunks) * kRun;
+  const int j0 = kt0 + run0;
+  const bool one_page = p.bs >= kRun && (p.bs & (p.bs - 1)) == 0;
+  size_t page_at = 0;
+  if (one_page && j0 < key_hi && j0 + kRun > key_lo) {
+    const int blk = table[j0 / p.bs];
+    page_at = (((size_t)blk * p.KV + kvh) * p.bs + (j0 & (p.bs - 1))) * HD + chunk * 8;
+  }
 #pragma unroll
-  for (int r = row0; r < kKeyTile; r += kRowsPerPass) {
-    const int j = kt0 + r;
+  for (int i = 0; i < kRun; ++i) {
+    const int j = j0 + i;
     const bool valid = j >= key_lo && j < key_hi;
     size_t at = 0;
     if (valid) {
-      const int blk = table[j / p.bs];
-      at = (((size_t)blk * p.KV + kvh) * p.bs + (j % p.bs)) * HD + chunk * 8;
+      if (one_page) {
+        at = page_at + (size_t)i * HD;
+      } else {
+        const int blk = table[j / p.bs];
+        at = (((size_t)blk * p.KV + kvh) * p.bs + (j % p.bs)) * HD + chunk * 8;
+      }
     }
-    const uint32_t off = tile_offset<HD>(r, chunk);
+    const uint32_t off = tile_offset<HD>(run0 + i, chunk);
     cp_async16(k_tile + off, p.k_cache + at, valid);
     cp_async16(v_tile + off, p.v_cache + at, valid);
   }
