@@ -12,7 +12,7 @@ from atomserve_b200.ops.library import KernelLibraryError, check, dtype_code, li
 KEY_TILE = 32
 TARGET_BLOCKS = 296  # two blocks for each of the 148 SMs before the key range is split
 SHORT_ROWS = 8  # requests with at most this many new tokens run row by row in the decode kernel
-DECODE_TARGET_BLOCKS = 592  # four resident decode blocks per SM keep the HBM stream busy
+DECODE_TARGET_BLOCKS = 8 * 3 * 148  # eight waves of three resident blocks per SM: a ragged last wave costs little
 
 
 # Which kernel serves prompt portions in bfloat16 with head size 128: "tcgen05" (scores and output
@@ -49,7 +49,8 @@ def plan_partitions(num_tokens: int, num_requests: int, num_kv_heads: int, group
 
 def plan_decode_partitions(rows: int, num_kv_heads: int, group: int, max_context: int, window: int) -> tuple[int, int]:
     """(partition size, partitions) for the tensor-core decode kernel: one block per (row, kv
-    head, partition); keys are split until the GPU is full, never below 256 keys a block."""
+    head, partition); keys are split until there are several waves of blocks (the last, partly
+    filled wave then wastes little), never below 256 keys a block."""
     blocks = rows * num_kv_heads * -(-group // 16)
     span = max_context if window <= 0 else min(max_context, window)
     if blocks >= DECODE_TARGET_BLOCKS or span <= 256:
