@@ -1,4 +1,6 @@
 // Error text of the last refused call on this thread, and the library's identity.
+#include <mutex>
+
 #include "common.cuh"
 
 namespace asb {
@@ -20,6 +22,17 @@ int check_launch(const char* what) {
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return fail("%s: %s", what, cudaGetErrorString(e));
   return 0;
+}
+
+void prefer_shared_carveout(const void* kernel) {
+  static std::mutex lock;
+  static const void* done[128];
+  static int count = 0;
+  std::lock_guard<std::mutex> guard(lock);
+  for (int i = 0; i < count; ++i)
+    if (done[i] == kernel) return;
+  if (count < 128) done[count++] = kernel;
+  cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
 }
 
 static bool g_pdl = false;

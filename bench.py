@@ -27,6 +27,11 @@ QWEN3_8B = dict(
     num_hidden_layers=36, num_attention_heads=32, num_key_value_heads=8, head_dim=128,
     rms_norm_eps=1e-6, rope_theta=1000000.0, tie_word_embeddings=False, max_position_embeddings=40960,
 )  # fmt: skip
+# the other two shapes that the reference's benchmark list names (its bench/engine.py runs whatever
+# checkpoint it is given); `--shape` picks one for the --only runs
+QWEN3_14B = {**QWEN3_8B, "hidden_size": 5120, "intermediate_size": 17408, "num_hidden_layers": 40, "num_attention_heads": 40}
+QWEN3_32B = {**QWEN3_8B, "hidden_size": 5120, "intermediate_size": 25600, "num_hidden_layers": 64, "num_attention_heads": 64}
+SHAPES = {"8b": QWEN3_8B, "14b": QWEN3_14B, "32b": QWEN3_32B}
 PROMPT_TOKENS = 2048
 CONTEXT = 4096
 BLOCK_SIZE = 16
@@ -88,7 +93,7 @@ class ClockSampler:
         return {"sm_mhz": sm[len(sm) // 2], "sm_max_mhz": int(rows[0][1]), "reasons": reasons, "samples": len(rows)}
 
 
-def build_engine(layers: int, max_seqs: int):
+def build_engine(layers: int, max_seqs: int, shape: dict = QWEN3_8B, context: int = CONTEXT, budget: int = PROMPT_TOKENS):
     import torch
 
     from atomserve_b200.config import EngineConfig
@@ -96,11 +101,11 @@ def build_engine(layers: int, max_seqs: int):
     from atomserve_b200.engine.engine import create_engine
     from atomserve_b200.weights import random_model
 
-    _, config = config_from_dict({**QWEN3_8B, "num_hidden_layers": layers})
+    _, config = config_from_dict({**shape, "num_hidden_layers": layers})
     model = random_model(config, seed=0, dtype="bfloat16", device="cuda")
-    blocks = max_seqs * (CONTEXT // BLOCK_SIZE) + 64
+    blocks = max_seqs * (context // BLOCK_SIZE) + 64
     engine_config = EngineConfig(block_size=BLOCK_SIZE, num_blocks=blocks, max_num_seqs=max_seqs,
-                                 max_num_batched_tokens=PROMPT_TOKENS, max_model_len=CONTEXT,
+                                 max_num_batched_tokens=budget, max_model_len=context,
                                  enable_prefix_caching=False)  # fmt: skip
     torch.cuda.synchronize()
     return config, model, create_engine(model, engine_config, sampler_seed=0)
@@ -126,9 +131,10 @@ def prefill_flops(config, tokens: int) -> float:
     return linear + attention
 
 
-def time_decode(engine, batch: int, steps: int, warmup: int):
+def time_decode(engine, batch: int, steps: int, warmup: int, prompt_tokens: int = PROMPT_TOKENS):
     """Prefill `batch` requests (untimed), then time `steps` decode steps two ways: on the
     device around the step function plus argmax, and end to end through Engine.step()."""
+    PROMPT_TOKENS = prompt_tokens
     import torch
 
     from atomserve_b200 import ops
@@ -193,6 +199,43 @@ def time_decode(engine, batch: int, steps: int, warmup: int):
     for h in handles:
         list(h)
     return device_ms, launches, mid_context, e2e_tokens / e2e_s, upload_bytes
+
+
+def time_serving(engine, requests: int, decode_tokens: int, seed: int = 0) -> dict:
+    """A mixed load through the public API: `requests` prompts of 128 to 2,048 synthetic ids
+    submitted at once, `decode_tokens` greedy tokens each; the scheduler cuts the prompts into
+    portions under its token budget beside the running decodes. Wall-clock time, host to host."""
+    import random
+
+    import torch
+
+    from atomserve_b200.engine.sequence import SamplingParams
+
+    rng = random.Random(seed)
+    lengths = [rng.randint(128, 2048) for _ in range(requests)]
+    batch = [[(1000 + 37 * b + i) % 150000 for i in range(n)] for b, n in enumerate(lengths)]
+    params = SamplingParams(temperature=0.0, max_tokens=decode_tokens, ignore_eos=True)
+    engine.generate(batch[:2], SamplingParams(temperature=0.0, max_tokens=4, ignore_eos=True))  # warm-up: builds, graphs
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    handles = [engine.submit(p, params) for p in batch]
+    kinds = {"decode": [0, 0.0], "mixed": [0, 0.0]}  # steps and seconds, by whether a prompt portion was in the step
+    last = time.perf_counter()
+    while engine.step():  # what Engine.generate does, with a clock read per step (the step ends with a device-to-host read)
+        now = time.perf_counter()
+        kind = kinds["decode" if engine.last_batch_tokens == engine.last_batch_seqs else "mixed"]
+        kind[0] += 1
+        kind[1] += now - last
+        last = now
+    outputs = [list(h) for h in handles]
+    torch.cuda.synchronize()
+    seconds = time.perf_counter() - t0
+    generated = sum(len(o) for o in outputs)
+    return {"requests": requests, "prompt_tokens": sum(lengths), "generated_tokens": generated, "seconds": round(seconds, 3),
+            "generated_tokens_per_s": round(generated / seconds, 1),
+            "total_tokens_per_s": round((generated + sum(lengths)) / seconds, 1),
+            "decode_steps": kinds["decode"][0], "decode_step_ms": round(1e3 * kinds["decode"][1] / max(kinds["decode"][0], 1), 3),
+            "mixed_steps": kinds["mixed"][0], "mixed_step_ms": round(1e3 * kinds["mixed"][1] / max(kinds["mixed"][0], 1), 3)}  # fmt: skip
 
 
 def time_prefill(engine, steps: int, warmup: int) -> float:
@@ -279,10 +322,16 @@ def main() -> int:
                         help="fewer layers than the model has (same layer sizes), where time or memory needs it")  # fmt: skip
     parser.add_argument("--batch", type=int, default=8)
     parser.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    parser.add_argument("--only", choices=["decode", "prefill", "gemm"], help="time just this (for profiling small cases)")
+    parser.add_argument("--only", choices=["decode", "prefill", "gemm", "serve"], help="time just this (for profiling small cases and the other shapes)")
+    parser.add_argument("--shape", default="8b", choices=sorted(SHAPES), help="with --only decode/prefill/serve: layer sizes of Qwen3-8B, -14B or -32B")
+    parser.add_argument("--context", type=int, default=PROMPT_TOKENS, help="with --only decode: tokens each request holds when decoding starts")
+    parser.add_argument("--requests", type=int, default=32, help="with --only serve: requests submitted at once")
+    parser.add_argument("--decode-tokens", type=int, default=256, help="with --only serve: tokens generated per request")
+    parser.add_argument("--budget", type=int, default=512, help="with --only serve: the scheduler's token budget per step")
     parser.add_argument("--gemm-shape", default="all", help="with --only gemm: qkv, o, gate_up, down, lm_head or all")
     parser.add_argument("--gemm-tokens", default="1,8,64,2048", help="with --only gemm: token counts, comma-separated")
     args = parser.parse_args()
+    args.layers_given = any(a == "--layers" or a.startswith("--layers=") for a in sys.argv[1:])
     if args.impl == "reference":
         print(json.dumps({"impl": "reference", "unavailable":
                           "the reference runs on Apple MPS or CPU only (no CUDA path) and does not install here: "
@@ -302,15 +351,30 @@ def main() -> int:
     if args.only == "gemm":
         time_gemms(args.gemm_shape, [int(t) for t in args.gemm_tokens.split(",")], max(args.steps // 4, 4))
         return 0
-    config, model, engine = build_engine(args.layers, max_seqs=64)
-    if args.only == "decode":
-        ms, launches, ctx, e2e, _ = time_decode(engine, args.batch, args.steps, warmup)
-        print(json.dumps({"only": "decode", "batch": args.batch, "layers": args.layers, "ms_per_step": round(ms, 4),
-                          "e2e_tokens_per_s": round(e2e, 1), "gpu_launches": launches}))  # fmt: skip
+    shape = SHAPES[args.shape]
+    layers = args.layers if args.layers_given else shape["num_hidden_layers"]
+    if args.only == "serve":
+        config, model, engine = build_engine(layers, max_seqs=args.requests, shape=shape,
+                                             context=2048 + args.decode_tokens + BLOCK_SIZE, budget=args.budget)  # fmt: skip
+        result = time_serving(engine, args.requests, args.decode_tokens)
+        print(json.dumps({"only": "serve", "shape": args.shape, "layers": layers, "layers_full": shape["num_hidden_layers"],
+                          "budget": args.budget, **result}))  # fmt: skip
         return 0
+    if args.only == "decode":
+        context = args.context + warmup + args.steps + args.batch + 64
+        config, model, engine = build_engine(layers, max_seqs=max(args.batch, 8), shape=shape,
+                                             context=-(-context // BLOCK_SIZE) * BLOCK_SIZE, budget=max(args.context, PROMPT_TOKENS))  # fmt: skip
+        ms, launches, ctx, e2e, _ = time_decode(engine, args.batch, args.steps, warmup, args.context)
+        gbs = step_bytes(config, args.batch, ctx) / (ms * 1e-3) / 1e9
+        print(json.dumps({"only": "decode", "shape": args.shape, "batch": args.batch, "layers": layers,
+                          "layers_full": shape["num_hidden_layers"], "context": ctx, "ms_per_step": round(ms, 4),
+                          "tokens_per_s": round(args.batch * 1000.0 / ms, 1), "e2e_tokens_per_s": round(e2e, 1),
+                          "gbs": round(gbs, 1), "hbm_frac": round(gbs / pk["hbm_gbs"], 4), "gpu_launches": launches}))  # fmt: skip
+        return 0
+    config, model, engine = build_engine(layers, max_seqs=64, shape=shape)
     if args.only == "prefill":
         ms = time_prefill(engine, steps=args.steps, warmup=warmup)
-        print(json.dumps({"only": "prefill", "layers": args.layers, "tokens": PROMPT_TOKENS, "ms": round(ms, 3)}))
+        print(json.dumps({"only": "prefill", "layers": layers, "tokens": PROMPT_TOKENS, "ms": round(ms, 3)}))
         return 0
     with ClockSampler() as clocks:
         device_ms, launches, ctx, e2e, upload_bytes = time_decode(engine, args.batch, args.steps, warmup)
@@ -338,7 +402,7 @@ def main() -> int:
         "dtype": "bf16",
         "data": "synthetic token ids, random-init weights N(0, 0.02)",
         "config": {
-            "model": "Qwen3-8B shape", "layers": args.layers, "layers_full": QWEN3_8B["num_hidden_layers"],
+            "model": "Qwen3-8B shape", "layers": layers, "layers_full": QWEN3_8B["num_hidden_layers"],
             "hidden": config.hidden_size, "heads": config.num_attention_heads, "kv_heads": config.num_key_value_heads,
             "head_dim": config.head_dim, "intermediate": config.intermediate_size, "vocab": config.vocab_size,
             "global_batch": args.batch, "seq_len": CONTEXT, "prompt_tokens": PROMPT_TOKENS, "block_size": BLOCK_SIZE,
@@ -354,9 +418,9 @@ def main() -> int:
         "points": points,
         "clocks": clocks.summary(),
     }  # fmt: skip
-    if args.layers == QWEN3_8B["num_hidden_layers"] and args.batch == 1:
+    if layers == QWEN3_8B["num_hidden_layers"] and args.batch == 1:
         line["vs_baseline"] = round(value / PUBLISHED_8B_BATCH1, 2)
-    elif "decode_b1" in points and args.layers == QWEN3_8B["num_hidden_layers"]:
+    elif "decode_b1" in points and layers == QWEN3_8B["num_hidden_layers"]:
         line["vs_baseline"] = round(points["decode_b1"] / PUBLISHED_8B_BATCH1, 2)
         line["vs_baseline_note"] = "decode_b1 over the reference's published Qwen3-8B batch-1 15.7 tok/s (M4 Pro)"
     print(json.dumps(line))
