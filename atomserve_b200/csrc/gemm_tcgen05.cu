@@ -33,8 +33,12 @@
 #include <cuda.h>
 
 #include "common.cuh"
+#include "gemm_partials.cuh"
 
 namespace {
+
+using asb::block_of;
+using asb::range_begin;
 
 constexpr int kThreads = 192;
 constexpr int BM = 128;   // P rows per tile = TMEM lanes
@@ -42,7 +46,7 @@ constexpr int BK = 64;    // K elements per stage: 128 bytes, one swizzle atom
 constexpr int UMMA_K = 16;
 constexpr uint32_t kMaxPolls = 1u << 24;
 
-enum Epilogue : int { kStoreBf16 = 0, kStoreBf16Residual = 1, kStoreF32 = 2, kStoreSwiGLU = 4 };
+enum Epilogue : int { kStoreBf16 = 0, kStoreBf16Residual = 1, kStoreF32 = 2, kStoreSwiGLU = 4, kPartialsOnly = 8 };
 
 struct GemmParams {
   void* out;             // bf16 or f32 [M, N]
@@ -52,26 +56,13 @@ struct GemmParams {
   int p_rows, q_rows;    // rows of P and Q (M and N, or N and M when swapped)
   int ldo;               // row stride of out (N)
   int swap;              // 1: P = w (lanes are output columns), Q = x
-  int epilogue;          // kStoreBf16 / kStoreBf16Residual / kStoreF32 / kStoreSwiGLU (out is [M, N / 2])
+  int epilogue;          // kStoreBf16 / kStoreBf16Residual / kStoreF32 / kStoreSwiGLU (out is [M, N / 2]) /
+                         // kPartialsOnly (every segment leaves its sums in a workspace slot; no out)
   int tiles_p, num_tiles;  // tile t -> (t % tiles_p, t / tiles_p)
   int kb_per_tile;       // K blocks of BK per tile
   int stream;            // 0: whole tiles round-robin; 1: equal contiguous ranges of K blocks
   int max_slots;         // workspace slots per tile
 };
-
-// First flattened K block of block c's range when `total` K blocks are cut into `parts` ranges.
-__host__ __device__ __forceinline__ long long range_begin(long long total, int parts, int c) {
-  return total * c / parts;
-}
-
-// The block whose range holds flattened K block `pos` (the largest c with range_begin(c) <= pos).
-__host__ __device__ __forceinline__ int block_of(long long total, int parts, long long pos) {
-  int c = (int)(pos * parts / total);
-  if (c >= parts) c = parts - 1;
-  while (c + 1 < parts && range_begin(total, parts, c + 1) <= pos) ++c;
-  while (c > 0 && range_begin(total, parts, c) > pos) --c;
-  return c;
-}
 
 // Walks the segments of one block: the same sequence in every warp role.
 struct SegmentWalk {
@@ -317,7 +308,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_cons
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       const int p0 = (walk.tile % p.tiles_p) * BM, q0 = (walk.tile / p.tiles_p) * BN;
       const int prow = p0 + quad * 32 + lane;
-      const bool whole = walk.kb0 == 0 && walk.kb1 == p.kb_per_tile;
+      const bool whole = walk.kb0 == 0 && walk.kb1 == p.kb_per_tile && p.epilogue != kPartialsOnly;
       float* slot = nullptr;
       if (!whole) {
         const long long total = (long long)p.num_tiles * p.kb_per_tile;
@@ -460,22 +451,28 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_cons
 // consecutive elements along the output's contiguous dimension. Tiles stored whole are skipped.
 template <int BN>
 __global__ void segment_reduce_kernel(const GemmParams p, int parts) {
-  asb::pdl_wait();  // the stream's previous kernel has completed (programmatic dependent launch)
-  asb::pdl_launch_dependents();
+  // the index arithmetic needs nothing from the GEMM: it runs while the GEMM drains
   const int tile = blockIdx.x;
   const long long total = (long long)p.num_tiles * p.kb_per_tile;
   const long long begin = (long long)tile * p.kb_per_tile;
   const int first = block_of(total, parts, begin), last = block_of(total, parts, begin + p.kb_per_tile - 1);
   const int slots = last - first + 1;
-  if (slots == 1) return;  // one block covered all of K and stored the tile itself
   const int p0 = (tile % p.tiles_p) * BM, q0 = (tile / p.tiles_p) * BN;
   const float* ws = p.workspace + (size_t)tile * p.max_slots * BM * BN;
   const int i = (blockIdx.y * blockDim.x + threadIdx.x) * 4;
+  asb::pdl_wait();  // the GEMM has completed (programmatic dependent launch)
+  asb::pdl_launch_dependents();
+  if (slots == 1) return;  // one block covered all of K and stored the tile itself
   if (i >= BM * BN) return;
   float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-  for (int s = 0; s < slots; ++s) {
-    const float4 a = *reinterpret_cast<const float4*>(ws + (size_t)s * BM * BN + i);
-    v.x += a.x; v.y += a.y; v.z += a.z; v.w += a.w;
+  for (int s0 = 0; s0 < slots; s0 += 4) {  // four loads in flight; the sum still runs in slot order
+    float4 a[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u)
+      if (s0 + u < slots) a[u] = *reinterpret_cast<const float4*>(ws + (size_t)(s0 + u) * BM * BN + i);
+#pragma unroll
+    for (int u = 0; u < 4; ++u)
+      if (s0 + u < slots) { v.x += a[u].x; v.y += a[u].y; v.z += a[u].z; v.w += a[u].w; }
   }
   const float e[4] = {v.x, v.y, v.z, v.w};
   if (p.epilogue == kStoreSwiGLU) {
@@ -601,7 +598,7 @@ int launch(const CUtensorMap& mp, const CUtensorMap& mq, const GemmParams& p, co
   if (e != cudaSuccess) return asb::fail("gemm_tcgen05: shared memory %d: %s", Config<BN>::kSmem, cudaGetErrorString(e));
   asb::launch(kern, pl.blocks, kThreads, Config<BN>::kSmem, stream, mp, mq, p);
   if (int rc = asb::check_launch("gemm_tcgen05")) return rc;
-  if (pl.stream) {
+  if (pl.stream && p.epilogue != kPartialsOnly) {
     asb::launch(segment_reduce_kernel<BN>, dim3(p.num_tiles, (BM * BN / 4 + 255) / 256), 256, 0, stream, p, pl.blocks);
     return asb::check_launch("gemm_tcgen05 segment_reduce");
   }
@@ -618,18 +615,33 @@ extern "C" long long asb_gemm_tcgen05_workspace(int M, int N, int K, int* stream
   return pl.workspace;
 }
 
+// How a shape is run: out7 = {cuts K (1) or whole tiles (0), swapped operands, workspace slots per
+// tile, token columns per tile, K blocks per tile, tiles, thread blocks}. A shape that cuts K with
+// swapped operands can leave its product as partial sums (mode 3 of asb_gemm_tcgen05), which
+// csrc/gemm_partials.cuh describes.
+extern "C" int asb_gemm_tcgen05_plan(int M, int N, int K, int* out7) {
+  if (M <= 0 || N <= 0 || K <= 0) return asb::fail("gemm_tcgen05_plan: empty shape");
+  const Plan pl = make_plan(M, N, K);
+  out7[0] = pl.stream; out7[1] = pl.swap; out7[2] = pl.max_slots; out7[3] = pl.bn;
+  out7[4] = pl.kb_per_tile; out7[5] = pl.tiles_p * pl.tiles_q; out7[6] = pl.blocks;
+  return 0;
+}
+
 // out = x . w^T (+ residual). x [M, K] and w [N, K] bfloat16, contiguous, K a multiple of 8 and
 // both bases 16-byte aligned (TMA's rules). out bfloat16 [M, N], float32, or [M, N / 2] by mode.
 // workspace: float32, asb_gemm_tcgen05_workspace(M, N, K) elements (null if that is 0); calls that
 // may overlap on the GPU need separate workspaces.
 // status: one int on the device; it stays 0 unless a pipeline wait ran out.
 // mode 0: out bfloat16 (+ residual); 1: out float32; 2: SwiGLU: the rows of w alternate gate and
-// up (row 2i gate_i, row 2i + 1 up_i) and out is bfloat16 [M, N / 2] = silu(gate) * up.
+// up (row 2i gate_i, row 2i + 1 up_i) and out is bfloat16 [M, N / 2] = silu(gate) * up; 3: no out:
+// the product stays in the workspace as float32 partial sums for a consumer kernel to add up
+// (only for shapes whose plan cuts K with swapped operands, and then tiles_q is 1).
 extern "C" int asb_gemm_tcgen05(void* out, const void* x, const void* w, const void* residual, int M,
                                 int N, int K, int mode, float* workspace, int* status,
                                 cudaStream_t stream) {
   const int out_f32 = mode == 1;
-  if (mode < 0 || mode > 2) return asb::fail("gemm_tcgen05: unknown mode %d", mode);
+  if (mode < 0 || mode > 3) return asb::fail("gemm_tcgen05: unknown mode %d", mode);
+  if (mode == 3 && residual) return asb::fail("gemm_tcgen05: the partial-sum form takes no residual");
   if (mode == 2 && (residual || N % 2)) return asb::fail("gemm_tcgen05: the SwiGLU form takes no residual and an even N");
   if (M == 0 || N == 0) return 0;
   if (K < 8 || K % 8) return asb::fail("gemm_tcgen05: K = %d must be a positive multiple of 8 (16-byte TMA rows)", K);
@@ -637,6 +649,8 @@ extern "C" int asb_gemm_tcgen05(void* out, const void* x, const void* w, const v
   if (out_f32 && residual) return asb::fail("gemm_tcgen05: the float32 result form takes no residual");
   if (!status) return asb::fail("gemm_tcgen05: a status word is required");
   const Plan pl = make_plan(M, N, K);
+  if (mode == 3 && !(pl.stream && pl.swap && pl.tiles_q == 1))
+    return asb::fail("gemm_tcgen05: [%d, %d] x [%d, %d] does not run with partial sums", M, K, N, K);
   if (pl.workspace > 0 && !workspace) return asb::fail("gemm_tcgen05: this shape needs a workspace of %lld floats", pl.workspace);
 
   GemmParams p;
@@ -648,7 +662,7 @@ extern "C" int asb_gemm_tcgen05(void* out, const void* x, const void* w, const v
   p.ldo = N;
   p.p_rows = pl.swap ? N : M;
   p.q_rows = pl.swap ? M : N;
-  p.epilogue = mode == 2 ? kStoreSwiGLU : (out_f32 ? kStoreF32 : (residual ? kStoreBf16Residual : kStoreBf16));
+  p.epilogue = mode == 3 ? kPartialsOnly : mode == 2 ? kStoreSwiGLU : (out_f32 ? kStoreF32 : (residual ? kStoreBf16Residual : kStoreBf16));
   p.tiles_p = pl.tiles_p;
   p.num_tiles = pl.tiles_p * pl.tiles_q;
   p.kb_per_tile = pl.kb_per_tile;

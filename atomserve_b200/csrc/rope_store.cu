@@ -13,6 +13,7 @@
 //   inv_freq     [rotary_dim/2] float32 or null (no rotation); dims >= rotary_dim pass through
 //   slots        [T] int32, or null / negative entries: nothing is stored for that token
 #include "common.cuh"
+#include "gemm_partials.cuh"
 
 namespace {
 
@@ -85,30 +86,38 @@ __global__ void qk_norm_rope_store_kernel(
 // takes kHeadsPerWarp heads of one token and computes the token's sines and cosines once: four
 // heads when there are many tokens, one when there are few (decoding), where spreading the
 // heads over more warps matters more than saving the trigonometry.
+//
+// qkv may also be given as the partial sums that the tensor-core GEMM left in its workspace
+// (ps.ws set, qkv null): each lane then adds its elements' slots up itself and rounds the sums to
+// T, as the GEMM's reduction kernel would have, which saves that kernel.
 template <typename T, int EPT, int kHeadsPerWarp>
 __global__ void qk_norm_rope_store_vec_kernel(
     T* __restrict__ q_out, T* __restrict__ k_cache, T* __restrict__ v_cache,
-    const T* __restrict__ qkv, const float* __restrict__ q_gain, const float* __restrict__ k_gain,
-    const float* __restrict__ inv_freq, const int* __restrict__ positions,
+    const T* __restrict__ qkv, const asb::PartialSums ps, const float* __restrict__ q_gain,
+    const float* __restrict__ k_gain, const float* __restrict__ inv_freq, const int* __restrict__ positions,
     const int* __restrict__ slots, int H, int KV, int block_size, float eps) {
-  asb::pdl_wait();  // the stream's previous kernel has completed (programmatic dependent launch)
-  asb::pdl_launch_dependents();
   constexpr int hd = EPT * 32;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int t = blockIdx.x;
   const int head_first = (blockIdx.y * kWarps + warp) * kHeadsPerWarp;
   const int heads = H + 2 * KV;
-  if (head_first >= heads) return;
-  const int slot = slots ? slots[t] : -1;
   const int e0 = lane * EPT;  // this lane's first element
-
+  // Positions and cache slots were uploaded before the step's first kernel, and the angles depend
+  // on nothing else: all of this overlaps the previous kernel's tail.
+  int slot = -1;
   float cs[EPT], sn[EPT];
-  if (inv_freq) {
-    const float pos = (float)positions[t];
-    const int i0 = (lane & 15) * EPT;
+  if (head_first < heads) {
+    slot = slots ? slots[t] : -1;
+    if (inv_freq) {
+      const float pos = (float)positions[t];
+      const int i0 = (lane & 15) * EPT;
 #pragma unroll
-    for (int k = 0; k < EPT; ++k) sincosf(pos * inv_freq[i0 + k], &sn[k], &cs[k]);
+      for (int k = 0; k < EPT; ++k) sincosf(pos * inv_freq[i0 + k], &sn[k], &cs[k]);
+    }
   }
+  asb::pdl_wait();  // the stream's previous kernel has completed (programmatic dependent launch)
+  asb::pdl_launch_dependents();
+  if (head_first >= heads) return;
   struct alignas(sizeof(T) * EPT > 16 ? 16 : sizeof(T) * EPT) Vec { T v[EPT]; };
 
   for (int head = head_first; head < min(head_first + kHeadsPerWarp, heads); ++head) {
@@ -123,7 +132,17 @@ __global__ void qk_norm_rope_store_vec_kernel(
       const size_t block = slot / block_size, off = slot % block_size;
       dst = (is_k ? k_cache : v_cache) + ((block * KV + kvh) * block_size + off) * (size_t)hd;
     }
-    const Vec in = *reinterpret_cast<const Vec*>(qkv + ((size_t)t * heads + head) * hd + e0);
+    Vec in;
+    if (ps.ws) {
+      const int col = head * hd + e0;
+      const int n = asb::partial_slots(ps, col / asb::kPartialRows);
+      float f[EPT];
+      asb::partial_sum<EPT>(ps, t, col, n, f);
+#pragma unroll
+      for (int k = 0; k < EPT; ++k) in.v[k] = asb::from_float<T>(f[k]);
+    } else {
+      in = *reinterpret_cast<const Vec*>(qkv + ((size_t)t * heads + head) * hd + e0);
+    }
     if (!is_q && !is_k) {
       *reinterpret_cast<Vec*>(dst + e0) = in;
       continue;
@@ -157,22 +176,29 @@ __global__ void qk_norm_rope_store_vec_kernel(
 }
 
 template <typename T, int EPT>
-void launch_vec(T* q_out, T* k_cache, T* v_cache, const T* qkv, const float* q_gain,
+void launch_vec(T* q_out, T* k_cache, T* v_cache, const T* qkv, const asb::PartialSums& ps, const float* q_gain,
                 const float* k_gain, const float* inv_freq, const int* positions, const int* slots,
                 int num_tokens, int H, int KV, int block_size, float eps, cudaStream_t stream) {
   if (num_tokens >= 256) {
     const int heads_per_block = kWarps * 4;
     dim3 grid(num_tokens, (H + 2 * KV + heads_per_block - 1) / heads_per_block);
     asb::launch(qk_norm_rope_store_vec_kernel<T, EPT, 4>, grid, kWarps * 32, 0, stream, 
-        q_out, k_cache, v_cache, qkv, q_gain, k_gain, inv_freq, positions, slots, H, KV, block_size, eps);
+        q_out, k_cache, v_cache, qkv, ps, q_gain, k_gain, inv_freq, positions, slots, H, KV, block_size, eps);
   } else {
     dim3 grid(num_tokens, (H + 2 * KV + kWarps - 1) / kWarps);
     asb::launch(qk_norm_rope_store_vec_kernel<T, EPT, 1>, grid, kWarps * 32, 0, stream, 
-        q_out, k_cache, v_cache, qkv, q_gain, k_gain, inv_freq, positions, slots, H, KV, block_size, eps);
+        q_out, k_cache, v_cache, qkv, ps, q_gain, k_gain, inv_freq, positions, slots, H, KV, block_size, eps);
   }
 }
 
 }  // namespace
+
+namespace {
+int rope_store(void* q_out, void* k_cache, void* v_cache, const void* qkv, const asb::PartialSums& ps,
+               const float* q_gain, const float* k_gain, const float* inv_freq, const int* positions,
+               const int* slots, int num_tokens, int H, int KV, int hd, int rotary_dim, int block_size,
+               float eps, int dtype, cudaStream_t stream);
+}
 
 extern "C" int asb_qk_norm_rope_store(void* q_out, void* k_cache, void* v_cache, const void* qkv,
                                       const float* q_gain, const float* k_gain,
@@ -180,6 +206,35 @@ extern "C" int asb_qk_norm_rope_store(void* q_out, void* k_cache, void* v_cache,
                                       const int* slots, int num_tokens, int H, int KV, int hd,
                                       int rotary_dim, int block_size, float eps, int dtype,
                                       cudaStream_t stream) {
+  const asb::PartialSums none = {nullptr, 0, 0, 0, 0, 0};
+  return rope_store(q_out, k_cache, v_cache, qkv, none, q_gain, k_gain, inv_freq, positions, slots, num_tokens,
+                    H, KV, hd, rotary_dim, block_size, eps, dtype, stream);
+}
+
+// The same with qkv given as the partial sums of asb_gemm_tcgen05 mode 3 on [tokens, K] x
+// [(H + 2 KV) hd, K]: bfloat16 only, head sizes 32, 64, 128, 256 with the whole head rotated.
+extern "C" int asb_qk_norm_rope_store_partial(void* q_out, void* k_cache, void* v_cache, const float* ws,
+                                              int max_slots, int bn, int kb_per_tile, int num_tiles, int blocks,
+                                              const float* q_gain, const float* k_gain, const float* inv_freq,
+                                              const int* positions, const int* slots, int num_tokens, int H,
+                                              int KV, int hd, int rotary_dim, int block_size, float eps,
+                                              cudaStream_t stream) {
+  if (!ws || ((uintptr_t)ws & 15)) return asb::fail("qk_norm_rope_store_partial: the partial sums must be 16-byte aligned");
+  if (num_tokens > bn || num_tiles * asb::kPartialRows < (H + 2 * KV) * hd)
+    return asb::fail("qk_norm_rope_store_partial: %d tokens x %d columns do not fit the partial sums (%d x %d)",
+                     num_tokens, (H + 2 * KV) * hd, bn, num_tiles * asb::kPartialRows);
+  if (!(hd == 32 || hd == 64 || hd == 128 || hd == 256) || (inv_freq && rotary_dim != hd))
+    return asb::fail("qk_norm_rope_store_partial: head_dim %d with rotary_dim %d is not taken", hd, rotary_dim);
+  const asb::PartialSums ps = {ws, max_slots, bn, kb_per_tile, num_tiles, blocks};
+  return rope_store(q_out, k_cache, v_cache, nullptr, ps, q_gain, k_gain, inv_freq, positions, slots, num_tokens,
+                    H, KV, hd, rotary_dim, block_size, eps, asb::kBFloat16, stream);
+}
+
+namespace {
+int rope_store(void* q_out, void* k_cache, void* v_cache, const void* qkv, const asb::PartialSums& ps,
+               const float* q_gain, const float* k_gain, const float* inv_freq, const int* positions,
+               const int* slots, int num_tokens, int H, int KV, int hd, int rotary_dim, int block_size,
+               float eps, int dtype, cudaStream_t stream) {
   if (num_tokens == 0) return 0;
   if (hd < 1 || hd > kMaxHeadDim) return asb::fail("qk_norm_rope_store: head_dim %d not in 1..%d", hd, kMaxHeadDim);
   if (inv_freq && (rotary_dim < 2 || rotary_dim > hd || rotary_dim % 2))
@@ -191,7 +246,7 @@ extern "C" int asb_qk_norm_rope_store(void* q_out, void* k_cache, void* v_cache,
   if (whole_head && aligned && (hd == 32 || hd == 64 || hd == 128 || hd == 256)) {
 #define ASB_ROPE_VEC(E)                                                                          \
   ASB_DISPATCH_DTYPE(dtype, T,                                                                   \
-                     launch_vec<T, E>((T*)q_out, (T*)k_cache, (T*)v_cache, (const T*)qkv, q_gain, \
+                     launch_vec<T, E>((T*)q_out, (T*)k_cache, (T*)v_cache, (const T*)qkv, ps, q_gain, \
                                       k_gain, inv_freq, positions, slots, num_tokens, H, KV,     \
                                       block_size, eps, stream))
     if (hd == 32) { ASB_ROPE_VEC(1); }
@@ -201,6 +256,7 @@ extern "C" int asb_qk_norm_rope_store(void* q_out, void* k_cache, void* v_cache,
 #undef ASB_ROPE_VEC
     return asb::check_launch("qk_norm_rope_store");
   }
+  if (ps.ws) return asb::fail("qk_norm_rope_store_partial: the pointers must be 16-byte aligned");
   dim3 grid(num_tokens, (H + 2 * KV + kWarps - 1) / kWarps);
   ASB_DISPATCH_DTYPE(dtype, T,
                      asb::launch(qk_norm_rope_store_kernel<T>, grid, kWarps * 32, 0, stream, 
@@ -208,3 +264,4 @@ extern "C" int asb_qk_norm_rope_store(void* q_out, void* k_cache, void* v_cache,
                          inv_freq, positions, slots, H, KV, hd, rotary_dim, block_size, eps));
   return asb::check_launch("qk_norm_rope_store");
 }
+}  // namespace

@@ -5,6 +5,7 @@ from __future__ import annotations
 import torch
 
 from atomserve_b200.ops.library import KernelLibraryError, check, dtype_code, lib, ptr, require_cuda, stream
+from atomserve_b200.ops.linear import PartialSums
 
 
 def _int32(t: torch.Tensor, name: str) -> None:
@@ -48,6 +49,28 @@ def rms_norm(x: torch.Tensor, gain: torch.Tensor, eps: float, rows: torch.Tensor
     return out
 
 
+def partial_add_rms_norm_fusable(width: int) -> bool:
+    return width % 8 == 0 and width <= 8192
+
+
+def partial_add_rms_norm(product: PartialSums, residual: torch.Tensor | None, gain: torch.Tensor,
+                         eps: float) -> tuple[torch.Tensor, torch.Tensor]:  # fmt: skip
+    """(product + residual, rms_norm(product + residual)) in one kernel, the product given as the
+    GEMM's partial sums. The same bits as `linear(..., residual)` followed by `rms_norm`."""
+    require_cuda(residual, gain)
+    T, N = product.tokens, product.columns
+    if not partial_add_rms_norm_fusable(N):
+        raise KernelLibraryError(f"partial_add_rms_norm: width {N} is not taken (a multiple of 8 up to 8192)")
+    _gain(gain, N, "gain")
+    if residual is not None and (residual.shape != (T, N) or residual.dtype != torch.bfloat16 or not residual.is_contiguous()):
+        raise KernelLibraryError("partial_add_rms_norm: residual must be a contiguous bfloat16 [tokens, width] tensor")
+    total = torch.empty(T, N, device=gain.device, dtype=torch.bfloat16)
+    normed = torch.empty_like(total)
+    check(lib().asb_partial_add_rmsnorm(ptr(total), ptr(normed), ptr(product.workspace), *product.layout(),
+                                        ptr(residual), ptr(gain), T, N, float(eps), stream()))  # fmt: skip
+    return total, normed
+
+
 def silu_mul(gate_up: torch.Tensor) -> torch.Tensor:
     """[T, 2I] (gate columns first, then up) -> silu(gate) * up, [T, I]."""
     require_cuda(gate_up)
@@ -59,8 +82,13 @@ def silu_mul(gate_up: torch.Tensor) -> torch.Tensor:
     return out
 
 
+def qk_norm_rope_store_takes_partial(head_dim: int, rotary_dim: int | None) -> bool:
+    """Whether `qk_norm_rope_store` can read its qkv from the GEMM's partial sums."""
+    return head_dim in (32, 64, 128, 256) and rotary_dim in (None, 0, head_dim)
+
+
 def qk_norm_rope_store(
-    qkv: torch.Tensor,
+    qkv: torch.Tensor | PartialSums,
     num_heads: int,
     num_kv_heads: int,
     head_dim: int,
@@ -81,10 +109,19 @@ def qk_norm_rope_store(
     [num_blocks, KV, block_size, hd]; slots: [T] int32 (block * block_size + offset, negative:
     not stored). With num_kv_heads == 0 only q heads are present and nothing is stored.
     """
-    require_cuda(qkv, positions, q_gain, k_gain, inv_freq, slots, k_cache, v_cache)
-    T = qkv.shape[0]
-    if qkv.dim() != 2 or qkv.shape[1] != (num_heads + 2 * num_kv_heads) * head_dim or not qkv.is_contiguous():
-        raise KernelLibraryError(f"qkv has shape {tuple(qkv.shape)}, expected [T, {(num_heads + 2 * num_kv_heads) * head_dim}]")
+    partial = qkv if isinstance(qkv, PartialSums) else None
+    if partial is not None:
+        require_cuda(positions, q_gain, k_gain, inv_freq, slots, k_cache, v_cache)
+        T, width, dtype, device = partial.tokens, partial.columns, torch.bfloat16, partial.workspace.device
+        if not qk_norm_rope_store_takes_partial(head_dim, rotary_dim if inv_freq is not None else None):
+            raise KernelLibraryError(f"qk_norm_rope_store: head_dim {head_dim} with rotary_dim {rotary_dim} is not read from partial sums")
+    else:
+        require_cuda(qkv, positions, q_gain, k_gain, inv_freq, slots, k_cache, v_cache)
+        T, width, dtype, device = qkv.shape[0], qkv.shape[1] if qkv.dim() == 2 else -1, qkv.dtype, qkv.device
+        if not qkv.is_contiguous():
+            width = -1
+    if width != (num_heads + 2 * num_kv_heads) * head_dim:
+        raise KernelLibraryError(f"qkv has width {width}, expected [T, {(num_heads + 2 * num_kv_heads) * head_dim}] contiguous")
     _int32(positions, "positions")
     _gain(q_gain, head_dim, "q_gain")
     _gain(k_gain, head_dim, "k_gain")
@@ -94,10 +131,16 @@ def qk_norm_rope_store(
     if num_kv_heads > 0 and slots is not None:
         _int32(slots, "slots")
         for c in (k_cache, v_cache):
-            if c is None or c.dtype != qkv.dtype or c.dim() != 4 or c.shape[1] != num_kv_heads or c.shape[3] != head_dim or not c.is_contiguous():
+            if c is None or c.dtype != dtype or c.dim() != 4 or c.shape[1] != num_kv_heads or c.shape[3] != head_dim or not c.is_contiguous():
                 raise KernelLibraryError("cache entry must be [num_blocks, KV, block_size, head_dim] in the activations' dtype")
         block_size = k_cache.shape[2]
-    q = torch.empty(T, num_heads, head_dim, device=qkv.device, dtype=qkv.dtype)
+    q = torch.empty(T, num_heads, head_dim, device=device, dtype=dtype)
+    if partial is not None:
+        check(lib().asb_qk_norm_rope_store_partial(
+            ptr(q), ptr(k_cache), ptr(v_cache), ptr(partial.workspace), *partial.layout(), ptr(q_gain), ptr(k_gain),
+            ptr(inv_freq), ptr(positions), ptr(slots), T, num_heads, num_kv_heads, head_dim, rotary_dim, block_size,
+            float(eps), stream()))  # fmt: skip
+        return q
     check(lib().asb_qk_norm_rope_store(
         ptr(q), ptr(k_cache), ptr(v_cache), ptr(qkv), ptr(q_gain), ptr(k_gain), ptr(inv_freq),
         ptr(positions), ptr(slots), T, num_heads, num_kv_heads, head_dim, rotary_dim, block_size,

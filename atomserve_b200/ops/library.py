@@ -38,6 +38,9 @@ _SIGNATURES = {
     "asb_attention_reduce": [_P, _P, _P, _P, _I, _I, _I, _I, _P],
     "asb_attention_mma_supported": [_I, _I],
     "asb_gemm_tcgen05": [_P, _P, _P, _P, _I, _I, _I, _I, _P, _P, _P],
+    "asb_gemm_tcgen05_plan": [_I, _I, _I, _P],
+    "asb_partial_add_rmsnorm": [_P, _P, _P, _I, _I, _I, _I, _I, _P, _P, _I, _I, _F, _P],
+    "asb_qk_norm_rope_store_partial": [_P] * 4 + [_I] * 5 + [_P] * 5 + [_I] * 6 + [_F, _P],
     "asb_gemm_simt": [_P, _P, _P, _P, _I, _I, _I, _I, _I, _P],
     "asb_argmax_rows": [_P, _P, _I, _I, _P],
     "asb_presence_penalty": [_P, _P, _P, _P, _I, _I, _P],

@@ -12,6 +12,7 @@ accumulator, so logits are never rounded to bfloat16.
 from __future__ import annotations
 
 import ctypes
+import dataclasses
 import os
 
 import torch
@@ -84,6 +85,58 @@ def gemm_tcgen05(x: torch.Tensor, w: torch.Tensor, residual: torch.Tensor | None
     check(lib().asb_gemm_tcgen05(ptr(out), ptr(x), ptr(w), ptr(residual), M, N, K, 2 if swiglu else int(out_dtype == torch.float32),
                                  ptr(workspace), ptr(gemm_status(x.device)), stream()))  # fmt: skip
     return out
+
+
+@dataclasses.dataclass(frozen=True)
+class PartialSums:
+    """x . w^T as the tensor-core GEMM left it in its workspace when it cut K: float32 partial
+    sums, a few slots per tile of 128 output columns (csrc/gemm_partials.cuh). A kernel that
+    consumes the product can add the slots up itself (`partial_add_rms_norm`,
+    `qk_norm_rope_store`), which saves the GEMM's reduction kernel. The workspace is shared: the
+    sums are gone with the next tensor-core GEMM call, so they are consumed at once."""
+
+    workspace: torch.Tensor
+    tokens: int
+    columns: int
+    max_slots: int
+    tile_tokens: int
+    k_blocks_per_tile: int
+    tiles: int
+    blocks: int
+
+    def layout(self) -> tuple[int, int, int, int, int, int]:
+        """The arguments that the consuming kernels' entry points take after the workspace."""
+        return (self.max_slots, self.tile_tokens, self.k_blocks_per_tile, self.tiles, self.blocks)
+
+
+_PLANS: dict[tuple[int, int, int], tuple[int, ...]] = {}
+
+
+def _plan(M: int, N: int, K: int) -> tuple[int, ...]:
+    plan = _PLANS.get((M, N, K))
+    if plan is None:
+        out = (ctypes.c_int * 7)()
+        check(lib().asb_gemm_tcgen05_plan(M, N, K, out))
+        plan = _PLANS[(M, N, K)] = tuple(out)
+    return plan
+
+
+def linear_partial(x: torch.Tensor, w: torch.Tensor) -> PartialSums | None:
+    """x . w^T left as partial sums, or None where the product does not run that way (many
+    tokens, float32, another backend): the caller then takes `linear`."""
+    if BACKEND != "tcgen05" or x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or not x.is_cuda:
+        return None
+    if x.dim() != 2 or w.dim() != 2 or x.shape[1] != w.shape[1] or not x.is_contiguous() or not w.is_contiguous():
+        return None
+    if not tcgen05_supported(x, w):
+        return None
+    (M, K), N = x.shape, w.shape[0]
+    cuts_k, swapped, max_slots, tile_tokens, k_blocks, tiles, blocks = _plan(M, N, K)
+    if not (cuts_k and swapped) or tiles * 128 < N or M > tile_tokens:
+        return None
+    workspace = gemm_workspace(x.device, tiles * max_slots * 128 * tile_tokens)
+    check(lib().asb_gemm_tcgen05(None, ptr(x), ptr(w), None, M, N, K, 3, ptr(workspace), ptr(gemm_status(x.device)), stream()))
+    return PartialSums(workspace, M, N, max_slots, tile_tokens, k_blocks, tiles, blocks)
 
 
 def tcgen05_supported(x: torch.Tensor, w: torch.Tensor) -> bool:

@@ -7,7 +7,7 @@ from __future__ import annotations
 import torch
 
 from atomserve_b200 import ops
-from atomserve_b200.parts.base import CacheView, KVCacheSpec, Mixer, StepContext, build_part, register_part
+from atomserve_b200.parts.base import CacheView, KVCacheSpec, Mixer, Norm, StepContext, build_part, register_part
 from atomserve_b200.parts.spec import PartSpec, TensorSpec
 
 
@@ -65,12 +65,27 @@ class GQAttention(Mixer):
 
     def forward(self, h: torch.Tensor, residual: torch.Tensor, ctx: StepContext,
                 cache: CacheView | None, write_cache: bool = True) -> torch.Tensor:  # fmt: skip
+        return ops.linear(self.attend(h, ctx, cache, write_cache), self.o_proj, residual)
+
+    def forward_then(self, h: torch.Tensor, residual: torch.Tensor, ctx: StepContext, cache: CacheView | None,
+                     write_cache: bool, then: Norm) -> tuple[torch.Tensor, torch.Tensor]:  # fmt: skip
+        after_linear = getattr(then, "after_linear", None)
+        if after_linear is None:
+            return super().forward_then(h, residual, ctx, cache, write_cache, then)
+        return after_linear(self.attend(h, ctx, cache, write_cache), self.o_proj, residual)
+
+    def attend(self, h: torch.Tensor, ctx: StepContext, cache: CacheView | None, write_cache: bool) -> torch.Tensor:
+        """The heads' outputs side by side, [T, H * hd], before the output projection."""
         H, KV, hd = self.num_heads, self.num_kv_heads, self.head_dim
-        if write_cache:
-            qkv, kv_heads = ops.linear(h, self.qkv_proj), KV
-        else:  # reads another entry's keys and values: only queries are projected
-            qkv, kv_heads = ops.linear(h, self.qkv_proj[: H * hd]), 0
         pos = self.position
+        # reading another entry's keys and values, only queries are projected
+        weight, kv_heads = (self.qkv_proj, KV) if write_cache else (self.qkv_proj[: H * hd], 0)
+        qkv = None
+        if ops.qk_norm_rope_store_takes_partial(hd, pos.rotary_dim if pos else None):
+            # with few tokens the product stays as the GEMM's partial sums and the next kernel adds them up
+            qkv = ops.linear_partial(h, weight)
+        if qkv is None:
+            qkv = ops.linear(h, weight)
         q = ops.qk_norm_rope_store(
             qkv, H, kv_heads, hd, ctx.positions,
             q_gain=self.q_gain, k_gain=self.k_gain, eps=self.qk_norm_eps or 0.0,
@@ -83,7 +98,7 @@ class GQAttention(Mixer):
             num_requests=ctx.num_requests, max_context=ctx.max_context, window=self.window,
             scale=self.scale, host_q_lens=ctx.host_q_lens or None,
         )  # fmt: skip
-        return ops.linear(out.view(-1, H * hd), self.o_proj, residual)
+        return out.view(-1, H * hd)
 
 
 register_part("mixer", "gqa_attention", GQAttention)

@@ -104,6 +104,10 @@ class Norm(Part):
     def forward(self, x: torch.Tensor, rows: torch.Tensor | None = None) -> torch.Tensor:
         raise NotImplementedError
 
+    # A norm may also offer `after_linear(x, weight, residual) -> (s, forward(s))` with
+    # s = x . weight^T + residual: a mixer or feed-forward whose last step is such a projection
+    # hands it to the norm that follows, which may then run both in one kernel.
+
 
 class PositionEncoding(Part):
     """How positions enter a mixer. `prepare(device)` builds its tables once."""
@@ -123,10 +127,23 @@ class Mixer(Part):
                 cache: CacheView | None, write_cache: bool = True) -> torch.Tensor:  # fmt: skip
         raise NotImplementedError
 
+    def forward_then(self, h: torch.Tensor, residual: torch.Tensor, ctx: StepContext, cache: CacheView | None,
+                     write_cache: bool, then: Norm) -> tuple[torch.Tensor, torch.Tensor]:  # fmt: skip
+        """(out, then(out)) for out = forward(...): the block calls this when a norm follows, so
+        that a mixer can fuse its last projection with that norm. The default runs them in turn."""
+        out = self.forward(h, residual, ctx, cache, write_cache)
+        return out, then.forward(out)
+
 
 class FeedForward(Part):
     def forward(self, h: torch.Tensor, residual: torch.Tensor, ctx: StepContext) -> torch.Tensor:
         raise NotImplementedError
+
+    def forward_then(self, h: torch.Tensor, residual: torch.Tensor, ctx: StepContext,
+                     then: Norm) -> tuple[torch.Tensor, torch.Tensor]:  # fmt: skip
+        """(out, then(out)) for out = forward(...); see Mixer.forward_then."""
+        out = self.forward(h, residual, ctx)
+        return out, then.forward(out)
 
 
 class Block(Part):
@@ -147,6 +164,14 @@ class Block(Part):
     def forward(self, x: torch.Tensor, ctx: StepContext, cache: CacheView | None,
                 write_cache: bool = True) -> torch.Tensor:  # fmt: skip
         raise NotImplementedError
+
+    def forward_chain(self, x: torch.Tensor, normed: torch.Tensor | None, ctx: StepContext, cache: CacheView | None,
+                      write_cache: bool, then: Norm | None) -> tuple[torch.Tensor, torch.Tensor | None]:  # fmt: skip
+        """forward() for a block inside a run of blocks, which is how the model calls it. `normed`
+        is mixer_norm(x) where the previous block has computed it already; `then` is the norm
+        that the next block applies first. Returns (result, then(result)), or (result, None)
+        where the block leaves that norm to the next one, as this default does."""
+        return self.forward(x, ctx, cache, write_cache), None
 
 
 # ---- registries ------------------------------------------------------------------------------

@@ -6,7 +6,7 @@ from __future__ import annotations
 import torch
 
 from atomserve_b200 import ops
-from atomserve_b200.parts.base import FeedForward, StepContext, register_part
+from atomserve_b200.parts.base import FeedForward, Norm, StepContext, register_part
 from atomserve_b200.parts.spec import TensorSpec
 
 
@@ -36,12 +36,20 @@ class SwiGLU(FeedForward):
             self.gate_up_proj = torch.cat([gate, up]).contiguous()
         self.down_proj = tensors[p + "down_proj.weight"]
 
-    def forward(self, h: torch.Tensor, residual: torch.Tensor, ctx: StepContext) -> torch.Tensor:
+    def hidden(self, h: torch.Tensor) -> torch.Tensor:
         if self.fused:
-            hidden = ops.linear_swiglu(h, self.gate_up_proj)
-        else:
-            hidden = ops.silu_mul(ops.linear(h, self.gate_up_proj))
-        return ops.linear(hidden, self.down_proj, residual)
+            return ops.linear_swiglu(h, self.gate_up_proj)
+        return ops.silu_mul(ops.linear(h, self.gate_up_proj))
+
+    def forward(self, h: torch.Tensor, residual: torch.Tensor, ctx: StepContext) -> torch.Tensor:
+        return ops.linear(self.hidden(h), self.down_proj, residual)
+
+    def forward_then(self, h: torch.Tensor, residual: torch.Tensor, ctx: StepContext,
+                     then: Norm) -> tuple[torch.Tensor, torch.Tensor]:  # fmt: skip
+        after_linear = getattr(then, "after_linear", None)
+        if after_linear is None:
+            return super().forward_then(h, residual, ctx, then)
+        return after_linear(self.hidden(h), self.down_proj, residual)
 
 
 register_part("feed_forward", "swiglu", SwiGLU)

@@ -71,9 +71,13 @@ class DecoderModel:
     def forward(self, ctx: StepContext, views: list[CacheView | None]) -> torch.Tensor:
         """Run the T tokens of the step; float32 logits [len(ctx.logits_rows), vocab]."""
         x = self.embedding.forward(ctx.token_ids)
+        normed = None  # the next block's first norm of x, where the block before it has computed it
         for i, call in enumerate(self.schedule):
             own = call.cache_from is None
-            x = self.blocks[call.layer].forward(x, ctx, views[i if own else call.cache_from], own)
+            then = self.blocks[self.schedule[i + 1].layer].mixer_norm if i + 1 < len(self.schedule) else None
+            x, normed = self.blocks[call.layer].forward_chain(
+                x, normed, ctx, views[i if own else call.cache_from], own, then
+            )
         if ctx.logits_rows.shape[0] == 0:
             return torch.empty(0, self.spec.vocab_size, device=x.device, dtype=torch.float32)
         return self.head.forward(self.final_norm.forward(x, ctx.logits_rows))

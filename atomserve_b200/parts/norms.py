@@ -26,5 +26,17 @@ class RMSNorm(Norm):
     def forward(self, x: torch.Tensor, rows: torch.Tensor | None = None) -> torch.Tensor:
         return ops.rms_norm(x, self.gain, self.eps, rows)
 
+    def after_linear(self, x: torch.Tensor, weight: torch.Tensor,
+                     residual: torch.Tensor | None) -> tuple[torch.Tensor, torch.Tensor]:  # fmt: skip
+        """(s, forward(s)) for s = x . weight^T + residual. Where the product runs with partial
+        sums (few tokens), one kernel adds them up, adds the residual and normalises; the results
+        are the same bits either way."""
+        if ops.partial_add_rms_norm_fusable(self.width) and weight.shape[0] == self.width:
+            product = ops.linear_partial(x, weight)
+            if product is not None:
+                return ops.partial_add_rms_norm(product, residual, self.gain, self.eps)
+        total = ops.linear(x, weight, residual)
+        return total, self.forward(total)
+
 
 register_part("norm", "rms_norm", RMSNorm)

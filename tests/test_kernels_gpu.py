@@ -431,3 +431,78 @@ def test_gemm_tcgen05_swiglu(ops, M, I, K):
     gs, us = x.double().cpu() @ gate.double().cpu().T, x.double().cpu() @ up.double().cpu().T
     ref = gs / (1 + torch.exp(-gs)) * us
     assert out.shape == (M, I) and torch.allclose(out.double().cpu(), ref, atol=2e-2, rtol=2e-2)
+
+
+PARTIAL_NORM_SHAPES = [(1, 4096, 4096), (8, 4096, 12288), (5, 1024, 2048), (16, 640, 1024), (33, 2048, 4096),
+                       (64, 4096, 4096), (7, 5120, 17408), (3, 264, 2048)]  # fmt: skip
+
+
+@pytest.mark.parametrize("M,N,K", PARTIAL_NORM_SHAPES)
+def test_partial_add_rms_norm_is_the_unfused_result(ops, M, N, K):
+    """A product left as the GEMM's partial sums, added up with the residual and normalised in
+    one kernel: the same bits as the GEMM with its own reduction followed by rms_norm, and close
+    to float64."""
+    from atomserve_b200.ops.linear import check_gemm_status
+
+    g = torch.Generator().manual_seed(M + N + K)
+    x = torch.randn(M, K, generator=g).bfloat16().cuda()
+    w = (torch.randn(N, K, generator=g) / math.sqrt(K)).bfloat16().cuda()
+    res = torch.randn(M, N, generator=g).bfloat16().cuda()
+    gain = (1 + 0.1 * torch.randn(N, generator=g)).cuda()
+    product = ops.linear_partial(x, w)
+    assert product is not None, "these shapes cut K: the partial-sum form must be available"
+    assert (product.tokens, product.columns) == (M, N)
+    total, normed = ops.partial_add_rms_norm(product, res, gain, 1e-6)
+    plain_total = ops.linear(x, w, res)
+    plain_normed = ops.rms_norm(plain_total, gain, 1e-6)
+    check_gemm_status()
+    assert torch.equal(total, plain_total) and torch.equal(normed, plain_normed)
+    ref = x.double().cpu() @ w.double().cpu().T + res.double().cpu()
+    assert torch.allclose(total.double().cpu(), ref, atol=3e-2, rtol=2e-2)
+    # without a residual
+    total0, normed0 = ops.partial_add_rms_norm(ops.linear_partial(x, w), None, gain, 1e-6)
+    plain0 = ops.linear(x, w)
+    assert torch.equal(total0, plain0) and torch.equal(normed0, ops.rms_norm(plain0, gain, 1e-6))
+
+
+def test_linear_partial_declines_what_does_not_cut_k(ops):
+    """Many tokens, float32 operands and tiny products have no partial-sum form: None, and the
+    caller takes the plain product."""
+    x = torch.randn(300, 512, device="cuda").bfloat16()
+    w = torch.randn(1024, 512, device="cuda").bfloat16()
+    assert ops.linear_partial(x, w) is None
+    assert ops.linear_partial(x[:4].float(), w.float()) is None
+
+
+@pytest.mark.parametrize("H,KV,hd,K", [(8, 2, 128, 2048), (32, 8, 128, 4096), (4, 2, 64, 1024), (6, 3, 32, 2048), (2, 1, 256, 1024), (8, 0, 128, 2048)])
+@pytest.mark.parametrize("T", [1, 6, 40])
+def test_qk_norm_rope_store_from_partial_sums(ops, H, KV, hd, K, T):
+    """q/k norm, rotation and the cache write reading the qkv product from the GEMM's partial
+    sums: the same bits as from the reduced product (KV = 0: queries only, nothing stored)."""
+    from atomserve_b200.ops.linear import check_gemm_status
+
+    g = torch.Generator().manual_seed(H * 100 + hd + T)
+    bs, nblocks = 16, 8
+    x = torch.randn(T, K, generator=g).bfloat16().cuda()
+    w = (torch.randn((H + 2 * KV) * hd, K, generator=g) / math.sqrt(K)).bfloat16().cuda()
+    qg, kg = ((1 + 0.1 * torch.randn(hd, generator=g)).cuda() for _ in range(2))
+    inv_freq = plain.rope_inv_freq(hd, 1e6).cuda()
+    pos = torch.randint(0, 40000, (T,), generator=g).int().cuda()
+    slot_list = torch.randperm(nblocks * bs, generator=g)[:T].tolist()
+    if T > 1:
+        slot_list[1] = -1
+    slots = torch.tensor(slot_list, dtype=torch.int32, device="cuda")
+    results = []
+    for partial in (False, True):
+        kc = torch.zeros(nblocks, max(KV, 1), bs, hd, device="cuda", dtype=torch.bfloat16)
+        vc = torch.zeros_like(kc)
+        qkv = ops.linear_partial(x, w) if partial else ops.linear(x, w)
+        assert qkv is not None
+        store = dict(slots=slots, k_cache=kc, v_cache=vc) if KV else dict(slots=None, k_cache=None, v_cache=None)
+        q = ops.qk_norm_rope_store(qkv, H, KV, hd, pos, q_gain=qg, k_gain=kg, eps=1e-6, inv_freq=inv_freq,
+                                   rotary_dim=hd, **store)  # fmt: skip
+        results.append((q, kc, vc))
+    check_gemm_status()
+    for a, b in zip(*results):
+        assert torch.equal(a, b)
+    assert float(results[1][0].float().abs().max()) > 0
