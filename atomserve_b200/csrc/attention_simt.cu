@@ -197,13 +197,18 @@ paged_attention_kernel(const AttentionParams p) {
 }
 
 // Merge the partitions of one (token, head): weights exp(m_p - max m), empty partitions (sum 0)
-// are skipped, in ascending order of partition (atomserve/kernels.py:308-334).
+// are skipped, in ascending order of partition (atomserve/kernels.py:308-334). The weights go
+// through shared memory, kReduceChunk partitions at a time, so that the accumulator loads that
+// follow are unconditional and several are in flight.
+constexpr int kReduceChunk = 64;
+
 template <typename T>
 __global__ void attention_reduce_kernel(T* __restrict__ out, const float* __restrict__ part_m,
                                         const float* __restrict__ part_l,
                                         const float* __restrict__ part_acc, int NP, int hd) {
   asb::pdl_wait();  // the stream's previous kernel has completed (programmatic dependent launch)
   asb::pdl_launch_dependents();
+  __shared__ float weight[kReduceChunk];
   const size_t row = blockIdx.x;
   const float* pm = part_m + row * NP;
   const float* pl = part_l + row * NP;
@@ -213,11 +218,33 @@ __global__ void attention_reduce_kernel(T* __restrict__ out, const float* __rest
   float denom = 0.f;
   for (int i = 0; i < NP; ++i)
     if (pl[i] > 0.f) denom += pl[i] * expf(pm[i] - mx);
-  for (int e = threadIdx.x; e < hd; e += blockDim.x) {
-    float a = 0.f;
-    for (int i = 0; i < NP; ++i)
-      if (pl[i] > 0.f) a += part_acc[(row * NP + i) * hd + e] * expf(pm[i] - mx);
-    out[row * hd + e] = asb::from_float<T>(a / denom);
+  const int e = threadIdx.x;  // the launch gives hd <= blockDim.x a thread per element, else strides
+  float a[2] = {0.f, 0.f};    // up to two elements per thread (head sizes to 512 with 256 threads)
+  for (int i0 = 0; i0 < NP; i0 += kReduceChunk) {
+    const int n = min(kReduceChunk, NP - i0);
+    __syncthreads();
+    for (int i = threadIdx.x; i < n; i += blockDim.x) weight[i] = pl[i0 + i] > 0.f ? expf(pm[i0 + i] - mx) : -1.f;
+    __syncthreads();
+#pragma unroll
+    for (int k = 0; k < 2; ++k) {
+      const int col = e + k * blockDim.x;
+      if (col >= hd) break;
+      const float* acc = part_acc + (row * NP + i0) * hd + col;
+      for (int j0 = 0; j0 < n; j0 += 4) {
+        float v[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u)
+          if (j0 + u < n) v[u] = acc[(size_t)(j0 + u) * hd];
+#pragma unroll
+        for (int u = 0; u < 4; ++u)
+          if (j0 + u < n && weight[j0 + u] >= 0.f) a[k] += v[u] * weight[j0 + u];
+      }
+    }
+  }
+#pragma unroll
+  for (int k = 0; k < 2; ++k) {
+    const int col = e + k * blockDim.x;
+    if (col < hd) out[row * hd + col] = asb::from_float<T>(a[k] / denom);
   }
 }
 
@@ -266,6 +293,7 @@ extern "C" int asb_attention_reduce(void* out, const float* part_m, const float*
                                     const float* part_acc, int rows, int NP, int hd, int dtype,
                                     cudaStream_t stream) {
   if (rows == 0) return 0;
+  if (hd < 1 || hd > 512) return asb::fail("attention_reduce: head_dim %d not in 1..512", hd);
   int threads = 32;
   while (threads < hd && threads < 256) threads <<= 1;
   ASB_DISPATCH_DTYPE(dtype, T,

@@ -38,6 +38,9 @@ bool pdl_enabled();
 // GEMM calls measured 0.5 to 2 us shorter each. Set once per kernel function.
 void prefer_shared_carveout(const void* kernel);
 
+// Kernel launches made by this library so far (asb_launch_count reads it).
+void count_launch();
+
 template <typename... KArgs, typename... Args>
 inline void launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
                    Args&&... args) {
@@ -52,6 +55,7 @@ inline void launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
   config.attrs = attribute;
   config.numAttrs = pdl_enabled() ? 1 : 0;
   prefer_shared_carveout((const void*)kernel);
+  count_launch();
   cudaLaunchKernelEx(&config, kernel, std::forward<Args>(args)...);
 }
 

@@ -1,4 +1,5 @@
 // Error text of the last refused call on this thread, and the library's identity.
+#include <atomic>
 #include <mutex>
 
 #include "common.cuh"
@@ -35,13 +36,24 @@ void prefer_shared_carveout(const void* kernel) {
   cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
 }
 
+static std::atomic<long long> g_launches{0};
+void count_launch() { g_launches.fetch_add(1, std::memory_order_relaxed); }
+long long launch_count() { return g_launches.load(std::memory_order_relaxed); }
+
 static bool g_pdl = false;
 bool pdl_enabled() { return g_pdl; }
 void set_pdl(bool on) { g_pdl = on; }
 
 }  // namespace asb
 
-namespace asb { void set_pdl(bool on); }
+namespace asb {
+void set_pdl(bool on);
+long long launch_count();
+}  // namespace asb
+
+// Kernels launched by this library's entry points in this process (a launch recorded into a CUDA
+// graph counts once, at capture).
+extern "C" long long asb_launch_count() { return asb::launch_count(); }
 
 // Switch programmatic dependent launch on or off for every later launch of this library.
 extern "C" void asb_set_pdl(int on) { asb::set_pdl(on != 0); }

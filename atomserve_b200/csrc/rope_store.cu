@@ -103,13 +103,14 @@ __global__ void qk_norm_rope_store_vec_kernel(
   const int heads = H + 2 * KV;
   const int e0 = lane * EPT;  // this lane's first element
   // Positions and cache slots were uploaded before the step's first kernel, and the angles depend
-  // on nothing else: all of this overlaps the previous kernel's tail.
+  // on nothing else: all of this overlaps the previous kernel's tail. (Read from L2: an SM's L1
+  // could still hold these addresses' lines from an earlier step.)
   int slot = -1;
   float cs[EPT], sn[EPT];
   if (head_first < heads) {
-    slot = slots ? slots[t] : -1;
+    slot = slots ? __ldcg(slots + t) : -1;
     if (inv_freq) {
-      const float pos = (float)positions[t];
+      const float pos = (float)__ldcg(positions + t);
       const int i0 = (lane & 15) * EPT;
 #pragma unroll
       for (int k = 0; k < EPT; ++k) sincosf(pos * inv_freq[i0 + k], &sn[k], &cs[k]);

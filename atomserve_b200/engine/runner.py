@@ -24,7 +24,7 @@ import numpy as np
 import torch
 
 from atomserve_b200.cache.manager import CacheManager, RequestCache
-from atomserve_b200.ops.library import LAUNCHES
+from atomserve_b200.ops.library import launches, note_replay
 from atomserve_b200.parts.base import CacheView, StepContext
 from atomserve_b200.parts.model import DecoderModel
 
@@ -267,14 +267,14 @@ class ModelRunner:
             self.model.forward(ctx, self.views)
             torch.cuda.synchronize()
             graph = torch.cuda.CUDAGraph()
-            before = LAUNCHES[0]
+            before = launches()
             with torch.cuda.graph(graph):
                 out = self.model.forward(ctx, self.views)
-            entry = (graph, out, LAUNCHES[0] - before)
+            entry = (graph, out, launches() - before)
             self._graphs[key] = entry
-        graph, out, launches = entry
+        graph, out, recorded = entry
         graph.replay()
-        LAUNCHES[0] += launches  # the replay launched what the capture recorded
+        note_replay(recorded)  # the replay ran what the capture recorded
         return out[:wanted]
 
 

@@ -66,6 +66,7 @@ def lib() -> ctypes.CDLL:
                 f"the CUDA kernel library could not be built or loaded: {error}"
             ) from error
         handle.asb_last_error.restype = ctypes.c_char_p
+        handle.asb_launch_count.restype = ctypes.c_longlong
         handle.asb_set_pdl.argtypes = [c_int]
         handle.asb_set_pdl.restype = None
         # programmatic dependent launch: kernels are scheduled while their predecessor drains
@@ -90,11 +91,19 @@ def declare(name: str, argtypes: list) -> None:
         fn.argtypes, fn.restype = argtypes, c_int
 
 
-LAUNCHES = [0]  # entry-point calls of this library so far (each launches one to two kernels)
+_REPLAYED = [0]  # kernels run by CUDA-graph replays: counted from what each capture recorded
+
+
+def launches() -> int:
+    """Kernels of this library launched so far in this process, graph replays included."""
+    return int(lib().asb_launch_count()) + _REPLAYED[0]
+
+
+def note_replay(kernels: int) -> None:
+    _REPLAYED[0] += kernels
 
 
 def check(code: int) -> None:
-    LAUNCHES[0] += 1
     if code != 0:
         raise KernelLibraryError(lib().asb_last_error().decode())
 

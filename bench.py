@@ -140,7 +140,7 @@ def time_decode(engine, batch: int, steps: int, warmup: int, prompt_tokens: int 
     from atomserve_b200 import ops
     from atomserve_b200.engine.runner import Row
     from atomserve_b200.engine.sequence import SamplingParams
-    from atomserve_b200.ops.library import LAUNCHES
+    from atomserve_b200.ops.library import launches as kernel_launches
 
     runner, cache = engine.runner, engine.runner.cache
     # --- device-timed: the step function on fixed token ids, positions advancing ---
@@ -164,7 +164,7 @@ def time_decode(engine, batch: int, steps: int, warmup: int, prompt_tokens: int 
         pos += 1
     torch.cuda.synchronize()
     start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    launches_before = LAUNCHES[0]
+    launches_before = kernel_launches()
     start.record()
     for _ in range(steps):
         one_step(pos)
@@ -172,7 +172,7 @@ def time_decode(engine, batch: int, steps: int, warmup: int, prompt_tokens: int 
     end.record()
     torch.cuda.synchronize()
     device_ms = start.elapsed_time(end) / steps
-    launches = LAUNCHES[0] - launches_before
+    launches = kernel_launches() - launches_before
     mid_context = PROMPT_TOKENS + warmup + steps // 2
     for rc in reqs:
         cache.free(rc)
