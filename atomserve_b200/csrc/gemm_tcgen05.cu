@@ -62,6 +62,11 @@ struct GemmParams {
   int kb_per_tile;       // K blocks of BK per tile
   int stream;            // 0: whole tiles round-robin; 1: equal contiguous ranges of K blocks
   int max_slots;         // workspace slots per tile
+  // Optional timeline for profiling, null in normal use: %globaltimer stamps in rows of 8 words, 7
+  // used per block (entry, set-up done, dependency wait over, first stage complete, last MMA
+  // issued, last accumulator complete, epilogue done) and a row after the blocks for the reduction
+  // kernel (entry, wait over, end).
+  unsigned long long* stamps;
 };
 
 // Walks the segments of one block: the same sequence in every warp role.
@@ -94,6 +99,15 @@ struct SegmentWalk {
     return true;
   }
 };
+
+__device__ __forceinline__ unsigned long long global_timer() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t)::"memory");
+  return t;
+}
+__device__ __forceinline__ void stamp(const GemmParams& p, int which) {
+  if (p.stamps) p.stamps[(size_t)blockIdx.x * 8 + which] = global_timer();
+}
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
@@ -198,6 +212,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_cons
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
   if (threadIdx.x == 0) {
+    stamp(p, 0);
     for (int s = 0; s < C::kStages; ++s) {
       mbar_init(full_bar(s), 1);
       mbar_init(empty_bar(s), 1);
@@ -216,6 +231,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_cons
   __syncthreads();
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
   const uint32_t tmem_base = *tmem_slot;
+  if (threadIdx.x == 0) stamp(p, 1);
   // Everything above touched only this block's shared and tensor memory: with a programmatic
   // dependent launch it ran while the stream's previous kernel was finishing. Each role calls
   // pdl_wait() before it first reads that kernel's output; the TMA warp first fills the pipeline
@@ -238,6 +254,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_cons
         }
       }
       asb::pdl_wait();
+      stamp(p, 2);
       asb::pdl_launch_dependents();
       SegmentWalk walk(p);
       uint32_t it = 0;  // K blocks loaded so far by this block, across segments
@@ -279,6 +296,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_cons
           const uint32_t phase = (it / C::kStages) & 1u;
           ok = mbar_wait(full_bar(s), phase, p.status, 2);
           if (!ok) break;
+          if (it == 0) stamp(p, 3);
           asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
           const uint64_t da = smem_desc(base + s * C::kStage);
           const uint64_t db = smem_desc(base + s * C::kStage + C::kTileP);
@@ -289,6 +307,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_cons
           umma_commit(empty_bar(s));  // stage s may be refilled once these MMAs have read it
         }
         umma_commit(acc_full(buf));  // arrives when every MMA of this segment has completed
+        stamp(p, 4);
         ++seg;
       }
     }
@@ -305,6 +324,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_cons
       if (lane == 0) ok_i = mbar_wait(acc_full(buf), (seg >> 1) & 1u, p.status, 3) ? 1 : 0;  // one poller per warp
       ok = __shfl_sync(0xffffffffu, ok_i, 0) != 0;
       if (!ok) break;
+      if (warp == 2 && lane == 0) stamp(p, 5);
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       const int p0 = (walk.tile % p.tiles_p) * BM, q0 = (walk.tile / p.tiles_p) * BN;
       const int prow = p0 + quad * 32 + lane;
@@ -434,8 +454,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_cons
       __syncwarp();
       if (lane == 0) mbar_arrive(acc_empty(buf));
       ++seg;
-
     }
+    if (warp == 2 && lane == 0) stamp(p, 6);
   }
 
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -460,7 +480,15 @@ __global__ void segment_reduce_kernel(const GemmParams p, int parts) {
   const int p0 = (tile % p.tiles_p) * BM, q0 = (tile / p.tiles_p) * BN;
   const float* ws = p.workspace + (size_t)tile * p.max_slots * BM * BN;
   const int i = (blockIdx.y * blockDim.x + threadIdx.x) * 4;
+  unsigned long long* stamps = p.stamps ? p.stamps + (size_t)parts * 8 : nullptr;
+  const bool first_thread = blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == 0;
+  if (stamps && first_thread) stamps[0] = global_timer();
   asb::pdl_wait();  // the GEMM has completed (programmatic dependent launch)
+  if (stamps && first_thread) stamps[1] = global_timer();
+  struct AtExit {
+    unsigned long long* stamps;
+    __device__ ~AtExit() { if (stamps && threadIdx.x == 0) atomicMax(stamps + 2, global_timer()); }
+  } at_exit{stamps};
   asb::pdl_launch_dependents();
   if (slots == 1) return;  // one block covered all of K and stored the tile itself
   if (i >= BM * BN) return;
@@ -547,6 +575,8 @@ int sm_count() {
   return count;
 }
 
+unsigned long long* g_stamps = nullptr;  // asb_gemm_tcgen05_timeline
+
 struct Plan {
   int swap, bn, tiles_p, tiles_q, kb_per_tile, stream, blocks, max_slots;
   long long workspace;  // float32 elements
@@ -615,6 +645,10 @@ extern "C" long long asb_gemm_tcgen05_workspace(int M, int N, int K, int* stream
   return pl.workspace;
 }
 
+// Profiling aid: later calls write their timeline (see GemmParams::stamps) into `buffer`, device
+// memory of (blocks + 1) * 8 64-bit words that the caller zeroes; null switches it off again.
+extern "C" void asb_gemm_tcgen05_timeline(void* buffer) { g_stamps = (unsigned long long*)buffer; }
+
 // How a shape is run: out7 = {cuts K (1) or whole tiles (0), swapped operands, workspace slots per
 // tile, token columns per tile, K blocks per tile, tiles, thread blocks}. A shape that cuts K with
 // swapped operands can leave its product as partial sums (mode 3 of asb_gemm_tcgen05), which
@@ -668,6 +702,7 @@ extern "C" int asb_gemm_tcgen05(void* out, const void* x, const void* w, const v
   p.kb_per_tile = pl.kb_per_tile;
   p.stream = pl.stream;
   p.max_slots = pl.max_slots;
+  p.stamps = g_stamps;
   alignas(64) CUtensorMap mp, mq;
   if (int rc = make_map(&mp, pl.swap ? w : x, p.p_rows, K, BM)) return rc;
   if (int rc = make_map(&mq, pl.swap ? x : w, p.q_rows, K, pl.bn)) return rc;

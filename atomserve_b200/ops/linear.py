@@ -110,6 +110,8 @@ class PartialSums:
 
 
 _PLANS: dict[tuple[int, int, int], tuple[int, ...]] = {}
+# ATOMSERVE_B200_PARTIAL_SUMS=0: every product is reduced by the GEMM itself (for comparison)
+PARTIAL_SUMS = os.environ.get("ATOMSERVE_B200_PARTIAL_SUMS", "1") != "0"
 
 
 def _plan(M: int, N: int, K: int) -> tuple[int, ...]:
@@ -124,7 +126,7 @@ def _plan(M: int, N: int, K: int) -> tuple[int, ...]:
 def linear_partial(x: torch.Tensor, w: torch.Tensor) -> PartialSums | None:
     """x . w^T left as partial sums, or None where the product does not run that way (many
     tokens, float32, another backend): the caller then takes `linear`."""
-    if BACKEND != "tcgen05" or x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or not x.is_cuda:
+    if not PARTIAL_SUMS or BACKEND != "tcgen05" or x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or not x.is_cuda:
         return None
     if x.dim() != 2 or w.dim() != 2 or x.shape[1] != w.shape[1] or not x.is_contiguous() or not w.is_contiguous():
         return None
@@ -137,6 +139,17 @@ def linear_partial(x: torch.Tensor, w: torch.Tensor) -> PartialSums | None:
     workspace = gemm_workspace(x.device, tiles * max_slots * 128 * tile_tokens)
     check(lib().asb_gemm_tcgen05(None, ptr(x), ptr(w), None, M, N, K, 3, ptr(workspace), ptr(gemm_status(x.device)), stream()))
     return PartialSums(workspace, M, N, max_slots, tile_tokens, k_blocks, tiles, blocks)
+
+
+def gemm_timeline(buffer: torch.Tensor | None) -> None:
+    """Profiling aid: while `buffer` (zeroed int64 [blocks + 1, 8] on the device; 160 rows are
+    enough) is set, each tensor-core GEMM call overwrites it with %globaltimer stamps in
+    nanoseconds: per block entry, set-up done, dependency wait over, first stage complete, last
+    MMA issued, last accumulator complete, epilogue done; and in the row after the last
+    block the reduction kernel's entry, wait over and end. None switches it off."""
+    fn = lib().asb_gemm_tcgen05_timeline
+    fn.argtypes, fn.restype = [ctypes.c_void_p], None
+    fn(ptr(buffer))
 
 
 def tcgen05_supported(x: torch.Tensor, w: torch.Tensor) -> bool:

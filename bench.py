@@ -313,6 +313,58 @@ def time_gemms(which: str, tokens: list[int], steps: int) -> None:
         del ws
 
 
+def gemm_timelines(which: str, tokens: list[int]) -> None:
+    """Where a decode-size GEMM call's time goes: %globaltimer stamps that every block of the
+    kernel writes (ops.linear.gemm_timeline), read after a CUDA-graph loop of calls on rotating
+    weights. One JSON line per (shape, tokens): microseconds after the first block's entry, as
+    [fastest, median, slowest] over the blocks."""
+    import torch
+
+    from atomserve_b200.ops.linear import check_gemm_status, gemm_tcgen05, gemm_timeline
+
+    c = QWEN3_8B
+    shapes = {
+        "qkv": ((c["num_attention_heads"] + 2 * c["num_key_value_heads"]) * c["head_dim"], c["hidden_size"]),
+        "o": (c["hidden_size"], c["num_attention_heads"] * c["head_dim"]),
+        "gate_up": (2 * c["intermediate_size"], c["hidden_size"]), "down": (c["hidden_size"], c["intermediate_size"]),
+    }  # fmt: skip
+    names = ["entry", "setup", "wait_over", "first_stage", "last_mma", "last_accumulator", "epilogue_done"]
+    for name, (N, K) in shapes.items():
+        if which not in ("all", name):
+            continue
+        ws = [(torch.randn(N, K, device="cuda") * 0.02).bfloat16() for _ in range(6)]
+        for M in tokens:
+            if M > 64:
+                continue
+            x = torch.randn(M, K, device="cuda").bfloat16()
+            stamps = torch.zeros(160, 8, dtype=torch.int64, device="cuda")
+            for i in range(3):
+                gemm_tcgen05(x, ws[i], None, torch.bfloat16)
+            torch.cuda.synchronize()
+            gemm_timeline(stamps)
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                for i in range(12):
+                    gemm_tcgen05(x, ws[i % 6], None, torch.bfloat16)
+            gemm_timeline(None)
+            stamps.zero_()
+            graph.replay()
+            torch.cuda.synchronize()
+            check_gemm_status()
+            host = stamps.cpu()
+            blocks = int((host[:, 0] > 0).sum()) - 1  # the row after the blocks holds the reduction's three stamps
+            per_block, reduction = host[:blocks].double(), host[blocks].double()
+            t0 = per_block[:, 0].min()
+            line = {"gemm": name, "tokens": M, "blocks": blocks}
+            for i, n in enumerate(names):
+                col = (per_block[:, i] - t0) / 1000.0
+                line[n] = [round(float(col.min()), 2), round(float(col.median()), 2), round(float(col.max()), 2)]
+            if reduction[1] > 0:
+                line["reduction"] = {k: round(float((reduction[i] - t0) / 1000.0), 2) for i, k in enumerate(["entry", "wait_over", "end"])}
+            print(json.dumps(line))
+        del ws
+
+
 def main() -> int:
     parser = argparse.ArgumentParser()
     parser.add_argument("--gpus", type=int, default=1)
@@ -330,6 +382,7 @@ def main() -> int:
     parser.add_argument("--budget", type=int, default=512, help="with --only serve: the scheduler's token budget per step")
     parser.add_argument("--gemm-shape", default="all", help="with --only gemm: qkv, o, gate_up, down, lm_head or all")
     parser.add_argument("--gemm-tokens", default="1,8,64,2048", help="with --only gemm: token counts, comma-separated")
+    parser.add_argument("--timeline", action="store_true", help="with --only gemm: where a decode-size call's time goes")
     args = parser.parse_args()
     args.layers_given = any(a == "--layers" or a.startswith("--layers=") for a in sys.argv[1:])
     if args.impl == "reference":
@@ -348,6 +401,9 @@ def main() -> int:
 
     require_device()
     pk = peaks()
+    if args.only == "gemm" and args.timeline:
+        gemm_timelines(args.gemm_shape, [int(t) for t in args.gemm_tokens.split(",")])
+        return 0
     if args.only == "gemm":
         time_gemms(args.gemm_shape, [int(t) for t in args.gemm_tokens.split(",")], max(args.steps // 4, 4))
         return 0
