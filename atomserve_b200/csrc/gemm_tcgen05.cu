@@ -8,9 +8,9 @@
 //
 // The kernel multiplies two K-major operands: P (rows become TMEM lanes, tile of 128) and Q
 // (rows become TMEM columns, tile of BN = 16..256). With many tokens P = x and Q = w. With few
-// tokens (decoding) the operands swap: P = w, so that the 128-row MMA shape is filled with
-// weight rows and the handful of tokens is the narrow N; the kernel then streams weights at
-// HBM speed with a deep TMA pipeline.
+// tokens (decoding, and up to 256 tokens on matrices of few rows) the operands swap: P = w, so
+// that the 128-row MMA shape is filled with weight rows and the tokens are its N; the kernel
+// then streams weights at HBM speed with a deep TMA pipeline (make_plan has the rule).
 //
 // The kernel is persistent: one block per SM walks a list of work segments (output tile, range
 // of K blocks), the TMA pipeline running on across segment boundaries. Two schedules: whole
@@ -18,7 +18,8 @@
 // equal contiguous range per block (few tokens), so that every SM streams the same number of
 // weight bytes whatever the number of tiles. A segment that covers all of K is stored
 // directly; one that covers a part writes float32 partial sums to a workspace slot, and
-// `segment_reduce_kernel` sums a tile's slots afterwards.
+// `segment_reduce_kernel` sums a tile's slots afterwards, unless the caller asked for the partial
+// sums themselves (csrc/gemm_partials.cuh).
 //
 // Warp roles (192 threads): warp 0 issues TMA loads, warp 1 allocates TMEM and issues MMAs,
 // warps 2-5 run the epilogue (warp w reads TMEM lanes 32*(w%4)..+31). Stages are handed over
@@ -168,7 +169,19 @@ __device__ __forceinline__ void umma(uint32_t tmem_d, uint64_t a, uint64_t b, ui
 __device__ __forceinline__ void umma_commit(uint32_t bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
 }
-__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
+// 32 lanes x N consecutive columns (N = 16 or 32): thread i of the warp gets lane (base lane + i).
+__device__ __forceinline__ void tmem_ld(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+        "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+        "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr));
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_ld(uint32_t taddr, uint32_t (&r)[16]) {
   asm volatile(
       "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
       : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
@@ -333,26 +346,21 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_cons
       if (!whole) {
         const long long total = (long long)p.num_tiles * p.kb_per_tile;
         const int first = block_of(total, gridDim.x, (long long)walk.tile * p.kb_per_tile);
-        // slot layout follows the output's contiguous dimension: [lane][column] when lanes are
-        // tokens, [column][lane] when lanes are output columns (swapped operands)
+        // a slot is laid out [column][lane] (csrc/gemm_partials.cuh)
         slot = p.workspace + ((size_t)walk.tile * p.max_slots + (blockIdx.x - first)) * BM * BN;
       }
-      constexpr int kChunk = 16;
+      constexpr int kChunk = BN >= 32 ? 32 : 16;  // columns read from tensor memory at a time
 #pragma unroll 1
       for (int c = 0; c < BN; c += kChunk) {
         if (q0 + c >= p.q_rows) break;  // uniform: depends on the segment and c only
-        uint32_t raw[16];
-        tmem_ld16(tmem_base + ((uint32_t)(quad * 32) << 16) + buf * BN + (uint32_t)c, raw);
+        uint32_t raw[kChunk];
+        tmem_ld(tmem_base + ((uint32_t)(quad * 32) << 16) + buf * BN + (uint32_t)c, raw);
         if (!whole) {  // partial sums; rows beyond the matrix hold zeros
           const int row = quad * 32 + lane;
-          if (p.swap) {
+          // K is cut only with swapped operands: lanes are output columns, and a warp's 32 lanes
+          // store 128 contiguous bytes of the slot's [column][lane] layout per instruction
 #pragma unroll
-            for (int j = 0; j < kChunk; ++j) slot[(size_t)(c + j) * BM + row] = __uint_as_float(raw[j]);
-          } else {
-#pragma unroll
-            for (int j = 0; j < kChunk; j += 4)
-              *reinterpret_cast<uint4*>(slot + (size_t)row * BN + c + j) = make_uint4(raw[j], raw[j + 1], raw[j + 2], raw[j + 3]);
-          }
+          for (int j = 0; j < kChunk; ++j) slot[(size_t)(c + j) * BM + row] = __uint_as_float(raw[j]);
           continue;
         }
         if (p.epilogue == kStoreSwiGLU) {
@@ -367,16 +375,17 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_cons
                 ((__nv_bfloat16*)p.out)[(size_t)tok * (p.ldo / 2) + prow / 2] = __float2bfloat16_rn(swiglu(__uint_as_float(raw[j]), up));
             }
           } else if (prow < p.p_rows) {
-            // columns are weight rows: this thread holds eight (gate, up) pairs of its token
+            // columns are weight rows: this thread holds kChunk / 2 (gate, up) pairs of its token
             __nv_bfloat16* o = (__nv_bfloat16*)p.out + (size_t)prow * (p.ldo / 2) + (q0 + c) / 2;
             const int valid = min(kChunk, p.q_rows - (q0 + c)) / 2;
-            uint4 packed;
-            __nv_bfloat16* ob = reinterpret_cast<__nv_bfloat16*>(&packed);
+            uint4 packed[kChunk / 16];
+            __nv_bfloat16* ob = reinterpret_cast<__nv_bfloat16*>(packed);
 #pragma unroll
             for (int j = 0; j < kChunk / 2; ++j)
               ob[j] = __float2bfloat16_rn(swiglu(__uint_as_float(raw[2 * j]), __uint_as_float(raw[2 * j + 1])));
             if (valid == kChunk / 2 && (((uintptr_t)o) & 15) == 0) {
-              *reinterpret_cast<uint4*>(o) = packed;
+#pragma unroll
+              for (int v = 0; v < kChunk / 16; ++v) *reinterpret_cast<uint4*>(o + 8 * v) = packed[v];
             } else {
 #pragma unroll
               for (int j = 0; j < kChunk / 2; ++j)
@@ -421,13 +430,13 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_cons
             __nv_bfloat16* o = (__nv_bfloat16*)p.out + at;
             const __nv_bfloat16* res = p.epilogue == kStoreBf16Residual ? (const __nv_bfloat16*)p.residual + at : nullptr;
             if (valid == kChunk && (((uintptr_t)o) & 15) == 0 && (!res || (((uintptr_t)res) & 15) == 0)) {
-              uint4 rv[2];
+              uint4 rv[kChunk / 8];
               if (res) {
-                rv[0] = *reinterpret_cast<const uint4*>(res);
-                rv[1] = *reinterpret_cast<const uint4*>(res + 8);
+#pragma unroll
+                for (int v = 0; v < kChunk / 8; ++v) rv[v] = *reinterpret_cast<const uint4*>(res + 8 * v);
               }
               const __nv_bfloat16* rb = reinterpret_cast<const __nv_bfloat16*>(rv);
-              uint4 ov[2];
+              uint4 ov[kChunk / 8];
               __nv_bfloat162* ob = reinterpret_cast<__nv_bfloat162*>(ov);
 #pragma unroll
               for (int j = 0; j < kChunk; j += 2) {
@@ -435,8 +444,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_cons
                 if (res) { a += __bfloat162float(rb[j]); b += __bfloat162float(rb[j + 1]); }
                 ob[j >> 1] = __floats2bfloat162_rn(a, b);
               }
-              *reinterpret_cast<uint4*>(o) = ov[0];
-              *reinterpret_cast<uint4*>(o + 8) = ov[1];
+#pragma unroll
+              for (int v = 0; v < kChunk / 8; ++v) *reinterpret_cast<uint4*>(o + 8 * v) = ov[v];
             } else {
 #pragma unroll
               for (int j = 0; j < kChunk; ++j)
@@ -504,25 +513,24 @@ __global__ void segment_reduce_kernel(const GemmParams p, int parts) {
   }
   const float e[4] = {v.x, v.y, v.z, v.w};
   if (p.epilogue == kStoreSwiGLU) {
-    // the four sums are two (gate, up) pairs along the weight-row dimension, which is the slot's
-    // contiguous one in both layouts
+    // the four sums are two (gate, up) pairs along the weight-row dimension, the slot's contiguous one
 #pragma unroll
     for (int k = 0; k < 4; k += 2) {
-      const int row = p.swap ? (i + k) % BM : (i + k) / BN, col = p.swap ? (i + k) / BM : (i + k) % BN;
+      const int row = (i + k) % BM, col = (i + k) / BM;
       const int prow = p0 + row, qrow = q0 + col;
       if (prow >= p.p_rows || qrow >= p.q_rows) continue;
-      const size_t at = p.swap ? (size_t)qrow * (p.ldo / 2) + prow / 2 : (size_t)prow * (p.ldo / 2) + qrow / 2;
+      const size_t at = (size_t)qrow * (p.ldo / 2) + prow / 2;
       ((__nv_bfloat16*)p.out)[at] = __float2bfloat16_rn(swiglu(e[k], e[k + 1]));
     }
     return;
   }
 #pragma unroll
   for (int k = 0; k < 4; ++k) {
-    // slot layout: [column][lane] when swapped, [lane][column] otherwise
-    const int row = p.swap ? (i + k) % BM : (i + k) / BN, col = p.swap ? (i + k) / BM : (i + k) % BN;
+    // slot layout [column][lane]: lanes are output columns (weight rows), columns are tokens
+    const int row = (i + k) % BM, col = (i + k) / BM;
     const int prow = p0 + row, qrow = q0 + col;
     if (prow >= p.p_rows || qrow >= p.q_rows) continue;
-    const size_t at = p.swap ? (size_t)qrow * p.ldo + prow : (size_t)prow * p.ldo + qrow;
+    const size_t at = (size_t)qrow * p.ldo + prow;
     float o = e[k];
     if (p.epilogue == kStoreF32) {
       ((float*)p.out)[at] = o;
@@ -582,14 +590,19 @@ struct Plan {
   long long workspace;  // float32 elements
 };
 
-// How a shape is run. Operands swap at up to 64 tokens. One block runs per SM. Whole tiles are
-// dealt round-robin unless cutting the flattened K-block sequence into equal ranges shortens
-// the busiest SM's share of the operand stream by more than the partial sums cost to write and
-// read back.
+// How a shape is run. One block runs per SM. Operands swap (weights fill the 128-row MMA, tokens
+// are its N = 16..256) for up to 32 tokens always, and for up to 256 tokens where the unswapped
+// tiles of 128 x 256 would leave over half of the SMs idle (few weight rows: qkv, o, down); where
+// they fill the machine (gate/up, the head) whole unswapped tiles win from 33 tokens on (measured
+// on the 8B and 14B shapes). With swapped operands, whole tiles are dealt round-robin unless
+// cutting the flattened K-block sequence into equal ranges shortens the busiest SM's share of the
+// operand stream by more than the partial sums cost to write and read back; unswapped tiles are
+// never cut (their partial sums, 128 KB a tile, cost more than the idle SMs: measured).
 Plan make_plan(int M, int N, int K) {
   Plan pl;
-  pl.swap = M <= 64 ? 1 : 0;
-  pl.bn = pl.swap ? (M <= 16 ? 16 : (M <= 32 ? 32 : 64)) : (N <= 128 ? 128 : 256);
+  const int unswapped_tiles = ((M + BM - 1) / BM) * ((N + 255) / 256);
+  pl.swap = M <= 32 || (M <= 256 && 2 * unswapped_tiles < sm_count()) ? 1 : 0;
+  pl.bn = pl.swap ? (M <= 16 ? 16 : (M <= 32 ? 32 : (M <= 64 ? 64 : (M <= 128 ? 128 : 256)))) : (N <= 128 ? 128 : 256);
   const int p_rows = pl.swap ? N : M, q_rows = pl.swap ? M : N;
   pl.tiles_p = (p_rows + BM - 1) / BM;
   pl.tiles_q = (q_rows + pl.bn - 1) / pl.bn;
@@ -609,7 +622,7 @@ Plan make_plan(int M, int N, int K) {
   const double stream_cost = per_block + partial_bytes / kb_bytes / stream_blocks;
   // (measured: one SM draws about 60 GB/s however deep its pipeline, so few tiles never fill the
   // device without cutting K; many tiles in nearly whole waves are best left whole)
-  pl.stream = pl.swap && stream_cost < whole_cost * 0.97 ? 1 : 0;  // partial tiles of many tokens are too large to pay
+  pl.stream = pl.swap && stream_cost < whole_cost * 0.97 ? 1 : 0;
   pl.blocks = pl.stream ? stream_blocks : whole_blocks;
   pl.max_slots = 0;
   pl.workspace = 0;

@@ -334,8 +334,6 @@ def gemm_timelines(which: str, tokens: list[int]) -> None:
             continue
         ws = [(torch.randn(N, K, device="cuda") * 0.02).bfloat16() for _ in range(6)]
         for M in tokens:
-            if M > 64:
-                continue
             x = torch.randn(M, K, device="cuda").bfloat16()
             stamps = torch.zeros(160, 8, dtype=torch.int64, device="cuda")
             for i in range(3):

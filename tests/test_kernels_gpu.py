@@ -346,6 +346,7 @@ def test_presence_penalty(ops):
 GEMM_SHAPES = [
     (1, 128, 64), (3, 100, 72), (16, 256, 512), (17, 384, 4096), (33, 130, 1024), (64, 4096, 4096),
     (8, 4096, 12288), (65, 256, 128), (128, 300, 264), (300, 512, 1000), (2048, 1024, 512),
+    (200, 4096, 1024), (256, 512, 2048), (100, 24576, 256), (40, 20000, 128),
 ]  # fmt: skip
 
 
@@ -434,7 +435,7 @@ def test_gemm_tcgen05_swiglu(ops, M, I, K):
 
 
 PARTIAL_NORM_SHAPES = [(1, 4096, 4096), (8, 4096, 12288), (5, 1024, 2048), (16, 640, 1024), (33, 2048, 4096),
-                       (64, 4096, 4096), (7, 5120, 17408), (3, 264, 2048)]  # fmt: skip
+                       (64, 4096, 4096), (7, 5120, 17408), (3, 264, 2048), (100, 4096, 4096), (200, 1024, 2048)]  # fmt: skip
 
 
 @pytest.mark.parametrize("M,N,K", PARTIAL_NORM_SHAPES)
@@ -475,14 +476,14 @@ def test_linear_partial_declines_what_does_not_cut_k(ops):
 
 
 @pytest.mark.parametrize("H,KV,hd,K", [(8, 2, 128, 2048), (32, 8, 128, 4096), (4, 2, 64, 1024), (6, 3, 32, 2048), (2, 1, 256, 1024), (8, 0, 128, 2048)])
-@pytest.mark.parametrize("T", [1, 6, 40])
+@pytest.mark.parametrize("T", [1, 6, 40, 150])
 def test_qk_norm_rope_store_from_partial_sums(ops, H, KV, hd, K, T):
     """q/k norm, rotation and the cache write reading the qkv product from the GEMM's partial
     sums: the same bits as from the reduced product (KV = 0: queries only, nothing stored)."""
     from atomserve_b200.ops.linear import check_gemm_status
 
     g = torch.Generator().manual_seed(H * 100 + hd + T)
-    bs, nblocks = 16, 8
+    bs, nblocks = 16, 12
     x = torch.randn(T, K, generator=g).bfloat16().cuda()
     w = (torch.randn((H + 2 * KV) * hd, K, generator=g) / math.sqrt(K)).bfloat16().cuda()
     qg, kg = ((1 + 0.1 * torch.randn(hd, generator=g)).cuda() for _ in range(2))
