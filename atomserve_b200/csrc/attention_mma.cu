@@ -666,6 +666,30 @@ int launch_mma(const MmaParams& p, int run_decode, int run_prefill, cudaStream_t
 
 }  // namespace
 
+// How many blocks of the decode kernel the device holds at once (blocks per SM x SMs), which is
+// what the caller's choice of key partitions aims to fill evenly; 0 for a head size not served.
+extern "C" int asb_decode_attention_resident_blocks(int hd) {
+  if (hd != 64 && hd != 128) return 0;
+  static int cached[2] = {0, 0};
+  int& slot = cached[hd == 128];
+  if (slot) return slot;
+  int device = 0, sms = 0, per_sm = 0;
+  if (cudaGetDevice(&device) != cudaSuccess ||
+      cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device) != cudaSuccess)
+    return 0;
+  const int smem = 4 * kKeyTile * hd * 2 + 16 * hd * 2;
+  cudaError_t e;
+  if (hd == 64) {
+    cudaFuncSetAttribute(decode_attention_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, decode_attention_kernel<64>, kThreads, smem);
+  } else {
+    cudaFuncSetAttribute(decode_attention_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, decode_attention_kernel<128>, kThreads, smem);
+  }
+  if (e != cudaSuccess || per_sm < 1) return 0;
+  return slot = per_sm * sms;
+}
+
 // 1 if this (head size, group) is served by the tensor-core kernels.
 extern "C" int asb_attention_mma_supported(int hd, int group) {
   return (hd == 64 || hd == 128) && group >= 1 ? 1 : 0;

@@ -73,6 +73,7 @@ class ModelRunner:
         self.use_graphs = cuda_graphs and self.device.type == "cuda" and not cache.entry_state
         self._copy_done: torch.cuda.Event | None = None
         self._graphs: dict[tuple, tuple] = {}
+        self._graph_pool = None
         # request uid -> (generation, per group a numpy copy of its block table, extended as it grows)
         self._tables: dict[int, tuple[int, list[np.ndarray]]] = {}
         self._host: torch.Tensor | None = None
@@ -255,9 +256,10 @@ class ModelRunner:
         if wanted == len(rows) and len(rows) <= self.GRAPH_BATCHES[-1]:
             pad_r = next(b for b in self.GRAPH_BATCHES if b >= len(rows))
         ctx, groups, key = self.prepare(rows, pad_requests=pad_r, pad_width=pad_w)
-        ctx_bucket = 256
-        while ctx_bucket < ctx.max_context:
-            ctx_bucket *= 2
+        # the longest context rounded up by at most an eighth or so: the attention kernels size their
+        # key partitions for the rounded value, so a coarse bucket would leave partitions empty
+        step = 256 if ctx.max_context <= 2048 else (512 if ctx.max_context <= 8192 else 1024)
+        ctx_bucket = -(-ctx.max_context // step) * step
         ctx.max_context = ctx_bucket
         key = (*key, ctx_bucket)
         self._bind(groups)
@@ -267,8 +269,12 @@ class ModelRunner:
             self.model.forward(ctx, self.views)
             torch.cuda.synchronize()
             graph = torch.cuda.CUDAGraph()
+            if self._graph_pool is None:
+                # one memory pool for all graphs: only one of them runs at a time, and each step's
+                # logits are read before the next step
+                self._graph_pool = torch.cuda.graph_pool_handle()
             before = launches()
-            with torch.cuda.graph(graph):
+            with torch.cuda.graph(graph, pool=self._graph_pool):
                 out = self.model.forward(ctx, self.views)
             entry = (graph, out, launches() - before)
             self._graphs[key] = entry

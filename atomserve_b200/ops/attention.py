@@ -3,6 +3,7 @@
 from __future__ import annotations
 
 import ctypes
+import functools
 import os
 
 import torch
@@ -12,7 +13,6 @@ from atomserve_b200.ops.library import KernelLibraryError, check, dtype_code, li
 KEY_TILE = 32
 TARGET_BLOCKS = 296  # two blocks for each of the 148 SMs before the key range is split
 SHORT_ROWS = 8  # requests with at most this many new tokens run row by row in the decode kernel
-DECODE_TARGET_BLOCKS = 8 * 3 * 148  # eight waves of three resident blocks per SM: a ragged last wave costs little
 
 
 # Which kernel serves prompt portions in bfloat16 with head size 128: "tcgen05" (scores and output
@@ -47,20 +47,32 @@ def plan_partitions(num_tokens: int, num_requests: int, num_kv_heads: int, group
     return (size, parts) if parts > 1 else (1 << 30, 1)
 
 
-def plan_decode_partitions(rows: int, num_kv_heads: int, group: int, max_context: int, window: int) -> tuple[int, int]:
-    """(partition size, partitions) for the tensor-core decode kernel: one block per (row, kv
-    head, partition); keys are split until there are several waves of blocks (the last, partly
-    filled wave then wastes little), never below 256 keys a block."""
+@functools.lru_cache(maxsize=4096)
+def plan_decode_partitions(rows: int, num_kv_heads: int, group: int, max_context: int, window: int,
+                           head_dim: int = 128) -> tuple[int, int]:  # fmt: skip
+    """(partition size, partitions) for the tensor-core decode kernel, one block per (row, kv
+    head, partition). The device holds a fixed number of its blocks at once, so the blocks run in
+    waves; the choice minimises waves x (64-key tiles per block + 3 tiles' worth of start-up) plus
+    half a tile per partition for the merge, which is what a sweep over batch 4-128 and context
+    1k-8k fitted: small batches want one nearly full wave, large ones two to five, and a count
+    that spills a few blocks into one more wave is the worst. Never below 256 keys a block."""
     blocks = rows * num_kv_heads * -(-group // 16)
     span = max_context if window <= 0 else min(max_context, window)
-    if blocks >= DECODE_TARGET_BLOCKS or span <= 256:
-        return 1 << 30, 1
-    want = -(-DECODE_TARGET_BLOCKS // blocks)
-    size = max(256, -(-(-(-span // want)) // 64) * 64)
-    if window <= 0:
-        parts = (max_context - 1) // size + 1
-    else:
-        parts = min((max_context - 1) // size + 1, -(-span // size) + 1)
+    resident = lib().asb_decode_attention_resident_blocks(head_dim) or 3 * 148
+    best = None
+    for want in range(1, max(1, span // 256) + 1):
+        size = max(256, -(-(-(-span // want)) // 64) * 64)
+        if window <= 0:
+            parts = (max_context - 1) // size + 1
+        else:
+            parts = min((max_context - 1) // size + 1, -(-span // size) + 1)
+        waves = -(-blocks * parts // resident)
+        cost = waves * (size // 64 + 3) + 0.5 * parts
+        if best is None or cost < best[0]:
+            best = (cost, size, parts)
+        if want > 64:
+            break
+    _, size, parts = best
     return (size, parts) if parts > 1 else (1 << 30, 1)
 
 
@@ -151,7 +163,7 @@ def _paged_attention_mma(q, out, k_cache, v_cache, block_tables, req_q_start, re
         return out
     ps, np_ = 1 << 30, 1
     if has_short and not has_long:
-        ps, np_ = partitions or plan_decode_partitions(short_rows, KV, H // KV, max_context, win)
+        ps, np_ = partitions or plan_decode_partitions(short_rows, KV, H // KV, max_context, win, hd)
     part_m = part_l = part_acc = None
     if np_ > 1:
         part_m = torch.empty(T * H * np_, device=q.device, dtype=torch.float32)

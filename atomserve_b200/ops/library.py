@@ -37,6 +37,7 @@ _SIGNATURES = {
     "asb_attention_tcgen05_supported": [_I, _I, _I],
     "asb_attention_reduce": [_P, _P, _P, _P, _I, _I, _I, _I, _P],
     "asb_attention_mma_supported": [_I, _I],
+    "asb_decode_attention_resident_blocks": [_I],
     "asb_gemm_tcgen05": [_P, _P, _P, _P, _I, _I, _I, _I, _P, _P, _P],
     "asb_gemm_tcgen05_plan": [_I, _I, _I, _P],
     "asb_partial_add_rmsnorm": [_P, _P, _P, _I, _I, _I, _I, _I, _P, _P, _I, _I, _F, _P],
