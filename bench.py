@@ -313,6 +313,62 @@ def time_gemms(which: str, tokens: list[int], steps: int) -> None:
         del ws
 
 
+def attention_partition_sweep(batches: list[int], contexts: list[int]) -> None:
+    """Device time of the decode attention kernel plus its partition merge for every number of key
+    partitions, per (batch, context), at the 8B shape's heads; one JSON line each, with the plan
+    that the engine's planner picks. CUDA-graph loop, microseconds."""
+    import torch
+
+    from atomserve_b200 import ops
+    from atomserve_b200.ops.attention import plan_decode_partitions
+
+    c = QWEN3_8B
+    H, KV, hd, bs = c["num_attention_heads"], c["num_key_value_heads"], c["head_dim"], BLOCK_SIZE
+    for B in batches:
+        for ctx in contexts:
+            pages = -(-ctx // bs)
+            blocks = B * pages + 1
+            if blocks * KV * bs * hd * 2 * 2 > 24e9:
+                continue
+            k = (torch.randn(blocks, KV, bs, hd, device="cuda") * 0.5).bfloat16()
+            v = (torch.randn(blocks, KV, bs, hd, device="cuda") * 0.5).bfloat16()
+            tables = torch.randperm(blocks - 1, device="cuda")[: B * pages].int().view(B, pages).contiguous()
+            q = torch.randn(B, H, hd, device="cuda").bfloat16()
+            q_start = torch.arange(B + 1, dtype=torch.int32, device="cuda")
+            pos = torch.full((B,), ctx - 1, dtype=torch.int32, device="cuda")
+            times = {}
+            for want in range(1, 33):
+                size = max(256, -(-(-(-ctx // want)) // 64) * 64)
+                parts = (ctx - 1) // size + 1
+                if parts in times:
+                    continue
+                plan = (size, parts) if parts > 1 else (1 << 30, 1)
+
+                def run():
+                    return ops.paged_attention(q, k, v, tables, q_start, pos, num_requests=B, max_context=ctx, window=None,
+                                               scale=hd**-0.5, partitions=plan, host_q_lens=[1] * B)  # fmt: skip
+
+                run()
+                torch.cuda.synchronize()
+                graph = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(graph):
+                    for _ in range(10):
+                        run()
+                graph.replay()
+                torch.cuda.synchronize()
+                start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                start.record()
+                graph.replay()
+                end.record()
+                torch.cuda.synchronize()
+                times[parts] = round(start.elapsed_time(end) * 100, 1)
+            planned = plan_decode_partitions(B, KV, H // KV, ctx, 0, hd)
+            print(json.dumps({"attention": "decode", "batch": B, "context": ctx,
+                              "ideal_us": round(B * ctx * KV * hd * 2 * 2 / 7.3e12 * 1e6, 1),
+                              "planned_parts": planned[1], "us_by_parts": times}))  # fmt: skip
+            del k, v
+
+
 def gemm_timelines(which: str, tokens: list[int]) -> None:
     """Where a decode-size GEMM call's time goes: %globaltimer stamps that every block of the
     kernel writes (ops.linear.gemm_timeline), read after a CUDA-graph loop of calls on rotating
@@ -372,7 +428,7 @@ def main() -> int:
                         help="fewer layers than the model has (same layer sizes), where time or memory needs it")  # fmt: skip
     parser.add_argument("--batch", type=int, default=8)
     parser.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    parser.add_argument("--only", choices=["decode", "prefill", "gemm", "serve"], help="time just this (for profiling small cases and the other shapes)")
+    parser.add_argument("--only", choices=["decode", "prefill", "gemm", "serve", "attention"], help="time just this (for profiling small cases and the other shapes)")
     parser.add_argument("--shape", default="8b", choices=sorted(SHAPES), help="with --only decode/prefill/serve: layer sizes of Qwen3-8B, -14B or -32B")
     parser.add_argument("--context", type=int, default=PROMPT_TOKENS, help="with --only decode: tokens each request holds when decoding starts")
     parser.add_argument("--requests", type=int, default=32, help="with --only serve: requests submitted at once")
@@ -399,6 +455,9 @@ def main() -> int:
 
     require_device()
     pk = peaks()
+    if args.only == "attention":
+        attention_partition_sweep([4, 8, 16, 32, 64, 128], [2048, 8192])
+        return 0
     if args.only == "gemm" and args.timeline:
         gemm_timelines(args.gemm_shape, [int(t) for t in args.gemm_tokens.split(",")])
         return 0
