@@ -54,14 +54,25 @@ def check_gemm_status(device: torch.device | str = "cuda") -> None:
 
 
 _WORKSPACE: dict[torch.device, torch.Tensor] = {}
+_OUTGROWN: list[torch.Tensor] = []
 
 
 def gemm_workspace(device: torch.device, floats: int) -> torch.Tensor:
     """One float32 buffer per device for the partial sums of tensor-core GEMM calls that cut K
-    (they run on one stream, one after another, so they can share it). Grown, never shrunk."""
+    (they run on one stream, one after another, so they can share it). Grown when a call needs
+    more, to at least twice the size; a buffer that was outgrown is kept, not freed, because CUDA
+    graphs captured while it was current still write and read their partial sums there."""
     buf = _WORKSPACE.get(device)
     if buf is None or buf.numel() < floats:
-        buf = torch.zeros(max(floats, 1 << 22), device=device, dtype=torch.float32)
+        if buf is not None:
+            _OUTGROWN.append(buf)
+        size = max(floats, 1 << 24, 2 * buf.numel() if buf is not None else 0)
+        if torch.cuda.is_current_stream_capturing():
+            # allocated here it would belong to the graph being captured and be reused by it
+            raise KernelLibraryError(
+                f"the GEMM workspace must grow to {size} floats during a graph capture: run the step once outside capture first"
+            )
+        buf = torch.zeros(size, device=device, dtype=torch.float32)
         _WORKSPACE[device] = buf
     return buf
 

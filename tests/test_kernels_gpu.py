@@ -507,3 +507,28 @@ def test_qk_norm_rope_store_from_partial_sums(ops, H, KV, hd, K, T):
     for a, b in zip(*results):
         assert torch.equal(a, b)
     assert float(results[1][0].float().abs().max()) > 0
+
+
+def test_captured_gemm_survives_workspace_growth(ops):
+    """A CUDA graph captured while the GEMM's partial-sum workspace was small keeps working after
+    a larger call has replaced it: the outgrown buffer stays alive for the graphs that use it."""
+    from atomserve_b200.ops import linear as L
+
+    g = torch.Generator().manual_seed(5)
+    x = torch.randn(8, 4096, generator=g).bfloat16().cuda()
+    w = (torch.randn(4096, 4096, generator=g) / 64).bfloat16().cuda()
+    expect = L.gemm_tcgen05(x, w, None, torch.bfloat16).clone()
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        out = L.gemm_tcgen05(x, w, None, torch.bfloat16)
+    before = L.gemm_workspace(x.device, 1)
+    L.gemm_workspace(x.device, before.numel() + 1)  # a larger call comes along
+    assert L.gemm_workspace(x.device, 1) is not before
+    junk = [torch.full((before.numel(),), float("nan"), device="cuda") for _ in range(2)]  # would land in freed memory
+    out.zero_()
+    graph.replay()
+    torch.cuda.synchronize()
+    assert torch.equal(out, expect)
+    del junk
+    L.check_gemm_status()
