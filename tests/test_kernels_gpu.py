@@ -512,8 +512,9 @@ def test_qk_norm_rope_store_from_partial_sums(ops, H, KV, hd, K, T):
 def test_captured_gemm_survives_workspace_growth(ops):
     """A CUDA graph captured while the GEMM's partial-sum workspace was small keeps working after
     a larger call has replaced it: the outgrown buffer stays alive for the graphs that use it."""
-    from atomserve_b200.ops import linear as L
+    import importlib
 
+    L = importlib.import_module("atomserve_b200.ops.linear")  # `ops.linear` itself is the function
     g = torch.Generator().manual_seed(5)
     x = torch.randn(8, 4096, generator=g).bfloat16().cuda()
     w = (torch.randn(4096, 4096, generator=g) / 64).bfloat16().cuda()
