@@ -33,13 +33,14 @@ MAX_LIVE_REQUESTS = 8
 
 class TraceReplayer:
     def __init__(self, model_dir: str | Path, dtype: str, max_tokens: int, block_size: int = 16,
-                 device: str = "cuda", cuda_graphs: bool = True):  # fmt: skip
+                 device: str = "cuda", cuda_graphs: bool = True, max_live: int = MAX_LIVE_REQUESTS):  # fmt: skip
         _, self.config, self.model = load_model(model_dir, dtype, device)
         requirements = self.model.cache_requirements()
         # --max-tokens counts what live requests hold, each rounded up to whole pages of 64
         # tokens; with pages of `block_size` (a divisor of 64) that is this many pages.
         num_blocks = -(-max_tokens // block_size)
-        self.cache = CacheManager(requirements, block_size, num_blocks, MAX_LIVE_REQUESTS,
+        self.max_live = max_live  # requests that may hold pages and a state slot at once
+        self.cache = CacheManager(requirements, block_size, num_blocks, max_live,
                                   parse_dtype(dtype), device)  # fmt: skip
         self.runner = ModelRunner(self.model, self.cache, cuda_graphs=cuda_graphs)
         self.live: dict[str, tuple[RequestCache, int]] = {}  # id -> (cache, tokens computed)
@@ -51,7 +52,7 @@ class TraceReplayer:
             if rid not in self.live:
                 rc = self.cache.new_request()
                 if not self.cache.admit(rc):
-                    raise RuntimeError(f"more than {MAX_LIVE_REQUESTS} requests are live")
+                    raise RuntimeError(f"more than {self.max_live} requests are live")
                 self.live[rid] = (rc, 0)
             rc, computed = self.live[rid]
             tokens = [int(t) for t in e["tokens"]]

@@ -48,10 +48,10 @@ class Oracle:
 BF16_REPORT: list[tuple[str, float]] = []  # (what, error / allowance) of every bfloat16 check
 
 
-def replayer(folder, dtype, bs, max_tokens, graphs=True):
+def replayer(folder, dtype, bs, max_tokens, graphs=True, **more):
     from atomserve_b200.engine.replay import TraceReplayer
 
-    return TraceReplayer(folder, dtype, max_tokens, bs, cuda_graphs=graphs)
+    return TraceReplayer(folder, dtype, max_tokens, bs, cuda_graphs=graphs, **more)
 
 
 def check(got, oracle, dtype, what):
@@ -170,6 +170,29 @@ def test_long_decoding(models, dtype):
                 logits = rp.step([dict(id="x", tokens=[t], want=[0])], end=[])
                 if j % 7 == 0 or j > 290:
                     check(logits, ref[j : j + 1], dtype, f"{name} decode position {j} graphs={graphs}")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name,live", [("a", 70), ("d", 150)])
+def test_many_requests_decode_together(models, name, live, dtype):
+    """70 and 150 live requests of different lengths: their prompts in a few mixed steps, then
+    single tokens of all of them in one step each (the batch sizes where the GEMM runs its
+    medium-token shapes and the decode graphs their large buckets)."""
+    cfg, bs, folder, _, _ = models[name]
+    w = checkpoint(cfg, seed=21)
+    lengths = [3 + (7 * i) % 23 for i in range(live)]
+    ps = prompts(cfg, [n + 3 for n in lengths], seed=11)  # three more tokens each, fed one by one
+    rp = replayer(folder, dtype, bs, live * 64, max_live=live)
+    for first in range(0, live, 40):  # prompts, forty requests a step
+        ids = range(first, min(first + 40, live))
+        rp.step([dict(id=str(i), tokens=ps[i][: lengths[i]], want=[]) for i in ids], end=[])
+    refs = {i: Oracle(w, cfg, ps[i]) for i in range(0, live, 13)}  # a sample of the requests is checked
+    for k in range(3):
+        logits = rp.step([dict(id=str(i), tokens=[ps[i][lengths[i] + k]], want=[0]) for i in range(live)], end=[])
+        assert logits.shape[0] == live
+        for i, ref in refs.items():
+            at = lengths[i] + k
+            check(logits[i : i + 1], ref[at : at + 1], dtype, f"{name} {live} live, request {i} position {at}")
 
 
 def test_window_pages_are_given_back(models):
