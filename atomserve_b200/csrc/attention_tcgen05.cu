@@ -18,15 +18,14 @@
 //              memory are keys, exactly as the pages hold them.
 //   warps 2-5  softmax: thread r owns row r (a TMEM lane), so row maxima and sums need no
 //              shuffles. It reads its scores once, rescales its row of O in tensor memory only when
-//              the maximum moved by more than a factor of 256, writes P as bfloat16 into one of two
-//              shared-memory buffers in the swizzled K-major layout, and at the end stores O / sum.
-//              With two P buffers it waits for the previous P V only when it has to rescale, so
-//              softmax and tensor cores work on different tiles at the same time.
+//              the maximum moved by more than a factor of 256, writes P as bfloat16 into the
+//              shared-memory P buffer in the swizzled K-major layout (once the previous P V has
+//              read it), and at the end stores O / sum.
 //
-// Shared memory: Q 32 KB, five stages of (K 16 KB + V 16 KB), so that loads run several tiles
-// ahead of their use (a TMA load takes longer than a tile's arithmetic), P 2 x 16 KB. Tensor memory:
-// two score buffers of 64 columns and the output accumulator of 128. All barrier waits are bounded; a wait
-// that runs out sets *status and the roles wind down to the final barrier.
+// Shared memory: Q 32 KB, two stages of (K 16 KB + V 16 KB), P 16 KB: 112 KB, so that two blocks
+// share an SM and one's softmax overlaps the other's MMAs. Tensor memory: two score buffers of 64
+// columns and the output accumulator of 128, 256 columns a block. All barrier waits are bounded;
+// a wait that runs out sets *status and the roles wind down to the final barrier.
 #include "tcgen05.cuh"
 
 namespace {
@@ -42,9 +41,16 @@ constexpr int kQBytes = 2 * kBlockBytes;          // Q: the two 64-element halve
 constexpr int kKVBlockBytes = kKeys * 64 * 2;     // one [kKeys rows][64 elements] block: 8 KB
 constexpr int kKVBytes = 2 * kKVBlockBytes;       // K or V of a tile: two halves of the head
 constexpr int kStageBytes = 2 * kKVBytes;         // K and V
-constexpr int kStages = 5;                        // K/V tiles in flight: TMA latency is several tiles long
+// Two K/V stages and one P buffer keep a block's shared memory at 112 KB, so that two blocks share
+// an SM: while one block's softmax runs, the other's MMAs do (one block per SM with five stages and
+// two P buffers left the tensor cores waiting on the softmax-to-MMA hand-offs: 112 us against
+// 103 us at 2,048 tokens, 334 against 296 us at 4,096). The MMA warp looks one tile ahead, so at
+// least two stages.
+constexpr int kStages = 2;                        // K/V tiles in flight
+constexpr int kPBuffers = 1;                      // P buffers
+static_assert(kStages >= 2, "Q K^T of the next tile is issued while this tile's K/V are still in use");
 constexpr int kPBytes = (kKeys / 64) * kBlockBytes;  // one P buffer: [128 rows][kKeys] in blocks of 64 keys
-constexpr int kSmem = kQBytes + kStages * kStageBytes + 2 * kPBytes + 1024;  // two P buffers
+constexpr int kSmem = kQBytes + kStages * kStageBytes + kPBuffers * kPBytes + 256;  // tiles, then barriers
 constexpr uint32_t kTmemCols = 256;               // two score buffers of kKeys columns, 128 of output
 constexpr int kShortRows = 8;
 
@@ -66,29 +72,29 @@ __device__ __forceinline__ float fast_exp2(float x) {
   return y;
 }
 
-__global__ void __launch_bounds__(kThreads, 1)
+__global__ void __launch_bounds__(kThreads, 2)
 prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                                  const __grid_constant__ CUtensorMap map_v, const AttnParams p) {
-  extern __shared__ unsigned char smem_raw[];
-  const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
-  unsigned char* aligned = smem_raw + (base - smem_u32(smem_raw));
+  extern __shared__ __align__(1024) unsigned char smem_raw[];  // the swizzled tiles need this alignment
+  const uint32_t base = smem_u32(smem_raw);
+  unsigned char* aligned = smem_raw;
   const uint32_t q_smem = base;
   auto k_smem = [&](int s) { return base + kQBytes + (uint32_t)s * kStageBytes; };
   auto v_smem = [&](int s) { return base + kQBytes + (uint32_t)s * kStageBytes + kKVBytes; };
   const uint32_t p_smem = base + kQBytes + kStages * kStageBytes;
   unsigned char* p_ptr = aligned + kQBytes + kStages * kStageBytes;
-  const uint32_t bars = p_smem + 2 * kPBytes;
+  const uint32_t bars = p_smem + kPBuffers * kPBytes;
   const uint32_t q_full = bars;
   auto kv_full = [&](int s) { return bars + 8u * (1 + s); };
   auto kv_empty = [&](int s) { return bars + 8u * (1 + kStages + s); };
   auto s_full = [&](int b) { return bars + 8u * (1 + 2 * kStages + b); };
   const uint32_t p_full = bars + 8u * (3 + 2 * kStages);
   auto pv_done = [&](int b) { return bars + 8u * (4 + 2 * kStages + b); };  // one per P buffer
-  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(aligned + kQBytes + kStages * kStageBytes + 2 * kPBytes + 8 * (6 + 2 * kStages));
+  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(aligned + kQBytes + kStages * kStageBytes + kPBuffers * kPBytes + 8 * (6 + 2 * kStages));
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   // The 1 KB beyond the tiles holds the alignment padding and, after it, the barriers.
-  if (base - smem_u32(smem_raw) > 1024 - 8 * (7 + 2 * kStages)) {
+  if (base & 1023u) {  // the launch did not honour the declared alignment
     if (threadIdx.x == 0) atomicExch(p.status, 19);
     return;
   }
@@ -217,12 +223,12 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
         const int s = j % kStages;
 #pragma unroll
         for (int ks = 0; ks < kKeys / 16; ++ks) {  // 16 keys per MMA
-          const uint64_t a = desc_k_major(p_smem + (uint32_t)(j & 1) * kPBytes + (uint32_t)(ks / 4) * kBlockBytes + (uint32_t)(ks % 4) * 32u, 1024);
+          const uint64_t a = desc_k_major(p_smem + (uint32_t)(j % kPBuffers) * kPBytes + (uint32_t)(ks / 4) * kBlockBytes + (uint32_t)(ks % 4) * 32u, 1024);
           // V: rows are keys (128 bytes each), 8-key groups 1024 bytes apart, head halves one block apart
           const uint64_t b = desc_mn_major(v_smem(s) + (uint32_t)ks * 2048u, kKVBlockBytes, 1024);
           umma_bf16(tmem_o, a, b, idesc_pv, (uint32_t)((j | ks) != 0));
         }
-        umma_commit(pv_done(j & 1));
+        umma_commit(pv_done(j % kPBuffers));
         umma_commit(kv_empty(s));
       }
     }
@@ -281,7 +287,7 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
       const float m_use = m == -INFINITY ? 0.f : m;
       if (j > 0 && __any_sync(0xffffffffu, corr != 1.f)) {
         // rescale this row of O: the previous P V (tile j - 1) must have completed
-        if (lane == 0) ok_i = mbar_wait(pv_done((j - 1) & 1), ((uint32_t)(j - 1) >> 1) & 1u, p.status, 17) ? 1 : 0;
+        if (lane == 0) ok_i = mbar_wait(pv_done((j - 1) % kPBuffers), ((uint32_t)(j - 1) / kPBuffers) & 1u, p.status, 17) ? 1 : 0;
         ok = __shfl_sync(0xffffffffu, ok_i, 0) != 0;
         if (!ok) break;
         fence_after_sync();
@@ -295,9 +301,9 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
         }
         tmem_st_wait();
       }
-      if (j > 1) {
-        // this tile's P buffer was last read by the P V of tile j - 2
-        if (lane == 0) ok_i = mbar_wait(pv_done(j & 1), ((uint32_t)(j - 2) >> 1) & 1u, p.status, 20) ? 1 : 0;
+      if (j >= kPBuffers) {
+        // this tile's P buffer was last read by the P V of tile j - kPBuffers
+        if (lane == 0) ok_i = mbar_wait(pv_done(j % kPBuffers), ((uint32_t)(j - kPBuffers) / kPBuffers) & 1u, p.status, 20) ? 1 : 0;
         ok = __shfl_sync(0xffffffffu, ok_i, 0) != 0;
         if (!ok) break;
       }
@@ -317,7 +323,7 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
         }
         // keys c..c+7 of this row: one 16-byte chunk of block c / 64
         const int chunk = ((c % 64) / 8) ^ (row & 7);
-        *reinterpret_cast<uint4*>(p_ptr + (j & 1) * kPBytes + (c / 64) * kBlockBytes + row * 128 + chunk * 16) =
+        *reinterpret_cast<uint4*>(p_ptr + (j % kPBuffers) * kPBytes + (c / 64) * kBlockBytes + row * 128 + chunk * 16) =
             make_uint4(packed[0], packed[1], packed[2], packed[3]);
       }
       fence_async_smem();   // P is read by the tensor cores
@@ -328,7 +334,7 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
     // epilogue: O / sum, rounded once
     if (ok) {
       int ok_i = 1;
-      if (lane == 0) ok_i = mbar_wait(pv_done((num_tiles - 1) & 1), ((uint32_t)(num_tiles - 1) >> 1) & 1u, p.status, 18) ? 1 : 0;
+      if (lane == 0) ok_i = mbar_wait(pv_done((num_tiles - 1) % kPBuffers), ((uint32_t)(num_tiles - 1) / kPBuffers) & 1u, p.status, 18) ? 1 : 0;
       ok = __shfl_sync(0xffffffffu, ok_i, 0) != 0;
     }
     if (ok) {
