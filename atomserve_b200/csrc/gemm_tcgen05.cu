@@ -63,6 +63,7 @@ struct GemmParams {
   int kb_per_tile;       // K blocks of BK per tile
   int stream;            // 0: whole tiles round-robin; 1: equal contiguous ranges of K blocks
   int max_slots;         // workspace slots per tile
+  int bn;                // Q rows per tile actually used (<= the kernel's BN; narrower tiles of unswapped weights)
   // Optional timeline for profiling, null in normal use: %globaltimer stamps in rows of 8 words, 7
   // used per block (entry, set-up done, dependency wait over, first stage complete, last MMA
   // issued, last accumulator complete, epilogue done) and a row after the blocks for the reduction
@@ -223,6 +224,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_cons
   volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(aligned + C::kStages * C::kStage + 8 * (2 * C::kStages + 4));
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int bn = p.bn;                                               // Q rows per tile: BN unless the plan narrowed it
+  const uint32_t stage_bytes = (uint32_t)(C::kTileP + bn * BK * 2);  // what one K block's two boxes bring
 
   if (threadIdx.x == 0) {
     stamp(p, 0);
@@ -258,9 +261,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_cons
         SegmentWalk ahead(p);
         uint32_t it = 0;
         while (it < (uint32_t)C::kStages && ahead.next()) {
-          const int p0 = (ahead.tile % p.tiles_p) * BM, q0 = (ahead.tile / p.tiles_p) * BN;
+          const int p0 = (ahead.tile % p.tiles_p) * BM, q0 = (ahead.tile / p.tiles_p) * bn;
           for (int kb = ahead.kb0; kb < ahead.kb1 && it < (uint32_t)C::kStages; ++kb, ++it) {
-            mbar_expect_tx(full_bar(it), C::kStage);
+            mbar_expect_tx(full_bar(it), stage_bytes);
             if (p.swap) tma_load_2d(base + it * C::kStage, &map_p, full_bar(it), kb * BK, p0);
             else tma_load_2d(base + it * C::kStage + C::kTileP, &map_q, full_bar(it), kb * BK, q0);
           }
@@ -273,7 +276,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_cons
       uint32_t it = 0;  // K blocks loaded so far by this block, across segments
       bool ok = true;
       while (ok && walk.next()) {
-        const int p0 = (walk.tile % p.tiles_p) * BM, q0 = (walk.tile / p.tiles_p) * BN;
+        const int p0 = (walk.tile % p.tiles_p) * BM, q0 = (walk.tile / p.tiles_p) * bn;
         for (int kb = walk.kb0; kb < walk.kb1; ++kb, ++it) {
           const int s = it % C::kStages;
           if (it < (uint32_t)C::kStages) {  // the weight half is already on its way
@@ -284,7 +287,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_cons
           const uint32_t phase = (it / C::kStages) & 1u;
           ok = mbar_wait(empty_bar(s), phase ^ 1u, p.status, 1);
           if (!ok) break;
-          mbar_expect_tx(full_bar(s), C::kStage);
+          mbar_expect_tx(full_bar(s), stage_bytes);
           tma_load_2d(base + s * C::kStage, &map_p, full_bar(s), kb * BK, p0);
           tma_load_2d(base + s * C::kStage + C::kTileP, &map_q, full_bar(s), kb * BK, q0);
         }
@@ -293,7 +296,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_cons
   } else if (warp == 1) {
     asb::pdl_wait();
     if (lane == 0) {
-      constexpr uint32_t idesc = instr_desc(BM, BN);
+      const uint32_t idesc = instr_desc(BM, bn);
       SegmentWalk walk(p);
       uint32_t it = 0, seg = 0;
       bool ok = true;
@@ -339,7 +342,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_cons
       if (!ok) break;
       if (warp == 2 && lane == 0) stamp(p, 5);
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-      const int p0 = (walk.tile % p.tiles_p) * BM, q0 = (walk.tile / p.tiles_p) * BN;
+      const int p0 = (walk.tile % p.tiles_p) * BM, q0 = (walk.tile / p.tiles_p) * bn;
       const int prow = p0 + quad * 32 + lane;
       const bool whole = walk.kb0 == 0 && walk.kb1 == p.kb_per_tile && p.epilogue != kPartialsOnly;
       float* slot = nullptr;
@@ -351,7 +354,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_cons
       }
       constexpr int kChunk = BN >= 32 ? 32 : 16;  // columns read from tensor memory at a time
 #pragma unroll 1
-      for (int c = 0; c < BN; c += kChunk) {
+      for (int c = 0; c < bn; c += kChunk) {
         if (q0 + c >= p.q_rows) break;  // uniform: depends on the segment and c only
         uint32_t raw[kChunk];
         tmem_ld(tmem_base + ((uint32_t)(quad * 32) << 16) + buf * BN + (uint32_t)c, raw);
@@ -586,7 +589,7 @@ int sm_count() {
 unsigned long long* g_stamps = nullptr;  // asb_gemm_tcgen05_timeline
 
 struct Plan {
-  int swap, bn, tiles_p, tiles_q, kb_per_tile, stream, blocks, max_slots;
+  int swap, bn, bn_kernel, tiles_p, tiles_q, kb_per_tile, stream, blocks, max_slots;
   long long workspace;  // float32 elements
 };
 
@@ -603,6 +606,19 @@ Plan make_plan(int M, int N, int K) {
   const int unswapped_tiles = ((M + BM - 1) / BM) * ((N + 255) / 256);
   pl.swap = M <= 32 || (M <= 256 && 2 * unswapped_tiles < sm_count()) ? 1 : 0;
   pl.bn = pl.swap ? (M <= 16 ? 16 : (M <= 32 ? 32 : (M <= 64 ? 64 : (M <= 128 ? 128 : 256)))) : (N <= 128 ? 128 : 256);
+  pl.bn_kernel = pl.bn;
+  if (!pl.swap && M <= BM && pl.bn == 256) {
+    // One row of tiles over few tokens: an SM's time goes with the bytes it takes in per K block,
+    // the tokens' box (16 KB) and bn weight rows, so narrower tiles that spread the weight rows
+    // over more SMs are faster as long as they still fit one wave; the 256-column kernel runs them.
+    const int sms_now = sm_count();
+    double best = 1e30;
+    for (int bn = 256; bn >= 128; bn -= 32) {
+      const int tiles = (N + bn - 1) / bn;
+      const double cost = (double)((tiles + sms_now - 1) / sms_now) * (128 + bn);
+      if (cost < best) { best = cost; pl.bn = bn; }
+    }
+  }
   const int p_rows = pl.swap ? N : M, q_rows = pl.swap ? M : N;
   pl.tiles_p = (p_rows + BM - 1) / BM;
   pl.tiles_q = (q_rows + pl.bn - 1) / pl.bn;
@@ -715,11 +731,12 @@ extern "C" int asb_gemm_tcgen05(void* out, const void* x, const void* w, const v
   p.kb_per_tile = pl.kb_per_tile;
   p.stream = pl.stream;
   p.max_slots = pl.max_slots;
+  p.bn = pl.bn;
   p.stamps = g_stamps;
   alignas(64) CUtensorMap mp, mq;
   if (int rc = make_map(&mp, pl.swap ? w : x, p.p_rows, K, BM)) return rc;
   if (int rc = make_map(&mq, pl.swap ? x : w, p.q_rows, K, pl.bn)) return rc;
-  switch (pl.bn) {
+  switch (pl.bn_kernel) {
     case 16: return launch<16>(mp, mq, p, pl, stream);
     case 32: return launch<32>(mp, mq, p, pl, stream);
     case 64: return launch<64>(mp, mq, p, pl, stream);
