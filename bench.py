@@ -406,8 +406,8 @@ def gemm_timelines(which: str, tokens: list[int]) -> None:
             torch.cuda.synchronize()
             check_gemm_status()
             host = stamps.cpu()
-            blocks = int((host[:, 0] > 0).sum()) - 1  # the row after the blocks holds the reduction's three stamps
-            per_block, reduction = host[:blocks].double(), host[blocks].double()
+            blocks = int(((host[:, 0] > 0) & (host[:, 3] > 0)).sum())  # a block's row has a first-stage stamp
+            per_block, reduction = host[:blocks].double(), host[blocks].double()  # then the reduction's three stamps
             t0 = per_block[:, 0].min()
             line = {"gemm": name, "tokens": M, "blocks": blocks}
             for i, n in enumerate(names):
