@@ -21,8 +21,12 @@
 // `segment_reduce_kernel` sums a tile's slots afterwards, unless the caller asked for the partial
 // sums themselves (csrc/gemm_partials.cuh).
 //
-// Warp roles (192 threads): warp 0 issues TMA loads, warp 1 allocates TMEM and issues MMAs,
-// warps 2-5 run the epilogue (warp w reads TMEM lanes 32*(w%4)..+31). Stages are handed over
+// Warp roles: warp 0 issues TMA loads, warp 1 allocates TMEM and issues MMAs, warps 2-5 run the
+// epilogue (warp w reads TMEM lanes 32*(w%4)..+31). With narrow tiles (few tokens) a tcgen05.mma
+// takes the tensor pipe far less time than its issue takes the issuing thread (60-80 cycles an
+// instruction, whatever its shape: measured), so one thread cannot keep up with the weight stream:
+// there, warps 6.. issue too. Issuer i takes every kIssuers-th K block of a segment into an
+// accumulator of its own, and the epilogue adds the accumulators up. Stages are handed over
 // with mbarriers: full[s] (TMA bytes landed) and empty[s] (tcgen05.commit after the MMAs that
 // read stage s). The accumulator is double-buffered in TMEM: acc_full[b] tells the epilogue
 // that buffer b is complete, acc_empty[b] tells the MMA warp that it has been read out, so the
@@ -41,7 +45,7 @@ namespace {
 using asb::block_of;
 using asb::range_begin;
 
-constexpr int kThreads = 192;
+constexpr int kMaxThreads = 192 + 32;
 constexpr int BM = 128;   // P rows per tile = TMEM lanes
 constexpr int BK = 64;    // K elements per stage: 128 bytes, one swizzle atom
 constexpr int UMMA_K = 16;
@@ -197,7 +201,10 @@ struct Config {
   static constexpr int kTileQ = BN * BK * 2;
   static constexpr int kStage = kTileP + kTileQ;
   static constexpr int kStages = BN >= 256 ? 4 : (BN >= 128 ? 6 : 8);
-  static constexpr int kTmemCols = 2 * BN < 32 ? 32 : 2 * BN;   // two accumulators
+  static constexpr int kIssuers = BN <= 64 ? 2 : 1;             // threads that issue MMAs, an accumulator each
+  static constexpr int kThreads = 192 + 32 * (kIssuers - 1);
+  static constexpr int kAccCols = kIssuers * BN;                // tensor-memory columns of one buffer
+  static constexpr int kTmemCols = 2 * kAccCols < 32 ? 32 : 2 * kAccCols;   // two buffers
   static constexpr int kSmem = kStages * kStage + 1024 /* alignment slack */ + 256 /* barriers */;
 };
 
@@ -209,7 +216,7 @@ __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
 }
 
 template <int BN>
-__global__ void __launch_bounds__(kThreads, 1)
+__global__ void __launch_bounds__(kMaxThreads, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant__ CUtensorMap map_q,
                     const GemmParams p) {
   using C = Config<BN>;
@@ -234,7 +241,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_cons
       mbar_init(empty_bar(s), 1);
     }
     for (int b = 0; b < 2; ++b) {
-      mbar_init(acc_full(b), 1);
+      mbar_init(acc_full(b), C::kIssuers);  // one commit per issuing thread
       mbar_init(acc_empty(b), 4);  // one arrival per epilogue warp
     }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -293,9 +300,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_cons
         }
       }
     }
-  } else if (warp == 1) {
+  } else if (warp == 1 || warp >= 6) {
     asb::pdl_wait();
     if (lane == 0) {
+      const int me = warp == 1 ? 0 : warp - 5;  // which of the kIssuers issuing threads
       const uint32_t idesc = instr_desc(BM, bn);
       SegmentWalk walk(p);
       uint32_t it = 0, seg = 0;
@@ -306,8 +314,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_cons
         ok = mbar_wait(acc_empty(buf), ((seg >> 1) & 1u) ^ 1u, p.status, 4);
         if (!ok) break;
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        const uint32_t tmem_acc = tmem_base + buf * BN;
+        const uint32_t tmem_acc = tmem_base + buf * C::kAccCols + me * BN;
         for (int kb = walk.kb0; kb < walk.kb1; ++kb, ++it) {
+          if (C::kIssuers > 1 && (kb - walk.kb0) % C::kIssuers != me) continue;
           const int s = it % C::kStages;
           const uint32_t phase = (it / C::kStages) & 1u;
           ok = mbar_wait(full_bar(s), phase, p.status, 2);
@@ -319,11 +328,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_cons
 #pragma unroll
           for (int k = 0; k < BK / UMMA_K; ++k)  // 32 bytes further along K inside the swizzle atom
             umma(tmem_acc, da + (uint64_t)(k * UMMA_K * 2 >> 4), db + (uint64_t)(k * UMMA_K * 2 >> 4), idesc,
-                 (uint32_t)((kb > walk.kb0) | (k != 0)));
+                 (uint32_t)((kb - walk.kb0 >= C::kIssuers) | (k != 0)));
           umma_commit(empty_bar(s));  // stage s may be refilled once these MMAs have read it
         }
-        umma_commit(acc_full(buf));  // arrives when every MMA of this segment has completed
-        stamp(p, 4);
+        umma_commit(acc_full(buf));  // arrives when every MMA this thread issued for the segment has completed
+        if (me == 0) stamp(p, 4);
         ++seg;
       }
     }
@@ -357,7 +366,17 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_cons
       for (int c = 0; c < bn; c += kChunk) {
         if (q0 + c >= p.q_rows) break;  // uniform: depends on the segment and c only
         uint32_t raw[kChunk];
-        tmem_ld(tmem_base + ((uint32_t)(quad * 32) << 16) + buf * BN + (uint32_t)c, raw);
+        const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + buf * C::kAccCols + (uint32_t)c;
+        tmem_ld(taddr, raw);
+        // the other issuing threads' accumulators, as far as the segment gave them K blocks
+#pragma unroll
+        for (int i = 1; i < C::kIssuers; ++i) {
+          if (walk.kb1 - walk.kb0 <= i) break;
+          uint32_t more[kChunk];
+          tmem_ld(taddr + i * BN, more);
+#pragma unroll
+          for (int j = 0; j < kChunk; ++j) raw[j] = __float_as_uint(__uint_as_float(raw[j]) + __uint_as_float(more[j]));
+        }
         if (!whole) {  // partial sums; rows beyond the matrix hold zeros
           const int row = quad * 32 + lane;
           // K is cut only with swapped operands: lanes are output columns, and a warp's 32 lanes
@@ -655,7 +674,7 @@ int launch(const CUtensorMap& mp, const CUtensorMap& mq, const GemmParams& p, co
   auto kern = gemm_tcgen05_kernel<BN>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Config<BN>::kSmem);
   if (e != cudaSuccess) return asb::fail("gemm_tcgen05: shared memory %d: %s", Config<BN>::kSmem, cudaGetErrorString(e));
-  asb::launch(kern, pl.blocks, kThreads, Config<BN>::kSmem, stream, mp, mq, p);
+  asb::launch(kern, pl.blocks, Config<BN>::kThreads, Config<BN>::kSmem, stream, mp, mq, p);
   if (int rc = asb::check_launch("gemm_tcgen05")) return rc;
   if (pl.stream && p.epilogue != kPartialsOnly) {
     asb::launch(segment_reduce_kernel<BN>, dim3(p.num_tiles, (BM * BN / 4 + 255) / 256), 256, 0, stream, p, pl.blocks);
