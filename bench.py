@@ -53,8 +53,8 @@ def prompts(batch: int, length: int) -> list[list[int]]:
 
 
 class ClockSampler:
-    def __init__(self):
-        self.proc, self.path = None, ROOT / "gpurun_out" / "bench_clocks.csv"
+    def __init__(self, name: str = "bench_clocks.csv"):
+        self.proc, self.path = None, ROOT / "gpurun_out" / name
 
     def __enter__(self):
         try:
@@ -496,7 +496,9 @@ def main() -> int:
         ms, _, _, e, _ = time_decode(engine, b, max(args.steps // 2, 8), 3)
         points[f"decode_b{b}"] = round(b * 1000.0 / ms, 1)
         points[f"decode_b{b}_e2e"] = round(e, 1)
-    prefill_ms = time_prefill(engine, steps=5, warmup=3)
+    # long enough for the power cap to act and for a few clock samples: the prefill runs at the cap
+    with ClockSampler("bench_clocks_prefill.csv") as prefill_clocks:
+        prefill_ms = time_prefill(engine, steps=20, warmup=3)
 
     value = args.batch * 1000.0 / device_ms
     achieved = step_bytes(config, args.batch, ctx) / (device_ms * 1e-3) / 1e9
@@ -525,7 +527,9 @@ def main() -> int:
                 "d2h_bytes_per_step": 4 * args.batch},
         "gpu_launches": launches * 1,
         "prefill": {"value": round(PROMPT_TOKENS * 1000.0 / prefill_ms, 1), "tokens": PROMPT_TOKENS, "ms": round(prefill_ms, 3),
-                    "frac": round(flops / (prefill_ms * 1e-3) / (pk["bf16_tflops"] * 1e12), 4)},
+                    "frac": round(flops / (prefill_ms * 1e-3) / (pk["bf16_tflops"] * 1e12), 4),
+                    "frac_sustained": round(flops / (prefill_ms * 1e-3) / (pk["bf16_tflops_sustained"] * 1e12), 4),
+                    "sm_mhz": prefill_clocks.summary()["sm_mhz"]},
         "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
                      "frac": round(achieved / pk["hbm_gbs"], 4), "peaks": pk["source"]},
         "points": points,
