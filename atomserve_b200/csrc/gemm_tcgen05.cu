@@ -626,14 +626,16 @@ Plan make_plan(int M, int N, int K) {
   pl.swap = M <= 32 || (M <= 256 && 2 * unswapped_tiles < sm_count()) ? 1 : 0;
   pl.bn = pl.swap ? (M <= 16 ? 16 : (M <= 32 ? 32 : (M <= 64 ? 64 : (M <= 128 ? 128 : 256)))) : (N <= 128 ? 128 : 256);
   pl.bn_kernel = pl.bn;
-  if (!pl.swap && M <= BM && pl.bn == 256) {
-    // One row of tiles over few tokens: an SM's time goes with the bytes it takes in per K block,
-    // the tokens' box (16 KB) and bn weight rows, so narrower tiles that spread the weight rows
-    // over more SMs are faster as long as they still fit one wave; the 256-column kernel runs them.
+  if (!pl.swap && pl.bn == 256) {
+    // An SM's time per K block goes with the bytes it takes in, the tokens' box (16 KB) and bn
+    // weight rows, so where 256-row tiles leave SMs idle (one row of tiles over few tokens, or
+    // few weight rows under a few hundred tokens), narrower tiles that spread the weight rows over
+    // more SMs are faster as long as they need no further wave; the 256-column kernel runs them.
     const int sms_now = sm_count();
+    const int token_tiles = (M + BM - 1) / BM;
     double best = 1e30;
     for (int bn = 256; bn >= 128; bn -= 32) {
-      const int tiles = (N + bn - 1) / bn;
+      const int tiles = token_tiles * ((N + bn - 1) / bn);
       const double cost = (double)((tiles + sms_now - 1) / sms_now) * (128 + bn);
       if (cost < best) { best = cost; pl.bn = bn; }
     }

@@ -347,6 +347,7 @@ GEMM_SHAPES = [
     (1, 128, 64), (3, 100, 72), (16, 256, 512), (17, 384, 4096), (33, 130, 1024), (64, 4096, 4096),
     (8, 4096, 12288), (65, 256, 128), (128, 300, 264), (300, 512, 1000), (2048, 1024, 512),
     (200, 4096, 1024), (256, 512, 2048), (100, 24576, 256), (40, 20000, 128),
+    (300, 4096, 512), (512, 4104, 256), (700, 5120, 128), (384, 6144, 192),
 ]  # fmt: skip
 
 
