@@ -616,14 +616,19 @@ struct Plan {
 // are its N = 16..256) for up to 32 tokens always, and for up to 256 tokens where the unswapped
 // tiles of 128 x 256 would leave over half of the SMs idle (few weight rows: qkv, o, down); where
 // they fill the machine (gate/up, the head) whole unswapped tiles win from 33 tokens on (measured
-// on the 8B and 14B shapes). With swapped operands, whole tiles are dealt round-robin unless
+// on the 8B and 14B shapes). Up to 512 tokens the operands also swap where K is long (128 K blocks
+// or more: down) and the unswapped tiles would fill under 70 % of the SMs: the partial sums of a
+// 128 x 256 tile then cost less than the idle SMs (down at 300-512 tokens: 68 to 47-52 us on the 8B
+// shape); with K of 64-80 blocks they cost more (qkv: 27 to 35 us). With swapped operands, whole tiles are dealt round-robin unless
 // cutting the flattened K-block sequence into equal ranges shortens the busiest SM's share of the
 // operand stream by more than the partial sums cost to write and read back; unswapped tiles are
 // never cut (their partial sums, 128 KB a tile, cost more than the idle SMs: measured).
 Plan make_plan(int M, int N, int K) {
   Plan pl;
   const int unswapped_tiles = ((M + BM - 1) / BM) * ((N + 255) / 256);
-  pl.swap = M <= 32 || (M <= 256 && 2 * unswapped_tiles < sm_count()) ? 1 : 0;
+  const int kb_per_tile = (K + BK - 1) / BK;
+  pl.swap = M <= 32 || (M <= 256 && 2 * unswapped_tiles < sm_count()) ||
+            (M <= 512 && kb_per_tile >= 128 && 1.4 * unswapped_tiles < sm_count()) ? 1 : 0;
   pl.bn = pl.swap ? (M <= 16 ? 16 : (M <= 32 ? 32 : (M <= 64 ? 64 : (M <= 128 ? 128 : 256)))) : (N <= 128 ? 128 : 256);
   pl.bn_kernel = pl.bn;
   if (!pl.swap && pl.bn == 256) {

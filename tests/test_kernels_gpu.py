@@ -348,6 +348,7 @@ GEMM_SHAPES = [
     (8, 4096, 12288), (65, 256, 128), (128, 300, 264), (300, 512, 1000), (2048, 1024, 512),
     (200, 4096, 1024), (256, 512, 2048), (100, 24576, 256), (40, 20000, 128),
     (300, 4096, 512), (512, 4104, 256), (700, 5120, 128), (384, 6144, 192),
+    (300, 4096, 8192), (512, 1000, 8256), (257, 2048, 12288),
 ]  # fmt: skip
 
 
