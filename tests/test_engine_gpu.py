@@ -365,6 +365,121 @@ def test_a_toy_mixer_with_state_of_its_own_is_registered_built_and_stepped():
     assert torch.allclose(y, toy_parts.ema_reference((h @ mixer.w.T).cpu(), 0.8), atol=1e-5)
 
 
+def routed_spec(cfg, kinds):
+    """Two layers: the first with the dense feed-forward, the second with the test's routed one."""
+    from atomserve_b200.parts import LayerCall, LayerSpec, ModelSpec, PartSpec
+
+    d, eps, hd = cfg["hidden_size"], cfg["rms_norm_eps"], cfg["head_dim"]
+    t = "" if kinds == "cuda" else "torch_"
+    layers = []
+    for i in range(2):
+        p = f"model.layers.{i}."
+        if kinds == "cuda":
+            mixer = PartSpec("gqa_attention", dict(num_heads=cfg["num_attention_heads"], num_kv_heads=cfg["num_key_value_heads"],
+                             head_dim=hd, qk_norm_eps=eps, position=PartSpec("rotary", dict(head_dim=hd, theta=cfg["rope_theta"]))),
+                             p + "self_attn.")  # fmt: skip
+        else:
+            mixer = PartSpec("torch_attention", dict(num_heads=cfg["num_attention_heads"], num_kv_heads=cfg["num_key_value_heads"],
+                             head_dim=hd, eps=eps, theta=cfg["rope_theta"], window=None), p + "self_attn.")  # fmt: skip
+        dense = PartSpec(t + "swiglu", dict(intermediate_size=cfg["intermediate_size"]), p + "mlp.")
+        routed = PartSpec("toy_top1_experts", dict(num_experts=3, expert_size=40), p + "moe.")
+        layers.append(LayerSpec("pre_norm", mixer, routed if i else dense,
+                                PartSpec(t + "rms_norm", dict(eps=eps), p + "input_layernorm."),
+                                PartSpec(t + "rms_norm", dict(eps=eps), p + "post_attention_layernorm.")))  # fmt: skip
+    return ModelSpec(
+        hidden_size=d, vocab_size=cfg["vocab_size"], max_positions=512,
+        embedding=PartSpec("token_embedding" if kinds == "cuda" else "torch_embedding", dict(vocab_size=cfg["vocab_size"]), "model.embed_tokens."),
+        layers=tuple(layers), schedule=(LayerCall(0), LayerCall(1)),
+        final_norm=PartSpec(t + "rms_norm", dict(eps=eps), "model.norm."),
+        head=PartSpec("lm_head" if kinds == "cuda" else "torch_head", dict(vocab_size=cfg["vocab_size"], tied=False), "lm_head."),
+    )  # fmt: skip
+
+
+def test_a_toy_feed_forward_with_routing_is_registered_built_and_stepped():
+    """The second layer's feed-forward is the test's top-1 router over three small experts. The
+    model with the package's CUDA parts around it gives, whole and cut into portions, what the
+    same model of torch parts gives on the CPU; and the routed part alone matches a token-by-token
+    restatement that really does send tokens to different experts."""
+    cfg = {**TINY["b"][0], "num_hidden_layers": 2}
+    d = cfg["hidden_size"]
+    w = checkpoint(cfg, seed=21)
+    g = torch.Generator().manual_seed(5)
+    for k in [k for k in w if k.startswith("model.layers.1.mlp.")]:
+        del w[k]
+    w["model.layers.1.moe.router.weight"] = (torch.randn(3, d, generator=g) * 0.5).bfloat16().float()
+    for x in range(3):
+        for n, shape in (("gate", (40, d)), ("up", (40, d)), ("down", (d, 40))):
+            w[f"model.layers.1.moe.experts.{x}.{n}_proj.weight"] = (torch.randn(shape, generator=g) * 0.1).bfloat16().float()
+    ids = prompts(cfg, [41], seed=2)[0]
+    cuts = [9, 2, 17, 1, 1, 11]
+    ref_whole, ref_cut = run_whole_and_cut(custom_model(routed_spec(cfg, "torch"), w, "cpu", torch.float32), 8, ids, cuts, "cpu")
+    assert rel_error(ref_cut, ref_whole) < 1e-5
+    model = custom_model(routed_spec(cfg, "cuda"), w, "cuda", torch.float32)
+    whole, cut = run_whole_and_cut(model, 8, ids, cuts, "cuda")
+    assert rel_error(whole, ref_whole) < FLOAT32_TOLERANCE and rel_error(cut, ref_whole) < FLOAT32_TOLERANCE
+
+    ff = model.blocks[1].feed_forward
+    h = torch.randn(24, d, generator=g)
+    got = ff.forward(h.cuda(), torch.zeros(24, d, device="cuda"), None).cpu()
+    logits = h @ w["model.layers.1.moe.router.weight"].T
+    chosen = logits.argmax(-1)
+    assert len(set(chosen.tolist())) >= 2
+    for t in range(24):
+        x = int(chosen[t])
+        gate, up, down = (w[f"model.layers.1.moe.experts.{x}.{n}_proj.weight"] for n in ("gate", "up", "down"))
+        y = (torch.nn.functional.silu(h[t] @ gate.T) * (h[t] @ up.T)) @ down.T * torch.softmax(logits[t], -1)[x]
+        assert torch.allclose(got[t], y, atol=1e-5)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_another_position_encoding_through_the_attention_part(dtype):
+    """The package's attention with the test's position encoding (positions compressed by 4, 32
+    of 48 head elements rotated) and no q/k norm: two portions through its cache equal causal
+    grouped-query attention written out here in float64."""
+    from atomserve_b200.parts import CacheView, PartSpec, build_part
+
+    d, H, KV, hd, bs, T, theta, factor, rd = 56, 4, 2, 48, 4, 21, 5e3, 4.0, 32
+    g = torch.Generator().manual_seed(7)
+    names = {"q_proj": (H * hd, d), "k_proj": (KV * hd, d), "v_proj": (KV * hd, d), "o_proj": (d, H * hd)}
+    w = {n: (torch.randn(s, generator=g) * 0.1).bfloat16().float() for n, s in names.items()}
+    part = build_part("mixer", PartSpec("gqa_attention", dict(
+        num_heads=H, num_kv_heads=KV, head_dim=hd, qk_norm_eps=None,
+        position=PartSpec("toy_interpolated_rotary", dict(head_dim=hd, theta=theta, factor=factor, rotary_dim=rd))), "a."), d)  # fmt: skip
+    part.load({f"a.{n}.weight": v.cuda().to(dtype) for n, v in w.items()})
+    h = torch.randn(T, d, generator=g).bfloat16().float()
+    res = torch.randn(T, d, generator=g).bfloat16().float()
+
+    pos = torch.arange(T)
+    q = toy_parts.interpolated_rotary_reference((h @ w["q_proj"].T).view(T, H, hd), pos, theta, factor, rd)
+    k = toy_parts.interpolated_rotary_reference((h @ w["k_proj"].T).view(T, KV, hd), pos, theta, factor, rd)
+    v = (h @ w["v_proj"].T).view(T, KV, hd).double()
+    k, v = k.repeat_interleave(H // KV, dim=1), v.repeat_interleave(H // KV, dim=1)
+    scores = torch.einsum("thd,shd->hts", q, k) * hd**-0.5
+    scores = scores.masked_fill(pos[None, :, None] < pos[None, None, :], float("-inf"))
+    attn = torch.einsum("hts,shd->thd", torch.softmax(scores, -1), v).reshape(T, H * hd)
+    ref = (res.double() + attn @ w["o_proj"].double().T).float()
+
+    view = CacheView(k=torch.zeros(8, KV, bs, hd, device="cuda", dtype=dtype), block_size=bs)
+    view.v = torch.zeros_like(view.k)
+    table = [4, 1, 6, 0, 3, 7]
+    view.block_tables = torch.tensor([table], dtype=torch.int32, device="cuda")
+    outs = []
+    for start, n in ((0, 13), (13, 8)):
+        view.slots = torch.tensor([table[p // bs] * bs + p % bs for p in range(start, start + n)], dtype=torch.int32, device="cuda")
+        outs.append(part.forward(h[start : start + n].cuda().to(dtype), res[start : start + n].cuda().to(dtype),
+                                 step_context([n], [start]), view))  # fmt: skip
+    got = torch.cat(outs).float().cpu()
+    assert rel_error(got, ref) < (1e-5 if dtype == torch.float32 else 2e-2)
+    # and the encoding matters: the package's own rotary at the same theta gives something else
+    own = build_part("mixer", PartSpec("gqa_attention", dict(
+        num_heads=H, num_kv_heads=KV, head_dim=hd, qk_norm_eps=None,
+        position=PartSpec("rotary", dict(head_dim=hd, theta=theta))), "a."), d)  # fmt: skip
+    own.load({f"a.{n}.weight": v.cuda().to(dtype) for n, v in w.items()})
+    view.slots = torch.tensor([table[p // bs] * bs + p % bs for p in range(T)], dtype=torch.int32, device="cuda")
+    other = own.forward(h.cuda().to(dtype), res.cuda().to(dtype), step_context([T], [0]), view).float().cpu()
+    assert rel_error(other, ref) > 1e-2
+
+
 def test_full_width_layers_bfloat16_against_float32():
     """Two layers with the widths of Qwen3-8B (hidden 4096, 32 query and 8 kv heads of 128,
     intermediate 12288; a smaller vocabulary): the bfloat16 path (tcgen05 GEMM and attention,

@@ -4,7 +4,10 @@ Two uses. (1) Every hot part again in plain torch (`torch_*` kinds and the archi
 "ToyTorchLM"), reading and writing the paged cache through the same CacheView: with these
 the scheduler, cache manager, runner and engine run whole on the CPU. (2) `ema_mixer`, a mixer
 with state of its own (one vector per request, kept in the state slots), to show that such a
-part is registered, built and stepped without touching the package.
+part is registered, built and stepped without touching the package; `toy_top1_experts`, a
+feed-forward that routes each token to one of a few small experts; and
+`toy_interpolated_rotary`, another position encoding (positions compressed by a factor, only a
+part of the head rotated) that the package's attention takes in place of its own.
 
 They follow the package's interfaces and nothing else of it; the oracle stays plain_qwen3.
 """
@@ -19,7 +22,7 @@ import plain_qwen3 as plain
 from atomserve_b200.config.registry import register_architecture
 from atomserve_b200.parts import (
     CacheView, FeedForward, KVCacheSpec, LayerCall, LayerSpec, Mixer, ModelSpec, Norm, Part,
-    PartSpec, StateSpec, StepContext, TensorSpec, register_part,
+    PartSpec, PositionEncoding, StateSpec, StepContext, TensorSpec, register_part,
 )  # fmt: skip
 
 
@@ -178,7 +181,70 @@ def ema_reference(u: torch.Tensor, decay: float) -> torch.Tensor:
     return torch.stack(out)
 
 
+class Top1Experts(FeedForward):
+    """A feed-forward with routing: router logits in float32, each token goes to the expert with
+    the largest logit (ties to the lower index) and is scaled by that logit's softmax weight.
+    Every expert is a small SwiGLU. All experts run on all tokens and a mask picks, so the step
+    has no data-dependent shapes and can be captured in a graph."""
+
+    def __init__(self, hidden_size, prefix, num_experts, expert_size):
+        self.d, self.p, self.e, self.i = hidden_size, prefix, num_experts, expert_size
+
+    def tensor_specs(self):
+        specs = [TensorSpec(self.p + "router.weight", (self.e, self.d))]
+        for x in range(self.e):
+            specs += [TensorSpec(self.p + f"experts.{x}.gate_proj.weight", (self.i, self.d)),
+                      TensorSpec(self.p + f"experts.{x}.up_proj.weight", (self.i, self.d)),
+                      TensorSpec(self.p + f"experts.{x}.down_proj.weight", (self.d, self.i))]  # fmt: skip
+        return specs
+
+    def load(self, tensors):
+        self.router = tensors[self.p + "router.weight"]
+        self.experts = [tuple(tensors[self.p + f"experts.{x}.{n}_proj.weight"] for n in ("gate", "up", "down"))
+                        for x in range(self.e)]  # fmt: skip
+
+    def forward(self, h, residual, ctx):
+        return residual + top1_experts_reference(h, self.router, self.experts)
+
+
+def top1_experts_reference(h, router, experts):
+    logits = h.float() @ router.float().T
+    weight, choice = torch.softmax(logits, dim=-1).max(dim=-1)
+    out = torch.zeros_like(h, dtype=torch.float32)
+    for x, (gate, up, down) in enumerate(experts):
+        y = (torch.nn.functional.silu(h @ gate.T) * (h @ up.T)) @ down.T
+        out += y.float() * (weight * (choice == x)).unsqueeze(-1)
+    return out.to(h.dtype)
+
+
+class InterpolatedRotary(PositionEncoding):
+    """Rotary encoding with positions divided by `factor` and only the first `rotary_dim`
+    elements of a head rotated. It gives the attention part what it asks of a position encoding:
+    `prepare(device)`, `inv_freq` (float32, one entry per rotated pair) and `rotary_dim`."""
+
+    def __init__(self, hidden_size, prefix, head_dim, theta, factor, rotary_dim):
+        self.head_dim, self.theta, self.factor, self.rotary_dim = head_dim, float(theta), float(factor), rotary_dim
+        self.inv_freq = None
+
+    def prepare(self, device):
+        exponents = torch.arange(0, self.rotary_dim, 2, dtype=torch.float32) / self.rotary_dim
+        self.inv_freq = (1.0 / (self.theta**exponents) / self.factor).to(device)
+
+
+def interpolated_rotary_reference(x, positions, theta, factor, rotary_dim):
+    """x [T, heads, head_dim] rotated as InterpolatedRotary says, in float64."""
+    x = x.double()
+    inv = 1.0 / (theta ** (torch.arange(0, rotary_dim, 2, dtype=torch.float64) / rotary_dim)) / factor
+    angle = positions.double()[:, None] * inv[None, :]
+    cos, sin = angle.cos()[:, None, :], angle.sin()[:, None, :]
+    half = rotary_dim // 2
+    a, b = x[..., :half], x[..., half:rotary_dim]
+    return torch.cat([a * cos - b * sin, b * cos + a * sin, x[..., rotary_dim:]], dim=-1)
+
+
 register_part("norm", "torch_rms_norm", TorchRMSNorm)
+register_part("feed_forward", "toy_top1_experts", Top1Experts)
+register_part("position", "toy_interpolated_rotary", InterpolatedRotary)
 register_part("embedding", "torch_embedding", TorchEmbedding)
 register_part("head", "torch_head", TorchHead)
 register_part("feed_forward", "torch_swiglu", TorchSwiGLU)
