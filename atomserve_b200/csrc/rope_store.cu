@@ -176,10 +176,100 @@ __global__ void qk_norm_rope_store_vec_kernel(
   }
 }
 
+// Many tokens, bfloat16: one block per token walks all its heads, hd / 8 lanes per head with one
+// 16-byte vector each (a warp holds 256 / hd heads at a time), so that the angles are computed
+// once per token and every load and store moves 16 bytes. The rotation partner of a lane is the
+// lane hd / 16 further along in its group.
+template <int HD>
+__global__ void qk_norm_rope_store_wide_kernel(
+    __nv_bfloat16* __restrict__ q_out, __nv_bfloat16* __restrict__ k_cache, __nv_bfloat16* __restrict__ v_cache,
+    const __nv_bfloat16* __restrict__ qkv, const float* __restrict__ q_gain, const float* __restrict__ k_gain,
+    const float* __restrict__ inv_freq, const int* __restrict__ positions, const int* __restrict__ slots,
+    int H, int KV, int block_size, float eps) {
+  constexpr int kLanes = HD / 8;                 // lanes per head
+  constexpr int kHeadsAtOnce = kWarps * 32 / kLanes;
+  const int t = blockIdx.x;
+  const int sub = threadIdx.x % kLanes;          // this lane's place in its head
+  const int e0 = sub * 8;
+  const int heads = H + 2 * KV;
+  // the lanes of this head: groups of a warp take different branches below (a query head beside a
+  // value head), so their shuffles name only their own lanes
+  const unsigned group = kLanes == 32 ? 0xffffffffu : ((1u << kLanes) - 1u) << ((threadIdx.x & 31) / kLanes * kLanes);
+  // before the wait: what no kernel of the step writes
+  const int slot = slots ? __ldcg(slots + t) : -1;
+  float cs[8], sn[8], gq[8], gk[8];
+  if (inv_freq) {
+    const float pos = (float)__ldcg(positions + t);
+    const int i0 = (sub % (kLanes / 2)) * 8;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) sincosf(pos * inv_freq[i0 + k], &sn[k], &cs[k]);
+  }
+#pragma unroll
+  for (int k = 0; k < 8; ++k) {
+    gq[k] = q_gain ? q_gain[e0 + k] : 1.f;
+    gk[k] = k_gain ? k_gain[e0 + k] : 1.f;
+  }
+  asb::pdl_wait();  // the stream's previous kernel has completed (programmatic dependent launch)
+  asb::pdl_launch_dependents();
+  for (int head = threadIdx.x / kLanes; head < heads; head += kHeadsAtOnce) {
+    const bool is_q = head < H;
+    const bool is_k = !is_q && head < H + KV;
+    __nv_bfloat16* dst;
+    if (is_q) {
+      dst = q_out + ((size_t)t * H + head) * HD;
+    } else {
+      if (slot < 0) continue;
+      const int kvh = is_k ? head - H : head - H - KV;
+      const size_t block = slot / block_size, off = slot % block_size;
+      dst = (is_k ? k_cache : v_cache) + ((block * KV + kvh) * block_size + off) * (size_t)HD;
+    }
+    const uint4 raw = *reinterpret_cast<const uint4*>(qkv + ((size_t)t * heads + head) * HD + e0);
+    if (!is_q && !is_k) {
+      *reinterpret_cast<uint4*>(dst + e0) = raw;
+      continue;
+    }
+    const __nv_bfloat16* in = reinterpret_cast<const __nv_bfloat16*>(&raw);
+    float x[8];
+    float ss = 0.f;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      x[k] = __bfloat162float(in[k]);
+      ss += x[k] * x[k];
+    }
+    if (is_q ? q_gain != nullptr : k_gain != nullptr) {
+#pragma unroll
+      for (int o = kLanes / 2; o > 0; o >>= 1) ss += __shfl_xor_sync(group, ss, o);
+      const float rstd = rsqrtf(ss / (float)HD + eps);
+#pragma unroll
+      for (int k = 0; k < 8; ++k) x[k] = x[k] * rstd * (is_q ? gq[k] : gk[k]);
+    }
+    uint4 packed;
+    __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(&packed);
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      float y = x[k];
+      if (inv_freq) {
+        const float other = __shfl_xor_sync(group, x[k], kLanes / 2);
+        y = sub < kLanes / 2 ? x[k] * cs[k] - other * sn[k] : x[k] * cs[k] + other * sn[k];
+      }
+      o[k] = __float2bfloat16_rn(y);
+    }
+    *reinterpret_cast<uint4*>(dst + e0) = packed;
+  }
+}
+
 template <typename T, int EPT>
 void launch_vec(T* q_out, T* k_cache, T* v_cache, const T* qkv, const asb::PartialSums& ps, const float* q_gain,
                 const float* k_gain, const float* inv_freq, const int* positions, const int* slots,
                 int num_tokens, int H, int KV, int block_size, float eps, cudaStream_t stream) {
+  if constexpr (sizeof(T) == 2 && EPT >= 2) {  // (EPT 1 is head size 32: four lanes a head; left to the kernel below)
+    if (num_tokens >= 256 && !ps.ws) {
+      asb::launch(qk_norm_rope_store_wide_kernel<EPT * 32>, num_tokens, kWarps * 32, 0, stream,
+                  (__nv_bfloat16*)q_out, (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, (const __nv_bfloat16*)qkv,
+                  q_gain, k_gain, inv_freq, positions, slots, H, KV, block_size, eps);
+      return;
+    }
+  }
   if (num_tokens >= 256) {
     const int heads_per_block = kWarps * 4;
     dim3 grid(num_tokens, (H + 2 * KV + heads_per_block - 1) / heads_per_block);

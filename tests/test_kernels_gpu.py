@@ -139,6 +139,45 @@ def test_qk_norm_rope_store(ops, dtype, H, KV, hd, bs):
     assert float(kflat[untouched].abs().max()) == 0 and float(vflat[untouched].float().abs().max()) == 0
 
 
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("H,KV,hd,bs,gains", [(32, 8, 128, 16, True), (5, 1, 64, 8, True), (3, 3, 256, 4, False),
+                                              (6, 2, 32, 16, True), (7, 1, 48, 8, True)])  # fmt: skip
+def test_qk_norm_rope_store_many_tokens(ops, dtype, H, KV, hd, bs, gains):
+    """The forms that portions of hundreds of tokens take (a block per token, several heads a
+    warp), at head counts that leave warps half used, with some tokens not stored."""
+    T, eps, theta = 300, 1e-6, 5e5
+    g = torch.Generator().manual_seed(hd + H)
+    qkv = torch.randn(T, (H + 2 * KV) * hd, generator=g).cuda().to(dtype)
+    qg, kg = ((1 + 0.1 * torch.randn(hd, generator=g)).cuda() if gains else None for _ in range(2))
+    inv_freq = plain.rope_inv_freq(hd, theta).cuda()
+    pos = torch.randint(0, 30000, (T,), generator=g).int().cuda()
+    nblocks = T // bs + 3
+    slot_list = torch.randperm(nblocks * bs, generator=g)[:T].tolist()
+    for i in range(0, T, 7):
+        slot_list[i] = -1
+    slots = torch.tensor(slot_list, dtype=torch.int32, device="cuda")
+    kc = torch.zeros(nblocks, KV, bs, hd, device="cuda", dtype=dtype)
+    vc = torch.zeros_like(kc)
+    q = ops.qk_norm_rope_store(qkv, H, KV, hd, pos, q_gain=qg, k_gain=kg, eps=eps if gains else 0.0, inv_freq=inv_freq,
+                               rotary_dim=hd, slots=slots, k_cache=kc, v_cache=vc)  # fmt: skip
+    x = qkv.float().cpu().view(T, H + 2 * KV, hd)
+    angles = plain.rope_angles(pos.cpu().long(), hd, theta)
+    normed = (lambda v, gain: plain.rms_norm(v, gain.cpu(), eps)) if gains else (lambda v, gain: v)
+    q_ref = plain.apply_rope(normed(x[:, :H], qg), angles)
+    k_ref = plain.apply_rope(normed(x[:, H : H + KV], kg), angles)
+    t = dict(atol=3e-4, rtol=1e-4) if dtype == torch.float32 else tol(dtype)
+    assert torch.allclose(q.float().cpu(), q_ref, **t)
+    kflat = kc.float().cpu().permute(0, 2, 1, 3).reshape(nblocks * bs, KV, hd)
+    vflat = vc.cpu().permute(0, 2, 1, 3).reshape(nblocks * bs, KV, hd)
+    stored = torch.tensor([s >= 0 for s in slot_list])
+    at = torch.tensor([s for s in slot_list if s >= 0])
+    assert torch.allclose(kflat[at], k_ref[stored], **t)
+    assert torch.equal(vflat[at], qkv.cpu().view(T, H + 2 * KV, hd)[stored][:, H + KV :])
+    untouched = torch.ones(nblocks * bs, dtype=torch.bool)
+    untouched[at] = False
+    assert float(kflat[untouched].abs().max()) == 0 and float(vflat[untouched].float().abs().max()) == 0
+
+
 def paged_setup(ctx_lens, q_lens, H, KV, hd, bs, dtype, seed=0, special=None):
     """Random q/k/v for R requests; keys/values scattered over shuffled pages. Returns device
     inputs and the dense per-request k, v for the reference. `special` = (request, position):
