@@ -201,7 +201,7 @@ struct Config {
   static constexpr int kTileQ = BN * BK * 2;
   static constexpr int kStage = kTileP + kTileQ;
   static constexpr int kStages = BN >= 256 ? 4 : (BN >= 128 ? 6 : 8);
-  static constexpr int kIssuers = BN <= 64 ? 2 : 1;             // threads that issue MMAs, an accumulator each
+  static constexpr int kIssuers = BN <= 128 ? 2 : 1;            // threads that issue MMAs, an accumulator each
   static constexpr int kThreads = 192 + 32 * (kIssuers - 1);
   static constexpr int kAccCols = kIssuers * BN;                // tensor-memory columns of one buffer
   static constexpr int kTmemCols = 2 * kAccCols < 32 ? 32 : 2 * kAccCols;   // two buffers
