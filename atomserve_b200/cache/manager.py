@@ -89,6 +89,7 @@ class CacheManager:
                 self.entry_state[i] = {
                     s.name: self.state.register(f"{i}.{s.name}", tuple(s.shape), s.dtype) for s in states
                 }
+        self._windowed = any(g.window is not None for g in self.groups)  # only windows release pages early
         if self.device is not None:
             for g in self.groups:
                 shape = (len(g.entries), num_blocks, g.spec.num_kv_heads, block_size, g.spec.head_dim)
@@ -150,9 +151,12 @@ class CacheManager:
         """Make room for positions [start, start + num_new) in every group, or in none.
         Pages a window has passed are released first (that is never undone: no later step
         reads them)."""
-        self.release_passed(rc, start)
+        if self._windowed:
+            self.release_passed(rc, start)
         needed = blocks_for_tokens(start + num_new, self.block_size)
         missing = [max(0, needed - len(t)) for t in rc.block_tables]
+        if not any(missing):
+            return True  # the usual decode step: the last page still has room
         if any(m > g.allocator.num_free for g, m in zip(self.groups, missing)):
             return False
         for g, table, m in zip(self.groups, rc.block_tables, missing):

@@ -76,6 +76,10 @@ class ModelRunner:
         self._graph_pool = None
         # request uid -> (generation, per group a numpy copy of its block table, extended as it grows)
         self._tables: dict[int, tuple[int, list[np.ndarray]]] = {}
+        # decode steps: per group a host matrix [state slot, page] of the live requests' block tables,
+        # kept up to date row by row, so that a step's tables are one gather instead of a loop of copies
+        self._matrix: list[np.ndarray] = [np.zeros((0, 0), dtype=np.int32) for _ in cache.groups]
+        self._row_owner: list[dict[int, tuple[int, int, int]]] = [{} for _ in cache.groups]  # slot -> (uid, generation, pages held)
         self._host: torch.Tensor | None = None
         self._dev: torch.Tensor | None = None
         self.last_upload_bytes = 0  # size of the last step's packed host-to-device copy
@@ -85,19 +89,23 @@ class ModelRunner:
     def validate(self, rows: list[Row]) -> None:
         bs = self.block_size
         vocab = self.model.spec.vocab_size
+        groups = self.cache.groups
         for r in rows:
-            n = len(r.tokens)
+            tokens = r.tokens
+            n = len(tokens)
             if n < 1:
                 raise ValueError("a row must bring at least one token")
-            if min(r.tokens) < 0 or max(r.tokens) >= vocab:
+            lowest, highest = (tokens[0], tokens[0]) if n == 1 else (min(tokens), max(tokens))
+            if lowest < 0 or highest >= vocab:
                 raise ValueError(f"a token id lies outside [0, {vocab})")
             if r.start < 0:
                 raise ValueError(f"a row starts at position {r.start}")
-            if any(not 0 <= w < n for w in r.want):
-                raise ValueError(f"wanted places {r.want} lie outside the row's {n} tokens")
-            if len(r.cache.block_tables) != len(self.cache.groups):
+            for w in r.want:
+                if not 0 <= w < n:
+                    raise ValueError(f"wanted places {r.want} lie outside the row's {n} tokens")
+            if len(r.cache.block_tables) != len(groups):
                 raise ValueError("the row's request has block tables for another set of cache groups")
-            for g, table in zip(self.cache.groups, r.cache.block_tables):
+            for g, table in zip(groups, r.cache.block_tables):
                 if (r.start + n) > len(table) * bs:
                     raise ValueError(f"block table holds {len(table) * bs} slots, the row needs {r.start + n}")
                 if g.window is not None:  # only windows release pages before a request ends
@@ -119,6 +127,36 @@ class ModelRunner:
             have = np.concatenate([have, np.asarray(table[len(have) :], dtype=np.int32)])
         cached[g] = have
         return have
+
+    def _table_matrix(self, g: int, rows: list[Row], slot_ids: list[int], width: int) -> np.ndarray:
+        """Group g's matrix with the rows of these requests (each in its state slot) brought up to
+        date: a row is zeroed when its slot passes to another request or the request starts again,
+        and takes the pages added since (entries a window released keep their old id: never read)."""
+        m = self._matrix[g]
+        need_rows, need_cols = max(slot_ids) + 1, width
+        if m.shape[0] < need_rows or m.shape[1] < need_cols:
+            grown = np.zeros((max(need_rows, m.shape[0]), max(2 * need_cols, m.shape[1])), dtype=np.int32)
+            grown[: m.shape[0], : m.shape[1]] = m
+            m = self._matrix[g] = grown
+            for slot, (uid, generation, held) in list(self._row_owner[g].items()):
+                self._row_owner[g][slot] = (uid, generation, min(held, m.shape[1]))
+        owners = self._row_owner[g]
+        cap = m.shape[1]
+        for r, slot in zip(rows, slot_ids):
+            rc = r.cache
+            table = rc.block_tables[g]
+            owner = owners.get(slot)
+            if owner is None or owner[0] != rc.uid or owner[1] != rc.generation:
+                m[slot, :] = 0
+                held = 0
+            else:
+                held = owner[2]
+                if held >= len(table):
+                    continue
+            upto = min(len(table), cap)
+            m[slot, held:upto] = table[held:upto]
+            owners[slot] = (rc.uid, rc.generation, upto)
+        return m
 
     def _layout(self, T: int, R: int, W: list[int], B: int) -> _Packed:
         lay = _Packed()
@@ -169,7 +207,21 @@ class ModelRunner:
         qs, ps, ss, lr = (hv[k].numpy() for k in ("req_q_start", "req_pos_start", "state_slots", "logits_rows"))
         flat = b = 0
         max_context = 0
-        for i, r in enumerate(rows):
+        single = T == R  # every row brings one token (a decode step): no per-token loops
+        if single:
+            starts = [r.start for r in rows]
+            tok[:real] = [r.tokens[0] for r in rows]
+            pos[:real] = starts
+            ps[:real] = starts
+            qs[:real] = range(real)
+            ss[:real] = [r.cache.state_slot for r in rows]
+            for i, r in enumerate(rows):
+                if r.want:
+                    lr[b] = i
+                    b += 1
+            flat = real
+            max_context = max(starts) + 1
+        for i, r in enumerate(() if single else rows):
             n = len(r.tokens)
             tok[flat : flat + n] = r.tokens
             pos[flat : flat + n] = range(r.start, r.start + n)
@@ -184,10 +236,18 @@ class ModelRunner:
             flat += 1
             b += 1
         qs[R] = flat
+        slot_ids = [r.cache.state_slot for r in rows] if single else []
+        gather = single and real > 0 and min(slot_ids) >= 0  # every request sits in a state slot of its own
         for g, width in enumerate(widths):
             slots, tables = hv[f"slots{g}"].numpy(), hv[f"tables{g}"].numpy().reshape(R, width)
             flat = 0
-            for i, r in enumerate(rows):
+            if gather:
+                m = self._table_matrix(g, rows, slot_ids, width)
+                at, first = np.asarray(slot_ids), np.asarray(starts)
+                tables[:real] = m[at, :width]
+                slots[:real] = m[at, first // bs].astype(np.int64) * bs + first % bs
+                flat = real
+            for i, r in enumerate(() if gather else rows):
                 table = self._table_array(r.cache, g)
                 n = len(r.tokens)
                 used = min(len(table), width)
