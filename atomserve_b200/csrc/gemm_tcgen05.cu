@@ -639,7 +639,7 @@ Plan make_plan(int M, int N, int K) {
     const int sms_now = sm_count();
     const int token_tiles = (M + BM - 1) / BM;
     double best = 1e30;
-    for (int bn = 256; bn >= 128; bn -= 32) {
+    for (int bn = 256; bn >= 128; bn -= 32) {  // multiples of 32: the epilogue reads 32 columns at a time
       const int tiles = token_tiles * ((N + bn - 1) / bn);
       const double cost = (double)((tiles + sms_now - 1) / sms_now) * (128 + bn);
       if (cost < best) { best = cost; pl.bn = bn; }
