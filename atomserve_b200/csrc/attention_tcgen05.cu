@@ -13,9 +13,10 @@
 //   warp 0     TMA: the Q tile once, then per key tile the pages of K and of V named by the
 //              block table, each page as two boxes (the two 64-element halves of the head).
 //   warp 1     MMA: S[b] = Q K^T into score buffer b = tile & 1 (two buffers, so the next tile's
-//              scores are computed while this tile's softmax runs), then O += P V once the
-//              softmax has written P. V is consumed as an MN-major operand: its rows in shared
-//              memory are keys, exactly as the pages hold them.
+//              scores are computed while this tile's softmax runs).
+//   warp 6     MMA: O += P V once the softmax has written P. V is consumed as an MN-major operand:
+//              its rows in shared memory are keys, exactly as the pages hold them. (A thread of
+//              its own, because issuing the next tile's Q K^T would hold this product back.)
 //   warps 2-5  softmax: thread r owns row r (a TMEM lane), so row maxima and sums need no
 //              shuffles. It reads its scores once, rescales its row of O in tensor memory only when
 //              the maximum moved by more than a factor of 256, writes P as bfloat16 into the
@@ -32,7 +33,7 @@ namespace {
 
 using namespace asb::t5;
 
-constexpr int kThreads = 192;
+constexpr int kThreads = 224;
 constexpr int HD = 128;
 constexpr int kRows = 128;
 constexpr int kKeys = 64;                         // keys per tile
@@ -90,7 +91,8 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
   auto s_full = [&](int b) { return bars + 8u * (1 + 2 * kStages + b); };
   const uint32_t p_full = bars + 8u * (3 + 2 * kStages);
   auto pv_done = [&](int b) { return bars + 8u * (4 + 2 * kStages + b); };  // one per P buffer
-  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(aligned + kQBytes + kStages * kStageBytes + kPBuffers * kPBytes + 8 * (6 + 2 * kStages));
+  auto s_empty = [&](int b) { return bars + 8u * (6 + 2 * kStages + b); };  // score buffer b has been read out
+  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(aligned + kQBytes + kStages * kStageBytes + kPBuffers * kPBytes + 8 * (8 + 2 * kStages));
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   // The 1 KB beyond the tiles holds the alignment padding and, after it, the barriers.
@@ -135,6 +137,8 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
     mbar_init(p_full, 4);  // one arrival per softmax warp
     mbar_init(pv_done(0), 1);
     mbar_init(pv_done(1), 1);
+    mbar_init(s_empty(0), 4);  // one arrival per softmax warp
+    mbar_init(s_empty(1), 4);
     mbar_init_fence();
   }
   if (warp == 1) tmem_alloc(smem_u32((const void*)tmem_slot), kTmemCols);
@@ -149,7 +153,7 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
 
   if (warp == 0) {
     // The whole warp looks up the pages of a key tile (one page per lane, the loads in flight
-    // together); lane 0 waits for the stage and issues the TMA loads.
+    // together); lane 0 waits for the stage, and the lanes issue the tile's TMA loads together.
     if (lane == 0) {
       mbar_expect_tx(q_full, kQBytes);
       tma_load_3d(q_smem, &map_q, q_full, 0, head0, row0);
@@ -178,21 +182,23 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
       }
       ok = __shfl_sync(0xffffffffu, ok_i, 0) != 0;
       if (!ok) break;
-      for (int i = 0; i < boxes_per_tile; ++i) {
+      // one box per lane: box i's four copies (K and V, the two halves of the head) go out from
+      // lanes 4i..4i+3 in one instruction instead of one after another from a single lane
+      {
+        const int i = lane >> 2, which = lane & 3;
         const int y = __shfl_sync(0xffffffffu, row_y, i);
-        if (lane == 0) {
-          const uint32_t off = (uint32_t)(i * box_rows) * 128u;
-          tma_load_2d(k_smem(s) + off, &map_k, kv_full(s), 0, y);
-          tma_load_2d(k_smem(s) + kKVBlockBytes + off, &map_k, kv_full(s), 64, y);
-          tma_load_2d(v_smem(s) + off, &map_v, kv_full(s), 0, y);
-          tma_load_2d(v_smem(s) + kKVBlockBytes + off, &map_v, kv_full(s), 64, y);
+        if (i < boxes_per_tile) {
+          const uint32_t off = (uint32_t)(i * box_rows) * 128u + (uint32_t)(which & 1) * kKVBlockBytes;
+          if (which < 2) tma_load_2d(k_smem(s) + off, &map_k, kv_full(s), (which & 1) * 64, y);
+          else tma_load_2d(v_smem(s) + off, &map_v, kv_full(s), (which & 1) * 64, y);
         }
       }
     }
   } else if (warp == 1) {
+    // Q K^T, one tile ahead of the softmax. (Issuing a tcgen05.mma takes its thread 60-80 cycles
+    // whatever its shape, so the two products have a thread each: warp 6 issues P V.)
     if (lane == 0) {
       constexpr uint32_t idesc_qk = instr_desc_bf16(kRows, kKeys, false);
-      constexpr uint32_t idesc_pv = instr_desc_bf16(kRows, HD, true);
       auto issue_qk = [&](int j) {
         const int s = j % kStages;
 #pragma unroll
@@ -210,13 +216,21 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
         fence_after_sync();
         issue_qk(0);
       }
+      for (int j = 0; j + 1 < num_tiles && ok; ++j) {
+        ok = mbar_wait(kv_full((j + 1) % kStages), ((uint32_t)(j + 1) / kStages) & 1u, p.status, 14);
+        // score buffer (j + 1) & 1 held tile j - 1, the buffer's use number (j - 1) / 2: read out?
+        if (ok && j >= 1) ok = mbar_wait(s_empty((j + 1) & 1), ((uint32_t)(j - 1) >> 1) & 1u, p.status, 18);
+        if (!ok) break;
+        fence_after_sync();
+        issue_qk(j + 1);
+      }
+    }
+  } else if (warp == 6) {
+    // O += P V as soon as the softmax has written a tile's P
+    if (lane == 0) {
+      constexpr uint32_t idesc_pv = instr_desc_bf16(kRows, HD, true);
+      bool ok = true;
       for (int j = 0; j < num_tiles && ok; ++j) {
-        if (j + 1 < num_tiles) {
-          ok = mbar_wait(kv_full((j + 1) % kStages), ((uint32_t)(j + 1) / kStages) & 1u, p.status, 14);
-          if (!ok) break;
-          fence_after_sync();
-          issue_qk(j + 1);
-        }
         ok = mbar_wait(p_full, (uint32_t)j & 1u, p.status, 15);
         if (!ok) break;
         fence_after_sync();
@@ -229,6 +243,7 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
           umma_bf16(tmem_o, a, b, idesc_pv, (uint32_t)((j | ks) != 0));
         }
         umma_commit(pv_done(j % kPBuffers));
+        // (Q K^T of this tile completed before its softmax ran, so this commit frees K as well as V)
         umma_commit(kv_empty(s));
       }
     }
@@ -260,6 +275,10 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
 #pragma unroll
       for (int c = 0; c < kKeys; c += 32) tmem_ld32_nowait(tmem_s(j) + lane_addr + (uint32_t)c, raw + c);
       tmem_ld_wait();
+      // the scores are in registers: the buffer may take the Q K^T of the tile after next
+      fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(s_empty(j & 1));
       float raw_max = -INFINITY;
       if (inside) {
 #pragma unroll
