@@ -58,6 +58,52 @@ def test_step_function_matches_the_oracle_in_a_mixed_batch(setup):
     assert torch.allclose(second[9:], ob[[10, 3]], atol=2e-4)
 
 
+def test_decode_steps_pack_the_block_tables_of_whoever_holds_the_slot(setup):
+    """Steps of single tokens gather their block tables from a matrix kept per state slot: it has
+    to follow tables that grow, a slot that passes to another request, a request that is freed
+    and starts again, and requests that skip steps."""
+    import random
+
+    cfg, bs, w, model = setup
+    cache = CacheManager(model.cache_requirements(), bs, 64, 3, torch.float32, "cpu")
+    runner = ModelRunner(model, cache, cuda_graphs=False)
+    rng = random.Random(3)
+    live = {}  # uid -> [request, tokens held]
+    for step in range(120):
+        if len(live) < 3 and rng.random() < 0.5:
+            rc = cache.new_request()
+            assert cache.admit(rc)
+            n = rng.randint(1, 3 * bs)
+            assert cache.reserve(rc, 0, n)
+            runner.step([Row([1] * n, 0, rc, [])])  # a prompt portion: the general path
+            live[rc.uid] = [rc, n]
+        if live and rng.random() < 0.15:
+            rc = live.pop(rng.choice(list(live)))[0]
+            cache.free(rc)  # the slot goes back; the next request may get it
+            if rng.random() < 0.5:  # the same request starts again
+                assert cache.admit(rc) and cache.reserve(rc, 0, 2)
+                runner.step([Row([2, 3], 0, rc, [])])
+                live[rc.uid] = [rc, 2]
+        rows = []
+        for rc, held in live.values():
+            if rng.random() < 0.8 and held + 1 < 12 * bs and cache.reserve(rc, held, 1):
+                rows.append(Row([5], held, rc, [0]))
+        if not rows:
+            continue
+        with torch.inference_mode():  # as inside ModelRunner.step
+            ctx, groups, _ = runner.prepare(rows)
+        for g, (slots, tables) in enumerate(groups):
+            group = cache.groups[g]
+            for i, r in enumerate(rows):
+                table = r.cache.block_tables[g]
+                first = cache.first_needed_block(group, r.start)
+                needed = r.start // bs + 1
+                assert tables[i, first:needed].tolist() == table[first:needed], (step, g, i)
+                assert int(slots[i]) == table[r.start // bs] * bs + r.start % bs
+        for r in rows:
+            live[r.cache.uid][1] += 1
+
+
 def test_runner_rejects_bad_rows(setup):
     cfg, bs, w, model = setup
     cache = CacheManager(model.cache_requirements(), bs, 8, 2, torch.float32, "cpu")
