@@ -406,12 +406,16 @@ decode_attention_kernel(const MmaParams p) {
       mm[warp * 16 + g] = m[0]; mm[warp * 16 + g + 8] = m[1];
       ml[warp * 16 + g] = l[0]; ml[warp * 16 + g + 8] = l[1];
     }
+    // only the rows that are query heads (gc of the 16) are read back
+    if (g < gc) {
 #pragma unroll
-    for (int i = 0; i < HD / 8; ++i) {
-      float* a0 = ma + ((size_t)(warp * 16 + g) * HD + i * 8 + t * 2);
-      float* a1 = ma + ((size_t)(warp * 16 + g + 8) * HD + i * 8 + t * 2);
-      a0[0] = acc[i][0]; a0[1] = acc[i][1];
-      a1[0] = acc[i][2]; a1[1] = acc[i][3];
+      for (int i = 0; i < HD / 8; ++i)
+        *reinterpret_cast<float2*>(ma + ((size_t)(warp * 16 + g) * HD + i * 8 + t * 2)) = make_float2(acc[i][0], acc[i][1]);
+    }
+    if (g + 8 < gc) {
+#pragma unroll
+      for (int i = 0; i < HD / 8; ++i)
+        *reinterpret_cast<float2*>(ma + ((size_t)(warp * 16 + g + 8) * HD + i * 8 + t * 2)) = make_float2(acc[i][2], acc[i][3]);
     }
   }
   __syncthreads();
