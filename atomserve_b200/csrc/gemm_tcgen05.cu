@@ -382,7 +382,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_cons
           // K is cut only with swapped operands: lanes are output columns, and a warp's 32 lanes
           // store 128 contiguous bytes of the slot's [column][lane] layout per instruction
 #pragma unroll
-          for (int j = 0; j < kChunk; ++j) slot[(size_t)(c + j) * BM + row] = __uint_as_float(raw[j]);
+          for (int j = 0; j < kChunk; ++j)
+            if (q0 + c + j < p.q_rows) slot[(size_t)(c + j) * BM + row] = __uint_as_float(raw[j]);  // tokens that exist
           continue;
         }
         if (p.epilogue == kStoreSwiGLU) {
@@ -523,6 +524,7 @@ __global__ void segment_reduce_kernel(const GemmParams p, int parts) {
   asb::pdl_launch_dependents();
   if (slots == 1) return;  // one block covered all of K and stored the tile itself
   if (i >= BM * BN) return;
+  if (q0 + i / BM >= p.q_rows) return;  // a column (token) beyond the matrix: its slots were not written
   float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
   for (int s0 = 0; s0 < slots; s0 += 4) {  // four loads in flight; the sum still runs in slot order
     float4 a[4];
