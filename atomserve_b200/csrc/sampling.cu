@@ -71,32 +71,102 @@ struct Scratch {
   int cand_n;
 };
 
-// Descending radix select over 32-bit keys. `item(i, key, weight)` says whether element i takes
+// Calls f(i, value, valid) for every element of the row, the same number of times in every
+// thread of the block (valid false: no such element), so that f may use warp-wide ballots. The
+// full row is read with 16-byte loads, four in flight per thread; one scalar load per trip would
+// leave a row of 150,000 logits bound by the latency of its loads.
+template <typename F>
+__device__ __forceinline__ void for_each_value(const RowView& row, F f) {
+  int done = 0;
+  if (row.id == nullptr && ((uintptr_t)row.val & 15) == 0) {
+    const float4* v4 = reinterpret_cast<const float4*>(row.val);
+    const int n4 = row.n >> 2;
+    for (int base = 0; base < n4; base += blockDim.x * 4) {
+      float4 x[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int at = base + threadIdx.x + u * blockDim.x;
+        x[u] = at < n4 ? v4[at] : make_float4(0.f, 0.f, 0.f, 0.f);
+      }
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int at = base + threadIdx.x + u * blockDim.x;
+        const float e[4] = {x[u].x, x[u].y, x[u].z, x[u].w};
+#pragma unroll
+        for (int k = 0; k < 4; ++k) f(at * 4 + k, e[k], at < n4);
+      }
+    }
+    done = n4 << 2;
+  }
+  for (int base = done; base < row.n; base += blockDim.x) {
+    const int i = base + threadIdx.x;
+    const bool valid = i < row.n;
+    f(i, valid ? row.value(i) : 0.f, valid);
+  }
+}
+
+// Descending radix select over 32-bit keys. `item(i, value, key, weight)` says whether element i takes
 // part, its key and its non-negative integer weight. Finds the largest key c such that the
 // weight of all taking-part elements with key > c is < target <= that weight plus the weight
 // of key == c. Returns c, and in `above` the weight strictly above c. (With weight 1 and
 // target k this is the k-th largest key.) If the total weight is below target, returns 0 with
 // `above` = total: everything is kept.
-template <typename Item>
+//
+// `last_shift` 16 stops after the two high digits: the result then has its low 16 bits clear and
+// names a bin of 65,536 keys, `above` and `equal` counting what lies above and inside it.
+//
+// A whole row's first digit falls into a handful of bins (sign and exponent of logits that lie
+// close together), so lanes of a warp that hit the same bin hand their weight to one of them
+// before the atomic addition: up to three such groups a warp, the rest add for themselves.
+//
+// kUnit: every weight is 1 (a count). A group's weight is then its number of lanes, and the
+// histograms are 32-bit, whose shared-memory atomics are native (64-bit ones are not).
+template <bool kUnit, typename Item>
 __device__ uint32_t radix_select(const RowView& row, Scratch& s, unsigned long long target,
-                                 unsigned long long* above, unsigned long long* equal, Item item) {
+                                 unsigned long long* above, unsigned long long* equal, Item item,
+                                 int last_shift = 0) {
   uint32_t prefix = 0, mask = 0;
   unsigned long long acc = 0;
-  for (int shift = 24; shift >= 0; shift -= 8) {
+  const int lane = threadIdx.x & 31;
+  for (int shift = 24; shift >= last_shift; shift -= 8) {
     for (int i = threadIdx.x; i < kHistCopies * kBins; i += blockDim.x) (&s.hist[0][0])[i] = 0ull;
     __syncthreads();
     unsigned long long* h = s.hist[(threadIdx.x >> 5) % kHistCopies];
-    for (int i = threadIdx.x; i < row.n; i += blockDim.x) {
-      uint32_t key;
-      unsigned long long w;
-      if (item(i, key, w) && (key & mask) == prefix && w) atomicAdd(&h[(key >> shift) & 255u], w);
-    }
+    unsigned int* h32 = reinterpret_cast<unsigned int*>(h);  // kUnit: the copy's first 256 words
+    for_each_value(row, [&](int i, float v, bool valid) {
+      uint32_t key = 0;
+      unsigned long long w = 0;
+      bool take = valid && item(i, v, key, w) && (key & mask) == prefix && w;
+      const uint32_t bin = (key >> shift) & 255u;
+      unsigned remaining = __ballot_sync(0xffffffffu, take);
+      for (int round = 0; round < 3 && remaining; ++round) {
+        const int leader = __ffs(remaining) - 1;
+        const uint32_t leader_bin = __shfl_sync(0xffffffffu, bin, leader);
+        const bool mine = take && bin == leader_bin;
+        const unsigned group = __ballot_sync(0xffffffffu, mine);
+        if (kUnit) {
+          if (lane == leader) atomicAdd(&h32[leader_bin], (unsigned int)__popc(group));
+        } else {
+          unsigned long long sum = mine ? w : 0ull;
+          if (group & (group - 1))  // more than one lane in the group (the whole warp agrees)
+            for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+          if (lane == leader) atomicAdd(&h[leader_bin], sum);
+        }
+        if (mine) take = false;
+        remaining &= ~group;
+      }
+      if (take) {
+        if (kUnit) atomicAdd(&h32[bin], 1u);
+        else atomicAdd(&h[bin], w);
+      }
+    });
     __syncthreads();
-    if (threadIdx.x < kBins) {
-      unsigned long long t = 0;
-      for (int c = 0; c < kHistCopies; ++c) t += s.hist[c][threadIdx.x];
-      s.hist[0][threadIdx.x] = t;
-    }
+    unsigned long long bin_total = 0;
+    if (threadIdx.x < kBins)
+      for (int c = 0; c < kHistCopies; ++c)
+        bin_total += kUnit ? (unsigned long long)reinterpret_cast<const unsigned int*>(s.hist[c])[threadIdx.x] : s.hist[c][threadIdx.x];
+    __syncthreads();  // copy 0's 32-bit words lie where the 64-bit totals are written next
+    if (threadIdx.x < kBins) s.hist[0][threadIdx.x] = bin_total;
     __syncthreads();
     if (threadIdx.x == 0) {
       int digit = -1;
@@ -146,15 +216,15 @@ __device__ Cut cut_with_ties(const RowView& row, Scratch& s, uint32_t key, unsig
   const unsigned long long want = (need + unit - 1) / unit;
   if (want * unit >= equal) return cut;  // all of them: no pass over the ids
   unsigned long long dummy, dummy2;
-  auto by_id = [&](int i, uint32_t& k2, unsigned long long& w2) {
+  auto by_id = [&](int i, float v, uint32_t& k2, unsigned long long& w2) {
     uint32_t k;
     unsigned long long w;
-    if (!item(i, k, w) || k != key) return false;
+    if (!item(i, v, k, w) || k != key) return false;
     k2 = ~(uint32_t)row.token(i);  // descending on ~id is ascending on id
     w2 = 1ull;
     return true;
   };
-  const uint32_t idk = radix_select(row, s, want, &dummy, &dummy2, by_id);
+  const uint32_t idk = radix_select<true>(row, s, want, &dummy, &dummy2, by_id);
   if (idk != 0u) cut.id = (int)~idk;
   return cut;
 }
@@ -249,44 +319,66 @@ sample_rows_kernel(int* __restrict__ out, const float* __restrict__ logits, int 
   const int k = top_k[b];
   Cut kcut{0u, 0x7fffffff};
   if (k > 0 && k < V) {
-    auto unit = [&](int i, uint32_t& key, unsigned long long& w) {
-      key = order_key(row.value(i));
+    auto unit = [&](int i, float v, uint32_t& key, unsigned long long& w) {
+      key = order_key(v);
       w = 1ull;
       return true;
     };
     unsigned long long above, equal;
-    const uint32_t key = radix_select(row, s, (unsigned long long)k, &above, &equal, unit);
-    kcut = cut_with_ties(row, s, key, (unsigned long long)k - above, equal, 1ull, unit);
-    if (k <= kCompact) {  // later passes read the candidates from shared memory
-      if (threadIdx.x == 0) s.cand_n = 0;
-      __syncthreads();
-      for (int i = threadIdx.x; i < V; i += blockDim.x) {
-        const float v = row.value(i);
-        if (kcut.keeps(order_key(v), i)) {
-          const int at = atomicAdd(&s.cand_n, 1);
-          if (at < kCompact) { s.cand_val[at] = v; s.cand_id[at] = i; }
-        }
+    bool early = false;
+    if (k <= kCompact) {
+      // The two high digits of the k-th largest key: if everything from that bin of 65,536 keys
+      // upwards fits the candidate buffer (it holds at least k), gather it now and finish the
+      // selection, like all later passes, on the candidates in shared memory.
+      const uint32_t high = radix_select<true>(row, s, (unsigned long long)k, &above, &equal, unit, 16);
+      if (above + equal <= (unsigned long long)kCompact) {
+        early = true;
+        if (threadIdx.x == 0) s.cand_n = 0;
+        __syncthreads();
+        for_each_value(row, [&](int i, float v, bool valid) {
+          if (valid && order_key(v) >= high) {
+            const int at = atomicAdd(&s.cand_n, 1);
+            if (at < kCompact) { s.cand_val[at] = v; s.cand_id[at] = i; }
+          }
+        });
+        __syncthreads();
+        row = RowView{s.cand_val, s.cand_id, min(s.cand_n, kCompact)};
+        const uint32_t key = radix_select<true>(row, s, (unsigned long long)k, &above, &equal, unit);
+        kcut = cut_with_ties(row, s, key, (unsigned long long)k - above, equal, 1ull, unit);
       }
-      __syncthreads();
-      row = RowView{s.cand_val, s.cand_id, min(s.cand_n, kCompact)};
-      kcut = Cut{0u, 0x7fffffff};
+    }
+    if (!early) {
+      const uint32_t key = radix_select<true>(row, s, (unsigned long long)k, &above, &equal, unit);
+      kcut = cut_with_ties(row, s, key, (unsigned long long)k - above, equal, 1ull, unit);
+      if (k <= kCompact) {  // later passes read the candidates from shared memory
+        if (threadIdx.x == 0) s.cand_n = 0;
+        __syncthreads();
+        for_each_value(row, [&](int i, float v, bool valid) {
+          if (valid && kcut.keeps(order_key(v), i)) {
+            const int at = atomicAdd(&s.cand_n, 1);
+            if (at < kCompact) { s.cand_val[at] = v; s.cand_id[at] = i; }
+          }
+        });
+        __syncthreads();
+        row = RowView{s.cand_val, s.cand_id, min(s.cand_n, kCompact)};
+        kcut = Cut{0u, 0x7fffffff};
+      }
     }
   }
 
   // total mass of the kept, then the top-p cut
-  auto massed = [&](int i, uint32_t& key, unsigned long long& w) {
-    const float v = row.value(i);
+  auto massed = [&](int i, float v, uint32_t& key, unsigned long long& w) {
     key = order_key(v);
     if (!kcut.keeps(key, row.token(i))) return false;
     w = mass_of(v, vmax, inv_t);
     return true;
   };
   unsigned long long total = 0;
-  for (int i = threadIdx.x; i < row.n; i += blockDim.x) {
+  for_each_value(row, [&](int i, float v, bool valid) {
     uint32_t key;
     unsigned long long w;
-    if (massed(i, key, w)) total += w;
-  }
+    if (valid && massed(i, v, key, w)) total += w;
+  });
   {
     // integer sum over the block: exact, so independent of the order
     for (int o = 16; o > 0; o >>= 1) total += __shfl_xor_sync(0xffffffffu, total, o);
@@ -312,7 +404,7 @@ sample_rows_kernel(int* __restrict__ out, const float* __restrict__ logits, int 
     if (target < 1ull) target = 1ull;  // the best token always stays
     if (target > total) target = total;
     unsigned long long above, equal;
-    const uint32_t key = radix_select(row, s, target, &above, &equal, massed);
+    const uint32_t key = radix_select<false>(row, s, target, &above, &equal, massed);
     // mass of one tied token (all ties share the key, hence the value)
     unsigned long long unit = mass_of(__uint_as_float((key & 0x80000000u) ? (key & 0x7fffffffu) : ~key), vmax, inv_t);
     pcut = cut_with_ties(row, s, key, target - above, equal, unit, massed);
@@ -322,11 +414,11 @@ sample_rows_kernel(int* __restrict__ out, const float* __restrict__ logits, int 
   const unsigned long long sd = seed[b], ctr = counter[b];
   float best_score = -1.f;
   int best_token = 0x7fffffff;
-  for (int i = threadIdx.x; i < row.n; i += blockDim.x) {
-    const float v = row.value(i);
+  for_each_value(row, [&](int i, float v, bool valid) {
+    if (!valid) return;
     const uint32_t key = order_key(v);
     const int token = row.token(i);
-    if (!kcut.keeps(key, token) || !pcut.keeps(key, token)) continue;
+    if (!kcut.keeps(key, token) || !pcut.keeps(key, token)) return;
     const float w = expf((v - vmax) * inv_t);
     const uint32_t bits = Philox::draw(sd, ctr, (uint32_t)token);
     const float u = ((float)(bits >> 8) + 0.5f) * (1.f / 16777216.f);  // (0, 1)
@@ -336,7 +428,7 @@ sample_rows_kernel(int* __restrict__ out, const float* __restrict__ logits, int 
       best_score = score;
       best_token = token;
     }
-  }
+  });
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) {
     const float os = __shfl_xor_sync(0xffffffffu, best_score, o);
