@@ -168,17 +168,45 @@ __device__ uint32_t radix_select(const RowView& row, Scratch& s, unsigned long l
     __syncthreads();  // copy 0's 32-bit words lie where the 64-bit totals are written next
     if (threadIdx.x < kBins) s.hist[0][threadIdx.x] = bin_total;
     __syncthreads();
-    if (threadIdx.x == 0) {
-      int digit = -1;
-      unsigned long long a = acc;
-      for (int b = kBins - 1; b >= 0; --b) {
-        const unsigned long long hb = s.hist[0][b];
-        if (a + hb >= target) { digit = b; break; }
-        a += hb;
+    if (threadIdx.x < 32) {
+      // The first bin, from the top, at which the weight so far reaches the target: lane l walks
+      // bins 255 - 8l downwards, after a scan over the lanes has told it the weight above them.
+      unsigned long long mine[8], lane_sum = 0;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        mine[j] = s.hist[0][kBins - 1 - (8 * lane + j)];
+        lane_sum += mine[j];
       }
-      s.bcast[0] = a;
-      s.bcast[1] = (unsigned long long)(long long)digit;
-      s.bcast[3] = digit >= 0 ? s.hist[0][digit] : 0ull;
+      unsigned long long upto = lane_sum;  // inclusive scan over the lanes
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const unsigned long long t = __shfl_up_sync(0xffffffffu, upto, o);
+        if (lane >= o) upto += t;
+      }
+      unsigned long long a = acc + upto - lane_sum;
+      int found = -1;
+#pragma unroll
+      for (int j = 0; j < 8; ++j)
+        if (found < 0) {
+          if (a + mine[j] >= target) found = j;
+          else a += mine[j];
+        }
+      const unsigned hit = __ballot_sync(0xffffffffu, found >= 0);
+      if (hit == 0u) {
+        if (lane == 31) {  // the whole set weighs less than the target
+          s.bcast[0] = acc + upto;
+          s.bcast[1] = (unsigned long long)(long long)-1;
+          s.bcast[3] = 0ull;
+        }
+      } else if (lane == __ffs(hit) - 1) {
+        unsigned long long in_bin = 0;
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+          if (j == found) in_bin = mine[j];
+        s.bcast[0] = a;
+        s.bcast[1] = (unsigned long long)(long long)(kBins - 1 - (8 * lane + found));
+        s.bcast[3] = in_bin;
+      }
     }
     __syncthreads();
     acc = s.bcast[0];
@@ -330,8 +358,18 @@ sample_rows_kernel(int* __restrict__ out, const float* __restrict__ logits, int 
       // The two high digits of the k-th largest key: if everything from that bin of 65,536 keys
       // upwards fits the candidate buffer (it holds at least k), gather it now and finish the
       // selection, like all later passes, on the candidates in shared memory.
-      const uint32_t high = radix_select<true>(row, s, (unsigned long long)k, &above, &equal, unit, 16);
-      if (above + equal <= (unsigned long long)kCompact) {
+      // Only keys within four first-digit bins of the largest (a factor of 16 or so below the best
+      // logit when it is positive) are counted here, which spares the atomics of nearly the whole
+      // row; if fewer than k lie there, `high` comes back 0 and the full selection below runs.
+      const uint32_t top_bin = order_key(vmax) >> 24;
+      const uint32_t floor_key = top_bin >= 3u ? (top_bin - 3u) << 24 : 0u;
+      auto unit_near_top = [&](int i, float v, uint32_t& key, unsigned long long& w) {
+        key = order_key(v);
+        w = 1ull;
+        return key >= floor_key;
+      };
+      const uint32_t high = radix_select<true>(row, s, (unsigned long long)k, &above, &equal, unit_near_top, 16);
+      if (high != 0u && above + equal <= (unsigned long long)kCompact) {
         early = true;
         if (threadIdx.x == 0) s.cand_n = 0;
         __syncthreads();
