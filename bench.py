@@ -369,6 +369,46 @@ def attention_partition_sweep(batches: list[int], contexts: list[int]) -> None:
             del k, v
 
 
+def time_sampling(batches: list[int], vocab: int) -> None:
+    """Device time of the sampling kernels on float32 logits [B, vocab] (normal, standard deviation
+    3), from a CUDA-graph loop of 20 calls: greedy, the reference's default settings, top-p alone."""
+    import torch
+
+    from atomserve_b200 import ops
+
+    for B in batches:
+        logits = torch.randn(B, vocab, device="cuda") * 3
+        temperature = torch.full((B,), 0.6, device="cuda")
+        top_k = torch.full((B,), 20, dtype=torch.int32, device="cuda")
+        no_top_k = torch.zeros(B, dtype=torch.int32, device="cuda")
+        top_p = torch.full((B,), 0.95, device="cuda")
+        seed = torch.arange(B, dtype=torch.int64, device="cuda")
+        counter = torch.zeros(B, dtype=torch.int64, device="cuda")
+        cases = {
+            "argmax_us": lambda: ops.argmax_rows(logits),
+            "top_k20_top_p_us": lambda: ops.sample_rows(logits, temperature, top_k, top_p, seed, counter),
+            "top_p_only_us": lambda: ops.sample_rows(logits, temperature, no_top_k, top_p, seed, counter),
+        }
+        line = {"sampling": "rows", "batch": B, "vocab": vocab}
+        for name, fn in cases.items():
+            for _ in range(3):
+                fn()
+            torch.cuda.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                for _ in range(20):
+                    fn()
+            graph.replay()
+            torch.cuda.synchronize()
+            start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            start.record()
+            graph.replay()
+            end.record()
+            torch.cuda.synchronize()
+            line[name] = round(start.elapsed_time(end) * 1000 / 20, 1)
+        print(json.dumps(line))
+
+
 def gemm_timelines(which: str, tokens: list[int]) -> None:
     """Where a decode-size GEMM call's time goes: %globaltimer stamps that every block of the
     kernel writes (ops.linear.gemm_timeline), read after a CUDA-graph loop of calls on rotating
@@ -428,7 +468,7 @@ def main() -> int:
                         help="fewer layers than the model has (same layer sizes), where time or memory needs it")  # fmt: skip
     parser.add_argument("--batch", type=int, default=8)
     parser.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    parser.add_argument("--only", choices=["decode", "prefill", "gemm", "serve", "attention"], help="time just this (for profiling small cases and the other shapes)")
+    parser.add_argument("--only", choices=["decode", "prefill", "gemm", "serve", "attention", "sampling"], help="time just this (for profiling small cases and the other shapes)")
     parser.add_argument("--shape", default="8b", choices=sorted(SHAPES), help="with --only decode/prefill/serve: layer sizes of Qwen3-8B, -14B or -32B")
     parser.add_argument("--context", type=int, default=PROMPT_TOKENS, help="with --only decode: tokens each request holds when decoding starts")
     parser.add_argument("--requests", type=int, default=32, help="with --only serve: requests submitted at once")
@@ -457,6 +497,9 @@ def main() -> int:
     pk = peaks()
     if args.only == "attention":
         attention_partition_sweep([4, 8, 16, 32, 64, 128], [2048, 8192])
+        return 0
+    if args.only == "sampling":
+        time_sampling([1, 8, 64], SHAPES[args.shape]["vocab_size"])
         return 0
     if args.only == "gemm" and args.timeline:
         gemm_timelines(args.gemm_shape, [int(t) for t in args.gemm_tokens.split(",")])
