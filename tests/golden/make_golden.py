@@ -94,7 +94,9 @@ def prompts_for(cfg: dict, seed: int) -> tuple[list[int], list[int]]:
 
 
 def main() -> None:
-    ref = pathlib.Path(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    if len(sys.argv) != 2:
+        sys.exit("usage: make_golden.py <folder of the aneesh-sathe/atomserve checkout>")
+    ref = pathlib.Path(sys.argv[1])
     install_hook(ref)
     from atomserve.config import ModelConfig
     from atomserve.kv_cache import KVPool
