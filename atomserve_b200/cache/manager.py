@@ -154,9 +154,12 @@ class CacheManager:
         if self._windowed:
             self.release_passed(rc, start)
         needed = blocks_for_tokens(start + num_new, self.block_size)
-        missing = [max(0, needed - len(t)) for t in rc.block_tables]
-        if not any(missing):
+        for t in rc.block_tables:
+            if len(t) < needed:
+                break
+        else:
             return True  # the usual decode step: the last page still has room
+        missing = [max(0, needed - len(t)) for t in rc.block_tables]
         if any(m > g.allocator.num_free for g, m in zip(self.groups, missing)):
             return False
         for g, table, m in zip(self.groups, rc.block_tables, missing):

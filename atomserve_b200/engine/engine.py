@@ -159,11 +159,11 @@ class Engine:
         """Run one scheduled step and sample: a sequence that reaches the end of its known
         tokens gets one new token (atomserve/runner.py:194-212)."""
         logits = self.runner.step(rows_for(out.seqs, out.num_new_tokens))
-        sampling = [s for s, n in zip(out.seqs, out.num_new_tokens) if s.reaches_end(n)]
-        sampled = iter(self.sampler.sample(logits, sampling))
+        ends = [s.num_computed_tokens + n == len(s.token_ids) for s, n in zip(out.seqs, out.num_new_tokens)]  # reaches_end
+        sampled = iter(self.sampler.sample(logits, [s for s, end in zip(out.seqs, ends) if end]))
         return [
-            StepResult([next(sampled)] if seq.reaches_end(n) else [], seq.num_computed_tokens + n)
-            for seq, n in zip(out.seqs, out.num_new_tokens)
+            StepResult([next(sampled)] if end else [], seq.num_computed_tokens + n)
+            for seq, n, end in zip(out.seqs, out.num_new_tokens, ends)
         ]
 
     def step(self) -> bool:

@@ -350,8 +350,9 @@ def rows_for(seqs, num_new_tokens: list[int]) -> list[Row]:
     (atomserve/runner.py:59-68)."""
     rows = []
     for seq, n in zip(seqs, num_new_tokens, strict=True):
-        start = seq.num_computed_tokens
-        if n < 1 or start + n > seq.num_tokens:
-            raise ValueError(f"cannot run tokens {start}:{start + n} of {seq.num_tokens}")
-        rows.append(Row(seq.token_ids[start : start + n], start, seq.cache, [n - 1] if seq.reaches_end(n) else []))
+        start, tokens = seq.num_computed_tokens, seq.token_ids
+        known = len(tokens)
+        if n < 1 or start + n > known:
+            raise ValueError(f"cannot run tokens {start}:{start + n} of {known}")
+        rows.append(Row(tokens[start : start + n], start, seq.cache, [n - 1] if start + n == known else []))
     return rows

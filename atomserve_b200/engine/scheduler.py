@@ -65,7 +65,9 @@ class Scheduler:
         for seq in list(self.running):  # a copy: preemption shrinks the list
             if seq.status is not SequenceStatus.RUNNING:
                 continue  # preempted earlier in this loop
-            n = min(seq.num_tokens - seq.num_computed_tokens, budget)
+            n = len(seq.token_ids) - seq.num_computed_tokens
+            if n > budget:
+                n = budget
             if n == 0:
                 continue  # budget spent; it waits for the next step
             while not self.cache.reserve(seq.cache, seq.num_computed_tokens, n):
@@ -116,7 +118,7 @@ class Scheduler:
             if seq.status is SequenceStatus.FINISHED:
                 continue
             # the newest token's keys and values come with the next step
-            seq.num_computed_tokens = min(result.num_computed, seq.num_tokens - 1)
+            seq.num_computed_tokens = min(result.num_computed, len(seq.token_ids) - 1)
             if self.prefix_caching:
                 self.cache.register_full_blocks(seq.cache, seq.token_ids, seq.num_computed_tokens)
         return new_tokens
@@ -131,11 +133,10 @@ class Scheduler:
         return None
 
     def _finish_reason(self, seq: Sequence, token: int) -> str | None:
-        if token in self.eos_token_ids and not seq.params.ignore_eos:
+        params, known = seq.params, len(seq.token_ids)
+        if token in self.eos_token_ids and not params.ignore_eos:
             return "stop"
-        if seq.num_tokens - seq.num_prompt_tokens >= seq.params.max_tokens:
-            return "length"
-        if seq.num_tokens >= self.config.max_model_len:
+        if known - seq.num_prompt_tokens >= params.max_tokens or known >= self.config.max_model_len:
             return "length"
         return None
 
