@@ -28,6 +28,8 @@ class Sampler:
     def __init__(self, device: torch.device | str, base_seed: int | None = None):
         self.device = torch.device(device)
         self.base_seed = base_seed if base_seed is not None else int.from_bytes(os.urandom(8), "little")
+        self._host: torch.Tensor | None = None  # the per-row settings of a step, packed for one upload
+        self._dev: torch.Tensor | None = None
 
     def seed_of(self, seq: Sequence) -> int:
         if seq.params.seed is not None:
@@ -46,13 +48,23 @@ class Sampler:
         if all(s.params.temperature == 0 for s in seqs):
             return ops.argmax_rows(logits).tolist()
         n = len(seqs)
-        floats = torch.tensor(
-            [[s.params.temperature for s in seqs], [s.params.top_p for s in seqs]], dtype=torch.float32
-        )
-        top_k = torch.tensor([s.params.top_k for s in seqs], dtype=torch.int32)
-        keys = torch.tensor([[self.seed_of(s) for s in seqs], [s.num_tokens - s.num_prompt_tokens for s in seqs]], dtype=torch.int64)
-        floats, top_k, keys = (t.to(self.device, non_blocking=True) for t in (floats, top_k, keys))
-        out = ops.sample_rows(logits, floats[0], top_k, floats[1], keys[0], keys[1])
+        # One upload from pinned memory: four rows of n 64-bit words, seeds, draw counters, then
+        # temperatures and top-p as the float32 halves of the third row, top-k as int32 in the fourth.
+        # (The previous step's upload has left the host buffer: that step ended with a read of its result.)
+        if self._host is None or self._host.shape[0] < 4 * n:
+            cap = max(4 * n, 1024)
+            self._host = torch.empty(cap, dtype=torch.int64, pin_memory=self.device.type == "cuda")
+            self._dev = torch.empty(cap, dtype=torch.int64, device=self.device)
+        host, dev = self._host[: 4 * n].view(4, n), self._dev[: 4 * n].view(4, n)
+        host[0] = torch.tensor([self.seed_of(s) for s in seqs], dtype=torch.int64)
+        host[1] = torch.tensor([len(s.token_ids) - s.num_prompt_tokens for s in seqs], dtype=torch.int64)
+        floats = host[2].view(torch.float32)
+        floats[:n] = torch.tensor([s.params.temperature for s in seqs], dtype=torch.float32)
+        floats[n:] = torch.tensor([s.params.top_p for s in seqs], dtype=torch.float32)
+        host[3].view(torch.int32)[:n] = torch.tensor([s.params.top_k for s in seqs], dtype=torch.int32)
+        dev.copy_(host, non_blocking=True)
+        dev_floats = dev[2].view(torch.float32)
+        out = ops.sample_rows(logits, dev_floats[:n], dev[3].view(torch.int32)[:n], dev_floats[n:], dev[0], dev[1])
         assert out.shape[0] == n
         return out.tolist()
 
