@@ -238,37 +238,3 @@ def test_prefix_caching_is_off_for_windowed_or_stateful_models():
         cache = CacheManager(reqs, 4, 16, 4)
         s = Scheduler(EngineConfig(block_size=4, num_blocks=16, max_model_len=64, max_num_seqs=4), cache)
         assert not s.prefix_caching
-
-
-def test_decode_attention_partition_plans_cover_every_context(monkeypatch):
-    """The planner of the decode attention's key partitions is host arithmetic: whatever the
-    batch, context and window, its partitions are whole 64-key tiles, start at multiples of their
-    size and reach the last key."""
-    import random
-
-    import atomserve_b200.ops.attention as attention
-
-    class FakeLibrary:
-        def asb_decode_attention_resident_blocks(self, head_dim):
-            return 444
-
-    monkeypatch.setattr(attention, "lib", lambda: FakeLibrary())
-    attention.plan_decode_partitions.cache_clear()
-    rng = random.Random(0)
-    for _ in range(2000):
-        rows = rng.choice([1, 2, 3, 8, 17, 64, 200])
-        kv, group = rng.choice([(1, 1), (2, 4), (8, 4), (4, 20)])
-        context = rng.choice([1, 63, 64, 65, 300, 2048, 2088, 8191, 40000])
-        window = rng.choice([0, 0, 100, 4096])
-        size, parts = attention.plan_decode_partitions(rows, kv, group, context, window)
-        assert parts >= 1
-        if parts == 1:
-            assert size >= context
-            continue
-        assert size % 64 == 0 and size >= 64
-        if window <= 0:
-            assert (parts - 1) * size < context <= parts * size
-        else:
-            # a row's window of keys spans at most this many partitions of that size
-            assert parts <= -(-min(context, window) // size) + 1
-    attention.plan_decode_partitions.cache_clear()
