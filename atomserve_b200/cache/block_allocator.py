@@ -1,87 +1,141 @@
-"""Which pages of one cache pool are free, which are in use, and which hold a reusable prefix.
+"""The page ledger of one cache pool: which pages requests hold, which are idle, and which idle
+or held pages still carry a prefix that a later request may pick up.
 
-Bookkeeping over page ids only (no tensors), so policy is testable without a device. A page is
-in use (reference count > 0), free and still holding a hashed prefix (found again by lookup
-until the memory is needed), or free and empty. Free pages are handed out oldest first, which
-evicts the least recently freed prefix first. Full pages are named by a chained hash of their
-tokens and everything before them, so equal hashes mean equal keys and values. The rules are
-the reference's (atomserve/block_allocator.py:33-129).
+No tensors, so the policy is testable without a device. Every page is in one of three
+conditions: held (one or more requests count on it), idle but remembered (its contents are
+still named by a content key and `lookup` finds it until the memory is needed), or idle and
+blank. Idle pages wait in a queue threaded through two index arrays (`_toward_old`,
+`_toward_new`): a page joins at the young end when its last holder lets go and leaves from the
+old end when pages are handed out, so the prefix that has been idle longest is the first one
+overwritten; a remembered page that is picked up again is unhooked from the middle in O(1).
+
+A full page is named by sha256 over the name of the page before it and its own token ids, so
+equal names mean equal tokens all the way back to position 0 and therefore equal keys and
+values. The rules (oldest idle first, all-or-nothing hand-out, last page let go first, the
+first copy of a prefix wins) are the reference's (atomserve/block_allocator.py:33-129).
 """
 
 from __future__ import annotations
 
 import hashlib
 from array import array
-from collections import OrderedDict
+
+_NONE = -1  # end of the idle queue / not queued
 
 
 def blocks_for_tokens(num_tokens: int, block_size: int) -> int:
-    return -(-num_tokens // block_size)
+    """Pages needed to hold `num_tokens` positions."""
+    return (num_tokens + block_size - 1) // block_size
 
 
 def block_hash(parent: bytes, tokens: list[int]) -> bytes:
-    """sha256(parent hash || tokens as uint32): commits to the page and all before it."""
-    return hashlib.sha256(parent + array("I", tokens).tobytes()).digest()
+    """Content key of a full page: the key of the page before it, then its tokens as uint32."""
+    digest = hashlib.sha256(parent)
+    digest.update(array("I", tokens).tobytes())
+    return digest.digest()
 
 
 class OutOfBlocksError(RuntimeError):
-    """More pages were asked for than are free; none was taken."""
+    """A hand-out asked for more pages than are idle; nothing was taken."""
 
 
 class BlockAllocator:
     def __init__(self, num_blocks: int):
         self.num_blocks = num_blocks
-        self._refcount = [0] * num_blocks
-        self._free: OrderedDict[int, None] = OrderedDict.fromkeys(range(num_blocks))
-        self._hash_of: dict[int, bytes] = {}
-        self._block_of: dict[bytes, int] = {}
+        self._holders = array("i", bytes(4 * num_blocks))  # how many requests count on each page
+        # the idle queue, oldest first: page p's neighbours are _toward_old[p] and _toward_new[p]
+        self._toward_old = array("i", range(-1, num_blocks - 1))
+        self._toward_new = array("i", range(1, num_blocks + 1))
+        if num_blocks:
+            self._toward_new[num_blocks - 1] = _NONE
+        self._oldest = 0 if num_blocks else _NONE
+        self._youngest = num_blocks - 1
+        self._idle = num_blocks
+        self._key_of_page: list[bytes | None] = [None] * num_blocks
+        self._page_of_key: dict[bytes, int] = {}
+
+    # ---- counts --------------------------------------------------------------------------------
 
     @property
     def num_free(self) -> int:
-        return len(self._free)
+        return self._idle
 
     @property
     def num_cached(self) -> int:
-        return len(self._block_of)
+        return len(self._page_of_key)
 
     def refcount(self, block: int) -> int:
-        return self._refcount[block]
+        return self._holders[block]
+
+    # ---- the idle queue ------------------------------------------------------------------------
+
+    def _unhook(self, page: int) -> None:
+        older, younger = self._toward_old[page], self._toward_new[page]
+        if older == _NONE:
+            self._oldest = younger
+        else:
+            self._toward_new[older] = younger
+        if younger == _NONE:
+            self._youngest = older
+        else:
+            self._toward_old[younger] = older
+        self._idle -= 1
+
+    def _hook_youngest(self, page: int) -> None:
+        self._toward_old[page], self._toward_new[page] = self._youngest, _NONE
+        if self._youngest == _NONE:
+            self._oldest = page
+        else:
+            self._toward_new[self._youngest] = page
+        self._youngest = page
+        self._idle += 1
+
+    # ---- handing out and taking back -----------------------------------------------------------
 
     def allocate(self, n: int) -> list[int]:
-        """Take n free pages, oldest first; all or none."""
-        if n > len(self._free):
-            raise OutOfBlocksError(f"need {n} cache pages, only {len(self._free)} free")
-        taken = []
+        """The n pages that have been idle longest, each now held once; all of them or an error."""
+        if n > self._idle:
+            raise OutOfBlocksError(f"need {n} cache pages, only {self._idle} free")
+        pages = []
+        page = self._oldest
         for _ in range(n):
-            block, _ = self._free.popitem(last=False)
-            old = self._hash_of.pop(block, None)
-            if old is not None:  # about to be overwritten: its prefix must no longer be found
-                del self._block_of[old]
-            self._refcount[block] = 1
-            taken.append(block)
-        return taken
+            pages.append(page)
+            page = self._toward_new[page]
+        for page in pages:
+            self._unhook(page)
+            stale = self._key_of_page[page]
+            if stale is not None:  # the page is about to be overwritten: forget what it held
+                self._key_of_page[page] = None
+                del self._page_of_key[stale]
+            self._holders[page] = 1
+        return pages
 
     def free(self, blocks: list[int]) -> None:
-        """Drop one reference to each page, last page first, so that a prefix's later pages
-        are evicted before its earlier, more widely shared ones."""
-        for block in reversed(blocks):
-            if not 0 <= block < self.num_blocks or self._refcount[block] == 0:
-                raise ValueError(f"page {block} is not allocated")
-            self._refcount[block] -= 1
-            if self._refcount[block] == 0:
-                self._free[block] = None
+        """One holder fewer on each page. Pages are let go from the back of the list, so the tail
+        of a prefix becomes older in the idle queue than its head and is overwritten first (the
+        head is what most requests share)."""
+        for page in blocks[::-1]:
+            if not 0 <= page < self.num_blocks or self._holders[page] == 0:
+                raise ValueError(f"page {page} is not allocated")
+            self._holders[page] -= 1
+            if self._holders[page] == 0:
+                self._hook_youngest(page)
+
+    # ---- prefixes ------------------------------------------------------------------------------
 
     def lookup(self, h: bytes) -> int | None:
-        return self._block_of.get(h)
+        """The page remembered under content key `h`, held or idle, if any."""
+        return self._page_of_key.get(h)
 
     def acquire(self, block: int) -> None:
-        """Add a reference to a page found by lookup, reviving it if it was free."""
-        if self._refcount[block] == 0:
-            del self._free[block]
-        self._refcount[block] += 1
+        """Count one more holder on a page that `lookup` returned (an idle one leaves the queue)."""
+        if self._holders[block] == 0:
+            self._unhook(block)
+        self._holders[block] += 1
 
     def register(self, block: int, h: bytes) -> None:
-        """Record that `block` (full, computed) holds the prefix `h`; the first copy wins."""
-        if h not in self._block_of and block not in self._hash_of:
-            self._block_of[h] = block
-            self._hash_of[block] = h
+        """Remember that `block` (full and computed) holds the prefix named `h`. A prefix that is
+        already remembered elsewhere keeps its first page, and a page keeps its first name."""
+        if self._key_of_page[block] is None and h not in self._page_of_key:
+            self._key_of_page[block] = h
+            self._page_of_key[h] = block

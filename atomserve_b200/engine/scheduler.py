@@ -1,21 +1,27 @@
-"""The scheduler: every step, which sequences run and how many tokens each.
+"""The scheduler: who runs in the next step, and how many tokens each.
 
-Continuous batching under two limits, `max_num_seqs` running sequences and
-`max_num_batched_tokens` tokens per step (atomserve/scheduler.py:1-35, 88-135):
+Two limits bound a step: `max_num_seqs` sequences may hold cache at once, and
+`max_num_batched_tokens` tokens may run at once. Within them a step is filled in two passes
+(the policy is the reference's, atomserve/scheduler.py:1-35, 88-135):
 
- 1. Running sequences first, oldest first: one token for a decode, or the next portion of a
-    prompt, as much as the budget leaves. When the cache has no pages for one, the most
-    recently admitted sequence is preempted: everything it holds is given back and it returns
-    to the front of the queue, to be recomputed from its tokens. If the sequence in need is
-    itself the newest, it is the one preempted. Nothing is admitted in a step that preempted.
- 2. Waiting sequences are admitted first come, first served, while budget, sequence limit,
-    state slots and pages allow; the head of the queue is never skipped.
+  the resident pass   Every sequence that already holds cache gets its turn in the order it was
+                      let in: a decoding one asks for one token, one still inside its prompt for
+                      as much of the rest as the budget has left (so a long prompt is cut into
+                      portions by whatever the decodes before it left over). If the cache cannot
+                      give a sequence the pages it asks for, sequences are evicted from the young
+                      end of the resident list until it can: an evicted sequence gives back all
+                      it holds, goes to the front of the line and is computed again from its
+                      tokens when it is let in next. The asker may end up evicting itself.
+  the door pass       Skipped in a step that evicted anybody. Otherwise the line is served
+                      strictly from its head while budget, the sequence limit, a state slot and
+                      pages are there; the first sequence that does not fit stops the pass
+                      (nobody overtakes it). With prefix caching a newcomer first takes over the
+                      pages that hold its leading full blocks from some earlier request.
 
-A prompt takes what budget is left and continues next step (chunked prefill). With prefix
-caching, a sequence starts with the pages of its leading full blocks that some earlier request
-already computed, and publishes its own full blocks after every step.
+After the step, `update` appends what was sampled, retires what is done and, with prefix
+caching, publishes the pages that became full.
 
-Pure bookkeeping on sequences and the cache manager: no tensors.
+Bookkeeping only: sequences and the cache manager, no tensors.
 """
 
 from __future__ import annotations
@@ -30,8 +36,8 @@ from atomserve_b200.engine.sequence import Sequence, SequenceStatus, StepResult
 
 @dataclass
 class SchedulerOutput:
-    """The plan for one step: seqs[i] runs its next num_new_tokens[i] tokens; `preempted`
-    were evicted to make room and wait again."""
+    """One step's plan: seqs[i] runs its next num_new_tokens[i] tokens. `preempted` lost their
+    cache to make room and stand in line again."""
 
     seqs: list[Sequence] = field(default_factory=list)
     num_new_tokens: list[int] = field(default_factory=list)
@@ -41,116 +47,144 @@ class SchedulerOutput:
     def num_tokens(self) -> int:
         return sum(self.num_new_tokens)
 
+    def grant(self, seq: Sequence, n: int) -> None:
+        self.seqs.append(seq)
+        self.num_new_tokens.append(n)
+
 
 class Scheduler:
     def __init__(self, config: EngineConfig, cache: CacheManager, eos_token_ids: frozenset[int] = frozenset()):
-        self.config, self.cache, self.eos_token_ids = config, cache, frozenset(eos_token_ids)
+        self.config, self.cache = config, cache
+        self.eos_token_ids = frozenset(eos_token_ids)
         self.prefix_caching = config.enable_prefix_caching and cache.supports_prefix_caching
-        self.waiting: deque[Sequence] = deque()
-        self.running: list[Sequence] = []  # in admission order
+        self.waiting: deque[Sequence] = deque()  # the line, head first
+        self.running: list[Sequence] = []  # residents, in the order they were let in
+        self._known: dict[int, Sequence] = {}  # by request id, while waiting or resident
+
+    # ---- arrivals and departures ---------------------------------------------------------------
 
     def add(self, seq: Sequence) -> None:
         if seq.cache is None:
             seq.cache = self.cache.new_request()
+        self._known[seq.id] = seq
         self.waiting.append(seq)
 
     @property
     def has_work(self) -> bool:
-        return bool(self.waiting or self.running)
+        return bool(self._known)
+
+    def abort(self, seq_id: int) -> Sequence | None:
+        """Retire a sequence wherever it stands; None if it is not (or no longer) here."""
+        seq = self._known.get(seq_id)
+        if seq is None:
+            return None
+        if seq.status is SequenceStatus.WAITING:
+            self.waiting.remove(seq)
+        self._retire(seq, "abort")
+        return seq
+
+    def _retire(self, seq: Sequence, reason: str) -> None:
+        if seq.status is SequenceStatus.RUNNING:
+            self.running.remove(seq)
+        self._known.pop(seq.id, None)
+        if seq.cache is not None:
+            self.cache.free(seq.cache)
+        seq.status, seq.finish_reason = SequenceStatus.FINISHED, reason
+
+    def _evict_youngest(self) -> Sequence:
+        """The resident let in last has the least to compute again: it gives everything back and
+        goes to the head of the line."""
+        victim = self.running.pop()
+        self.cache.free(victim.cache)
+        victim.num_computed_tokens = 0
+        victim.status = SequenceStatus.WAITING
+        self.waiting.appendleft(victim)
+        return victim
+
+    # ---- planning a step -----------------------------------------------------------------------
 
     def schedule(self) -> SchedulerOutput:
-        budget = self.config.max_num_batched_tokens
-        out = SchedulerOutput()
+        plan = SchedulerOutput()
+        left = self._resident_pass(plan, self.config.max_num_batched_tokens)
+        if not plan.preempted:
+            self._door_pass(plan, left)
+        return plan
 
-        for seq in list(self.running):  # a copy: preemption shrinks the list
-            if seq.status is not SequenceStatus.RUNNING:
-                continue  # preempted earlier in this loop
-            n = len(seq.token_ids) - seq.num_computed_tokens
-            if n > budget:
-                n = budget
-            if n == 0:
-                continue  # budget spent; it waits for the next step
-            while not self.cache.reserve(seq.cache, seq.num_computed_tokens, n):
-                victim = self.running[-1]  # newest: it has the least to redo
-                self._preempt(victim)
-                out.preempted.append(victim)
+    def _resident_pass(self, plan: SchedulerOutput, budget: int) -> int:
+        residents, reserve = self.running, self.cache.reserve
+        # Evictions only ever shorten the list behind the sequence whose turn it is (or remove that
+        # sequence itself, which is then the last), so walking by index meets each survivor once.
+        turn = 0
+        while turn < len(residents):
+            seq = residents[turn]
+            turn += 1
+            ask = min(len(seq.token_ids) - seq.num_computed_tokens, budget)
+            if ask <= 0:
+                continue  # the budget is spent: it keeps what it holds and waits a step
+            while not reserve(seq.cache, seq.num_computed_tokens, ask):
+                victim = self._evict_youngest()
+                plan.preempted.append(victim)
                 if victim is seq:
                     break
-            if seq.status is SequenceStatus.RUNNING:
-                out.seqs.append(seq)
-                out.num_new_tokens.append(n)
-                budget -= n
+            else:
+                plan.grant(seq, ask)
+                budget -= ask
+        return budget
 
-        while self.waiting and not out.preempted and len(self.running) < self.config.max_num_seqs:
-            seq = self.waiting[0]
+    def _door_pass(self, plan: SchedulerOutput, budget: int) -> None:
+        line, cache = self.waiting, self.cache
+        while line and len(self.running) < self.config.max_num_seqs:
+            seq = line[0]
+            have = 0
             if self.prefix_caching:
-                seq.num_computed_tokens = self.cache.use_cached_prefix(seq.cache, seq.token_ids)
-                if not seq.output_ids:  # count hits on the prompt, not on redoing a preempted reply
-                    seq.num_cached_tokens = seq.num_computed_tokens
-            n = min(seq.num_tokens - seq.num_computed_tokens, budget)
-            if n == 0 or not self.cache.admit(seq.cache) or not self.cache.reserve(seq.cache, seq.num_computed_tokens, n):
-                self.cache.free(seq.cache)  # undo a prefix hit and the slot; retry next step
+                have = cache.use_cached_prefix(seq.cache, seq.token_ids)
+                # a hit counts for the prompt only, not for recomputing an evicted reply
+                seq.num_cached_tokens = have if len(seq.token_ids) == seq.num_prompt_tokens else seq.num_cached_tokens
+            ask = min(len(seq.token_ids) - have, budget)
+            if ask <= 0 or not cache.admit(seq.cache) or not cache.reserve(seq.cache, have, ask):
+                cache.free(seq.cache)  # gives back prefix pages and the slot, if it got that far
                 seq.num_computed_tokens = seq.num_cached_tokens = 0
-                break
-            self.waiting.popleft()
+                return  # it stays at the head; nobody behind it is tried
+            line.popleft()
+            seq.num_computed_tokens = have
             seq.status = SequenceStatus.RUNNING
             self.running.append(seq)
-            out.seqs.append(seq)
-            out.num_new_tokens.append(n)
-            budget -= n
-        return out
+            plan.grant(seq, ask)
+            budget -= ask
+
+    # ---- after a step --------------------------------------------------------------------------
 
     def update(self, out: SchedulerOutput, results: list[StepResult]) -> list[tuple[Sequence, list[int]]]:
-        """Apply a finished step; returns (sequence, its new tokens) for every sequence that
-        got any. A finished sequence has only the tokens up to its stop."""
-        new_tokens = []
+        """Book a finished step. Returns (sequence, tokens it gained) for each sequence that gained
+        any; a sequence that stops keeps nothing after its stopping token."""
+        gained: list[tuple[Sequence, list[int]]] = []
+        limit = self.config.max_model_len
         for seq, result in zip(out.seqs, results, strict=True):
-            appended = []
+            taken = 0
+            reason = None
             for token in result.tokens:
                 seq.token_ids.append(token)
-                appended.append(token)
-                reason = self._finish_reason(seq, token)
-                if reason:
-                    self._finish(seq, reason)
+                taken += 1
+                reason = self._why_stop(seq, token, limit)
+                if reason is not None:
                     break
-            if appended:
-                new_tokens.append((seq, appended))
-            if seq.status is SequenceStatus.FINISHED:
+            if taken:
+                gained.append((seq, result.tokens[:taken]))
+            if reason is not None:
+                self._retire(seq, reason)
                 continue
-            # the newest token's keys and values come with the next step
+            # the newest token has no keys and values yet: they come with the step that feeds it
             seq.num_computed_tokens = min(result.num_computed, len(seq.token_ids) - 1)
             if self.prefix_caching:
                 self.cache.register_full_blocks(seq.cache, seq.token_ids, seq.num_computed_tokens)
-        return new_tokens
+        return gained
 
-    def abort(self, seq_id: int) -> Sequence | None:
-        for seq in [*self.waiting, *self.running]:
-            if seq.id == seq_id:
-                if seq in self.waiting:
-                    self.waiting.remove(seq)
-                self._finish(seq, "abort")
-                return seq
-        return None
-
-    def _finish_reason(self, seq: Sequence, token: int) -> str | None:
-        params, known = seq.params, len(seq.token_ids)
-        if token in self.eos_token_ids and not params.ignore_eos:
+    def _why_stop(self, seq: Sequence, token: int, limit: int) -> str | None:
+        """"stop" on an end-of-sequence token (unless ignored), "length" when the reply or the
+        whole sequence is as long as allowed (atomserve/scheduler.py:167-176)."""
+        if token in self.eos_token_ids and not seq.params.ignore_eos:
             return "stop"
-        if known - seq.num_prompt_tokens >= params.max_tokens or known >= self.config.max_model_len:
+        total = len(seq.token_ids)
+        if total - seq.num_prompt_tokens >= seq.params.max_tokens or total >= limit:
             return "length"
         return None
-
-    def _preempt(self, seq: Sequence) -> None:
-        self.running.remove(seq)
-        self.cache.free(seq.cache)
-        seq.num_computed_tokens = 0
-        seq.status = SequenceStatus.WAITING
-        self.waiting.appendleft(seq)
-
-    def _finish(self, seq: Sequence, reason: str) -> None:
-        if seq in self.running:
-            self.running.remove(seq)
-        if seq.cache is not None:
-            self.cache.free(seq.cache)
-        seq.status = SequenceStatus.FINISHED
-        seq.finish_reason = reason

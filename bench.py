@@ -13,10 +13,12 @@ needed between timed iterations.
 from __future__ import annotations
 
 import argparse
+import dataclasses
 import json
 import pathlib
 import subprocess
 import sys
+import tempfile
 import time
 
 ROOT = pathlib.Path(__file__).resolve().parent
@@ -53,12 +55,17 @@ def prompts(batch: int, length: int) -> list[list[int]]:
 
 
 class ClockSampler:
+    """nvidia-smi's clocks and throttle reasons, sampled every 100 ms while the block runs."""
+
+    _folder = None
+
     def __init__(self, name: str = "bench_clocks.csv"):
-        self.proc, self.path = None, ROOT / "gpurun_out" / name
+        if ClockSampler._folder is None:
+            ClockSampler._folder = tempfile.TemporaryDirectory(prefix="atomserve_b200_bench_")
+        self.proc, self.path = None, pathlib.Path(ClockSampler._folder.name) / name
 
     def __enter__(self):
         try:
-            self.path.parent.mkdir(exist_ok=True)
             self.file = open(self.path, "w")
             self.proc = subprocess.Popen(
                 ["nvidia-smi", "--query-gpu=clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
@@ -177,10 +184,21 @@ def time_decode(engine, batch: int, steps: int, warmup: int, prompt_tokens: int 
     for rc in reqs:
         cache.free(rc)
 
-    # --- end to end: Engine.step(), host token ids in, sampled ids out, every step ---
+    e2e, upload_bytes = time_e2e(engine, batch, steps, warmup, PROMPT_TOKENS)
+    return device_ms, launches, mid_context, e2e, upload_bytes
+
+
+def time_e2e(engine, batch: int, steps: int, warmup: int, prompt_tokens: int, greedy: bool = True):
+    """End to end: Engine.step(), host token ids in, sampled ids out, every step; greedy, or the
+    reference's default settings (temperature 0.6, top-k 20, top-p 0.95: atomserve/sequence.py:47)."""
+    import torch
+
+    from atomserve_b200.engine.sequence import THINKING_PARAMS, SamplingParams
+
     # long enough that nobody finishes inside the timed region (later requests start later)
-    params = SamplingParams(temperature=0.0, max_tokens=warmup + steps + batch + 16, ignore_eos=True)
-    handles = [engine.submit(p, params) for p in prompts(batch, PROMPT_TOKENS)]
+    base = SamplingParams(temperature=0.0) if greedy else THINKING_PARAMS
+    params = dataclasses.replace(base, max_tokens=warmup + steps + batch + 16, ignore_eos=True)
+    handles = [engine.submit(p, params) for p in prompts(batch, prompt_tokens)]
     while any(h.first_token_at is None for h in handles):
         engine.step()
     for _ in range(warmup):
@@ -193,12 +211,38 @@ def time_decode(engine, batch: int, steps: int, warmup: int, prompt_tokens: int 
     torch.cuda.synchronize()
     e2e_s = time.perf_counter() - t0
     e2e_tokens = engine.num_generated_tokens - before
-    upload_bytes = runner.last_upload_bytes  # the packed int32 buffer of a decode step
+    upload_bytes = engine.runner.last_upload_bytes  # the packed int32 buffer of a decode step
     while engine.step():
         pass
     for h in handles:
         list(h)
-    return device_ms, launches, mid_context, e2e_tokens / e2e_s, upload_bytes
+    return e2e_tokens / e2e_s, upload_bytes
+
+
+def time_prefill_through_engine(model, budget: int, repeats: int, warmup: int) -> float:
+    """One cold prompt of 2,048 tokens, one output token, through Engine.generate under a token
+    budget per step (512 is the reference's default, atomserve/config.py:75: four portions), as
+    the reference times its prefill (bench/engine.py:121-126); milliseconds, CUDA events."""
+    import torch
+
+    from atomserve_b200.config import EngineConfig
+    from atomserve_b200.engine.engine import create_engine
+    from atomserve_b200.engine.sequence import SamplingParams
+
+    config = EngineConfig(block_size=BLOCK_SIZE, num_blocks=8 * (CONTEXT // BLOCK_SIZE) + 64, max_num_seqs=8,
+                          max_num_batched_tokens=budget, max_model_len=CONTEXT, enable_prefix_caching=False)  # fmt: skip
+    engine = create_engine(model, config, sampler_seed=0)
+    params = SamplingParams(temperature=0.0, max_tokens=1)
+    for _ in range(warmup):
+        engine.generate(prompts(1, PROMPT_TOKENS), params)
+    torch.cuda.synchronize()
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    for _ in range(repeats):
+        engine.generate(prompts(1, PROMPT_TOKENS), params)
+    end.record()
+    torch.cuda.synchronize()
+    return start.elapsed_time(end) / repeats
 
 
 def time_serving(engine, requests: int, decode_tokens: int, seed: int = 0) -> dict:
@@ -459,6 +503,52 @@ def gemm_timelines(which: str, tokens: list[int]) -> None:
         del ws
 
 
+def reference_arm(args) -> int:
+    """The same measurement on the unmodified reference (baseline/reference_arm.py): its own
+    engine, sampler and PyTorch model code on this GPU, nothing of this package."""
+    from baseline.reference_arm import ReferenceUnavailable, run
+
+    shape = SHAPES[args.shape]
+    layers = args.layers if args.layers_given else shape["num_hidden_layers"]
+    warmup = max(args.warmup, 3)
+    try:
+        with ClockSampler("reference_clocks.csv") as clocks:
+            r = run(shape, layers, args.batch, args.steps, warmup, PROMPT_TOKENS, CONTEXT, BLOCK_SIZE)
+    except ReferenceUnavailable as why:
+        print(json.dumps({"impl": "reference", "unavailable": str(why)}))
+        return 0
+    pk = peaks()
+    c = shape
+    flops = prefill_flops(argparse.Namespace(
+        num_attention_heads=c["num_attention_heads"], num_key_value_heads=c["num_key_value_heads"], head_dim=c["head_dim"],
+        hidden_size=c["hidden_size"], intermediate_size=c["intermediate_size"], num_hidden_layers=layers, vocab_size=c["vocab_size"],
+    ), PROMPT_TOKENS)  # fmt: skip
+    main_, ms = r["main"], r["main"]["device_ms"]
+    line = {
+        "impl": "reference",
+        "metric": "decode tok/s at batch 8 (Qwen3-8B shape, context 2048-4096); prefill tok/s at 2,048 tokens",
+        "value": round(main_["tokens_per_s_device"], 1), "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": warmup,
+        "ms_per_step": round(ms, 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+        "data": "synthetic token ids, random-init weights N(0, 0.02)",
+        "config": {
+            "model": "Qwen3-8B shape", "layers": layers, "layers_full": shape["num_hidden_layers"], "hidden": c["hidden_size"],
+            "heads": c["num_attention_heads"], "kv_heads": c["num_key_value_heads"], "head_dim": c["head_dim"],
+            "intermediate": c["intermediate_size"], "vocab": c["vocab_size"], "global_batch": args.batch, "seq_len": CONTEXT,
+            "prompt_tokens": PROMPT_TOKENS, "block_size": BLOCK_SIZE, "parallelism": "single-gpu",
+            "l2": "weights read per step exceed L2; no flush needed", "sampling": "greedy",
+            "path": "the reference's Engine.step on cuda: PyTorch matmul, SDPA, its own sampler",
+        },
+        "e2e": {"value": round(main_["tokens_per_s_e2e"], 1), "unit": "tokens/s"},
+        "prefill": {"value": round(PROMPT_TOKENS * 1000.0 / r["prefill_ms"], 1), "tokens": PROMPT_TOKENS, "ms": round(r["prefill_ms"], 3),
+                    "frac": round(flops / (r["prefill_ms"] * 1e-3) / (pk["bf16_tflops"] * 1e12), 4),
+                    "budget512_ms": round(r["prefill_budget512_ms"], 3)},
+        "points": r["points"],
+        "clocks": clocks.summary(),
+    }  # fmt: skip
+    print(json.dumps(line))
+    return 0
+
+
 def main() -> int:
     parser = argparse.ArgumentParser()
     parser.add_argument("--gpus", type=int, default=1)
@@ -479,14 +569,11 @@ def main() -> int:
     parser.add_argument("--timeline", action="store_true", help="with --only gemm: where a decode-size call's time goes")
     args = parser.parse_args()
     args.layers_given = any(a == "--layers" or a.startswith("--layers=") for a in sys.argv[1:])
-    if args.impl == "reference":
-        print(json.dumps({"impl": "reference", "unavailable":
-                          "the reference runs on Apple MPS or CPU only (no CUDA path) and does not install here: "
-                          "it needs Python >= 3.14 and the uv_build backend, neither in this image"}))  # fmt: skip
-        return 0
     if args.gpus != 1:
         print(f"bench.py measures one GPU; --gpus {args.gpus} is not supported (the engine is single-GPU)")
         return 2
+    if args.impl == "reference":
+        return reference_arm(args)
     warmup = max(args.warmup, 3)
 
     import torch
@@ -542,6 +629,9 @@ def main() -> int:
     # long enough for the power cap to act and for a few clock samples: the prefill runs at the cap
     with ClockSampler("bench_clocks_prefill.csv") as prefill_clocks:
         prefill_ms = time_prefill(engine, steps=20, warmup=3)
+    prefill_512_ms = time_prefill_through_engine(model, 512, repeats=10, warmup=3)
+    sampled_e2e, _ = time_e2e(engine, args.batch, max(args.steps // 2, 8), 3, PROMPT_TOKENS, greedy=False)
+    points[f"decode_b{args.batch}_sampled_e2e"] = round(sampled_e2e, 1)
 
     value = args.batch * 1000.0 / device_ms
     achieved = step_bytes(config, args.batch, ctx) / (device_ms * 1e-3) / 1e9
@@ -572,7 +662,7 @@ def main() -> int:
         "prefill": {"value": round(PROMPT_TOKENS * 1000.0 / prefill_ms, 1), "tokens": PROMPT_TOKENS, "ms": round(prefill_ms, 3),
                     "frac": round(flops / (prefill_ms * 1e-3) / (pk["bf16_tflops"] * 1e12), 4),
                     "frac_sustained": round(flops / (prefill_ms * 1e-3) / (pk["bf16_tflops_sustained"] * 1e12), 4),
-                    "sm_mhz": prefill_clocks.summary()["sm_mhz"]},
+                    "sm_mhz": prefill_clocks.summary()["sm_mhz"], "budget512_ms": round(prefill_512_ms, 3)},
         "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
                      "frac": round(achieved / pk["hbm_gbs"], 4), "peaks": pk["source"]},
         "points": points,
