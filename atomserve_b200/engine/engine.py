@@ -1,18 +1,23 @@
-"""The engine: one loop that owns the device and runs scheduled steps.
+"""The engine: the one thread that owns the device, and the mailboxes through which client
+threads reach it.
 
-    loop:
-        take new requests and aborts from the inbox    -> scheduler
-        plan    = scheduler.schedule()                  what runs this step (host only)
-        logits  = runner.step(rows of the plan)         one forward pass
-        tokens  = sampler.sample(logits, ...)           the step's one synchronisation
-        scheduler.update(plan, results)                 advance, retire finished requests
-        push each new token to its request's handle
+Clients never touch scheduler, cache or device. They post mail (`_Submit`, `_Cancel`) and read
+their request's `RequestHandle`, which the engine thread feeds with the token ids of each step
+and, last, a closing record with the reason. The engine thread (or whoever calls `step()` in
+its place) repeats:
 
-Clients talk to it through a thread-safe inbox and one outbox per request; it deals in token
-ids only. The programming interface follows the reference's (atomserve/engine.py:41-264):
-`create_engine`, `Engine.submit / abort / start / shutdown / generate / step / stats`, and
-`RequestHandle` as an iterator of token ids with `finish_reason`, `ttft` and
-`decode_tokens_per_s`.
+    read the mail                               new requests join the line, cancelled ones leave
+    plan   = scheduler.schedule()               who runs how many tokens (host only)
+    logits = runner.step(rows of the plan)      one pass over the step's tokens
+    ids    = sampler.sample(logits, ...)        reading them back is the step's one wait
+    the device's status words are looked at     a kernel that gave up a wait fails the step
+    scheduler.update(plan, results)             book tokens, retire what is done
+    hand each request its new ids
+
+It deals in token ids only. The programming interface is the reference's
+(atomserve/engine.py:41-264): `create_engine`, `Engine.submit / abort / start / shutdown /
+generate / step / stats`, and a handle that is iterated for ids and carries `finish_reason`,
+`ttft`, `decode_tokens_per_s` and `num_cached_tokens`.
 """
 
 from __future__ import annotations
@@ -34,116 +39,161 @@ from atomserve_b200.engine.sequence import SamplingParams, Sequence, SequenceSta
 from atomserve_b200.parts.model import DecoderModel
 from atomserve_b200.sampling.sampler import Sampler
 
+# ---- what travels between client threads and the engine thread ---------------------------------
+
 
 @dataclass
-class _Finished:
+class _Submit:
+    seq: Sequence
+    handle: "RequestHandle"
+
+
+@dataclass
+class _Cancel:
+    request_id: int
+
+
+class _Wake:
+    """Mail with no content: it only ends a blocking read of the mailbox (shutdown)."""
+
+
+@dataclass
+class _Closing:
+    """The last record a handle receives."""
+
     reason: str  # "stop", "length", "abort" or "error"
     error: BaseException | None = None
 
 
 class RequestHandle:
-    """The client's end of one request: iterate it to receive token ids as they are made."""
+    """A client's view of its request. Iterating it yields token ids as steps produce them and
+    ends when the request does; the figures below are filled in by the engine thread."""
 
-    def __init__(self, request_id: int, engine: "Engine", num_prompt_tokens: int):
+    def __init__(self, request_id: int, cancel, num_prompt_tokens: int):
         self.id = request_id
         self.num_prompt_tokens = num_prompt_tokens
         self.num_output_tokens = 0
-        self.num_cached_tokens = 0
+        self.num_cached_tokens = 0  # prompt tokens that the prefix cache supplied
         self.finish_reason: str | None = None
         self.submitted_at = time.perf_counter()
         self.first_token_at: float | None = None
         self.finished_at: float | None = None
-        self._engine = engine
-        self._outbox: queue.SimpleQueue = queue.SimpleQueue()
+        self._cancel = cancel
+        self._feed: queue.SimpleQueue = queue.SimpleQueue()  # lists of ids, then one _Closing
 
     def __iter__(self) -> Iterator[int]:
         while True:
-            event = self._outbox.get()
-            if isinstance(event, _Finished):
-                self.finish_reason = event.reason
-                if event.error is not None:
-                    raise RuntimeError("engine step failed") from event.error
+            item = self._feed.get()
+            if isinstance(item, _Closing):
+                self.finish_reason = item.reason
+                if item.error is not None:
+                    raise RuntimeError("engine step failed") from item.error
                 return
-            yield event
+            yield from item
 
     def abort(self) -> None:
-        self._engine.abort(self.id)
+        self._cancel(self.id)
 
     @property
     def ttft(self) -> float | None:
-        return None if self.first_token_at is None else self.first_token_at - self.submitted_at
+        """Seconds from submission to the first token."""
+        if self.first_token_at is None:
+            return None
+        return self.first_token_at - self.submitted_at
 
     @property
     def decode_tokens_per_s(self) -> float | None:
-        if self.first_token_at is None or self.finished_at is None or self.num_output_tokens < 2:
+        """Tokens per second after the first one (None until the request has ended with two)."""
+        if self.finished_at is None or self.first_token_at is None or self.num_output_tokens < 2:
             return None
         return (self.num_output_tokens - 1) / max(self.finished_at - self.first_token_at, 1e-9)
+
+    # engine thread only
+    def _deliver(self, tokens: list[int], now: float) -> None:
+        if self.first_token_at is None:
+            self.first_token_at = now
+        self.num_output_tokens += len(tokens)
+        self._feed.put(tokens)
+
+    def _close(self, reason: str, error: BaseException | None, cached: int) -> None:
+        self.num_cached_tokens = cached
+        self.finished_at = time.perf_counter()
+        self._feed.put(_Closing(reason, error))
+
+
+class DeviceFault(RuntimeError):
+    """A kernel reported through the device's status words that it could not finish its work;
+    the step's logits are not to be trusted."""
 
 
 class Engine:
     def __init__(self, runner: ModelRunner, scheduler: Scheduler, sampler: Sampler):
         self.runner, self.scheduler, self.sampler = runner, scheduler, sampler
-        self._inbox: queue.SimpleQueue = queue.SimpleQueue()
-        self._handles: dict[int, RequestHandle] = {}
-        self._ids = itertools.count()
+        self._mail: queue.SimpleQueue = queue.SimpleQueue()
+        self._open: dict[int, RequestHandle] = {}  # requests the scheduler still knows
+        self._next_id = itertools.count()
         self._thread: threading.Thread | None = None
-        self._stopping = False
+        self._stop = threading.Event()
+        # counters, written by the engine thread
         self.num_steps = 0
-        self.last_batch_seqs = 0
-        self.last_batch_tokens = 0
-        self.num_prompt_tokens = 0
-        self.num_cached_prompt_tokens = 0
+        self.last_batch_seqs = self.last_batch_tokens = 0
+        self.num_prompt_tokens = self.num_cached_prompt_tokens = 0
         self.num_generated_tokens = 0
         self.num_preemptions = 0
 
-    # ---- client side (any thread) ---------------------------------------------------------------
+    # ---- for clients, from any thread ----------------------------------------------------------
 
     def submit(self, prompt_ids: list[int], params: SamplingParams) -> RequestHandle:
-        limit = self.scheduler.config.max_model_len
-        if not 0 < len(prompt_ids) < limit:
-            raise ValueError(f"prompt has {len(prompt_ids)} tokens; must be 1 to {limit - 1}")
+        """Post a request; its handle comes back at once. Bad requests are refused here, on the
+        caller's thread, before they can reach a kernel."""
+        longest = self.scheduler.config.max_model_len
+        if not 0 < len(prompt_ids) < longest:
+            raise ValueError(f"prompt has {len(prompt_ids)} tokens; must be 1 to {longest - 1}")
         if params.max_tokens < 1:
             raise ValueError("max_tokens must be at least 1")
         vocab = self.runner.model.spec.vocab_size
         if min(prompt_ids) < 0 or max(prompt_ids) >= vocab:
             raise ValueError(f"prompt holds a token id outside [0, {vocab})")
-        request_id = next(self._ids)
-        handle = RequestHandle(request_id, self, len(prompt_ids))
-        self._inbox.put(("add", Sequence(request_id, list(prompt_ids), params), handle))
+        rid = next(self._next_id)
+        handle = RequestHandle(rid, self.abort, len(prompt_ids))
+        self._mail.put(_Submit(Sequence(rid, list(prompt_ids), params), handle))
         return handle
 
     def abort(self, request_id: int) -> None:
-        self._inbox.put(("abort", request_id))
+        """Ask for a request to be dropped; harmless if it has ended already."""
+        self._mail.put(_Cancel(request_id))
 
     def start(self) -> None:
-        self._thread = threading.Thread(target=self._loop, name="atomserve-b200-engine", daemon=True)
+        self._thread = threading.Thread(target=self._serve, name="atomserve-b200-engine", daemon=True)
         self._thread.start()
 
     def shutdown(self) -> None:
-        self._stopping = True
-        self._inbox.put(("wake",))
+        """Let the engine thread finish the step it is in, then end it."""
+        self._stop.set()
+        self._mail.put(_Wake())
         if self._thread is not None:
             self._thread.join()
 
     def generate(self, prompts: list[list[int]], params: SamplingParams) -> list[list[int]]:
-        """Run prompts to completion on the calling thread; each one's output ids. All are
-        submitted first, so they are batched together (atomserve/engine.py:137-146)."""
+        """Blocking convenience for tests, benchmarks and the command line: post every prompt,
+        step on this thread until nothing is left, return each prompt's ids. Posting all of them
+        before the first step is what batches them (atomserve/engine.py:137-146)."""
         handles = [self.submit(p, params) for p in prompts]
         while self.step():
             pass
         return [list(h) for h in handles]
 
     def stats(self) -> dict:
-        s = self.scheduler
-        total = s.cache.num_blocks
-        used = total - s.cache.num_free_blocks
+        sched, cache = self.scheduler, self.scheduler.cache
+        pages = cache.num_blocks
+        held = pages - cache.num_free_blocks
         return {
-            "running": len(s.running),
-            "waiting": len(s.waiting),
-            "kv_blocks_used": used,
-            "kv_blocks_total": total,
-            "kv_usage": used / total,
-            "kv_blocks_cached": sum(g.allocator.num_cached for g in s.cache.groups),
+            "running": len(sched.running),
+            "waiting": len(sched.waiting),
+            "kv_blocks_used": held,
+            "kv_blocks_total": pages,
+            "kv_usage": held / pages,
+            "kv_blocks_cached": sum(g.allocator.num_cached for g in cache.groups),
             "steps": self.num_steps,
             "last_batch_seqs": self.last_batch_seqs,
             "last_batch_tokens": self.last_batch_tokens,
@@ -153,82 +203,99 @@ class Engine:
             "preemptions": self.num_preemptions,
         }
 
-    # ---- engine side (engine thread only) -------------------------------------------------------
-
-    def execute(self, out: SchedulerOutput) -> list[StepResult]:
-        """Run one scheduled step and sample: a sequence that reaches the end of its known
-        tokens gets one new token (atomserve/runner.py:194-212)."""
-        logits = self.runner.step(rows_for(out.seqs, out.num_new_tokens))
-        ends = [s.num_computed_tokens + n == len(s.token_ids) for s, n in zip(out.seqs, out.num_new_tokens)]  # reaches_end
-        sampled = iter(self.sampler.sample(logits, [s for s, end in zip(out.seqs, ends) if end]))
-        return [
-            StepResult([next(sampled)] if end else [], seq.num_computed_tokens + n)
-            for seq, n, end in zip(out.seqs, out.num_new_tokens, ends)
-        ]
+    # ---- the engine thread ---------------------------------------------------------------------
 
     def step(self) -> bool:
-        """One scheduling step; False when there is nothing to do."""
-        self._drain_inbox(block=False)
+        """Plan, run and book one step. False when no request is left to work on."""
+        self._read_mail(wait=False)
         if not self.scheduler.has_work:
             return False
-        out = self.scheduler.schedule()
-        self.num_preemptions += len(out.preempted)
-        if not out.seqs:
+        plan = self.scheduler.schedule()
+        self.num_preemptions += len(plan.preempted)
+        if not plan.seqs:
             raise RuntimeError("scheduler has work but scheduled nothing")
-        results = self.execute(out)
-        new_tokens = self.scheduler.update(out, results)
+        results = self.execute(plan)
+        self._check_device()
+        gained = self.scheduler.update(plan, results)
 
-        now = time.perf_counter()
         self.num_steps += 1
-        self.last_batch_seqs, self.last_batch_tokens = len(out.seqs), out.num_tokens
-        for seq, tokens in new_tokens:
-            handle = self._handles[seq.id]
-            if handle.first_token_at is None:
-                handle.first_token_at = now
-            handle.num_output_tokens += len(tokens)
+        self.last_batch_seqs, self.last_batch_tokens = len(plan.seqs), plan.num_tokens
+        now = time.perf_counter()
+        for seq, tokens in gained:
             self.num_generated_tokens += len(tokens)
-            for token in tokens:
-                handle._outbox.put(token)
+            self._open[seq.id]._deliver(tokens, now)
             if seq.status is SequenceStatus.FINISHED:
                 self._close(seq)
         return True
 
-    def _drain_inbox(self, block: bool) -> None:
+    def execute(self, plan: SchedulerOutput) -> list[StepResult]:
+        """The device's part of a step: run the plan's rows and sample one token for every
+        sequence whose row reaches the end of its known tokens (atomserve/runner.py:194-212).
+        The status words are sent on their way to the host behind the model's kernels, so that
+        the read of the sampled ids, the step's one wait, brings them along."""
+        rows = rows_for(plan.seqs, plan.num_new_tokens)
+        logits = self.runner.step(rows)
+        status = getattr(self.runner, "device_status", None)
+        if status is not None:
+            status.send_to_host()
+        picked = self.sampler.sample(logits, [seq for seq, row in zip(plan.seqs, rows) if row.want])
+        results, k = [], 0
+        for seq, row in zip(plan.seqs, rows):
+            reached = row.start + len(row.tokens)
+            if row.want:
+                results.append(StepResult([picked[k]], reached))
+                k += 1
+            else:
+                results.append(StepResult([], reached))
+        return results
+
+    def _check_device(self) -> None:
+        status = getattr(self.runner, "device_status", None)
+        if status is not None:
+            problem = status.problem_on_host()
+            if problem:
+                raise DeviceFault(problem)
+
+    def _read_mail(self, wait: bool) -> None:
+        """Move what clients posted into the scheduler; with `wait`, sleep until something comes."""
         while True:
             try:
-                message = self._inbox.get(block=block)
+                mail = self._mail.get(block=wait)
             except queue.Empty:
                 return
-            block = False
-            if message[0] == "add":
-                _, seq, handle = message
-                self._handles[seq.id] = handle
-                self.num_prompt_tokens += seq.num_prompt_tokens
-                self.scheduler.add(seq)
-            elif message[0] == "abort":
-                seq = self.scheduler.abort(message[1])
-                if seq is not None:
-                    self._close(seq)
+            wait = False
+            if isinstance(mail, _Submit):
+                self._open[mail.seq.id] = mail.handle
+                self.num_prompt_tokens += mail.seq.num_prompt_tokens
+                self.scheduler.add(mail.seq)
+            elif isinstance(mail, _Cancel):
+                dropped = self.scheduler.abort(mail.request_id)
+                if dropped is not None:
+                    self._close(dropped)
 
     def _close(self, seq: Sequence, error: BaseException | None = None) -> None:
-        handle = self._handles.pop(seq.id)
-        handle.num_cached_tokens = seq.num_cached_tokens
+        handle = self._open.pop(seq.id)
         self.num_cached_prompt_tokens += seq.num_cached_tokens
-        handle.finished_at = time.perf_counter()
         self.sampler.release(seq.id)
-        handle._outbox.put(_Finished(seq.finish_reason or "error", error))
+        handle._close(seq.finish_reason or "error", error, seq.num_cached_tokens)
 
-    def _loop(self) -> None:
-        while not self._stopping:
+    def _fail_everything(self, error: BaseException) -> None:
+        """A step raised: every request the scheduler knows ends with reason "error" and gives its
+        pages back; the engine itself carries on with whatever is submitted next."""
+        sched = self.scheduler
+        for seq in [*sched.running, *sched.waiting]:
+            sched.abort(seq.id)
+            seq.finish_reason = "error"
+            self._close(seq, error)
+
+    def _serve(self) -> None:
+        while not self._stop.is_set():
             try:
                 if not self.step():
-                    self._drain_inbox(block=True)
-            except Exception as error:  # noqa: BLE001  fail the requests, keep the engine alive
+                    self._read_mail(wait=True)
+            except Exception as error:  # noqa: BLE001  the requests fail, the engine lives on
                 traceback.print_exc(file=sys.stderr)
-                for seq in [*self.scheduler.running, *self.scheduler.waiting]:
-                    self.scheduler.abort(seq.id)
-                    seq.finish_reason = "error"
-                    self._close(seq, error)
+                self._fail_everything(error)
 
 
 def create_engine(
@@ -237,11 +304,9 @@ def create_engine(
     eos_token_ids: frozenset[int] = frozenset(),
     sampler_seed: int | None = None,
 ) -> Engine:
-    """Wire cache pools, runner, scheduler and sampler around a loaded model (the thread is
-    not started). atomserve/engine.py:237-264."""
-    cache = CacheManager(
-        model.cache_requirements(), engine_config.block_size, engine_config.num_blocks,
-        engine_config.max_num_seqs, model.dtype, model.device,
-    )  # fmt: skip
-    runner = ModelRunner(model, cache, engine_config.cuda_graphs)
-    return Engine(runner, Scheduler(engine_config, cache, eos_token_ids), Sampler(model.device, sampler_seed))
+    """Cache pools, runner, scheduler and sampler around a loaded model; the engine thread is
+    not started (atomserve/engine.py:237-264)."""
+    c = engine_config
+    cache = CacheManager(model.cache_requirements(), c.block_size, c.num_blocks, c.max_num_seqs, model.dtype, model.device)
+    runner = ModelRunner(model, cache, c.cuda_graphs)
+    return Engine(runner, Scheduler(c, cache, eos_token_ids), Sampler(model.device, sampler_seed))

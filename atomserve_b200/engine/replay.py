@@ -64,6 +64,10 @@ class TraceReplayer:
             rows.append(Row(tokens, computed, rc, [int(w) for w in e.get("want", [])]))
             self.live[rid] = (rc, computed + len(tokens))
         logits = self.runner.step(rows)
+        if self.runner.device_status is not None:
+            problem = self.runner.device_status.problem()  # a read of the device: replay is no hot path
+            if problem:
+                raise RuntimeError(f"step failed on the device: {problem}")
         for rid in end:
             rc, _ = self.live.pop(str(rid))
             self.cache.free(rc)

@@ -18,6 +18,7 @@ single tokens are replayed from CUDA graphs, captured per (requests, table width
 
 from __future__ import annotations
 
+from collections import OrderedDict
 from dataclasses import dataclass, field
 
 import numpy as np
@@ -25,6 +26,7 @@ import torch
 
 from atomserve_b200.cache.manager import CacheManager, RequestCache
 from atomserve_b200.ops.library import launches, note_replay
+from atomserve_b200.ops.status import status_for
 from atomserve_b200.parts.base import CacheView, StepContext
 from atomserve_b200.parts.model import DecoderModel
 
@@ -62,18 +64,77 @@ class _Packed:
         return {name: buffer[off : off + n] for name, off, n in self.parts}
 
 
+GRAPH_BATCHES = (1, 2, 4, 8, 12, 16, 24, 32, 48, 64, 96, 128, 192, 256)
+
+
+def batch_bucket(requests: int) -> int | None:
+    """The number of requests a decode graph is captured for: the batch rounded up to a few
+    sizes and padded with dummy requests; None beyond the largest."""
+    for b in GRAPH_BATCHES:
+        if b >= requests:
+            return b
+    return None
+
+
+def width_bucket(pages: int) -> int:
+    """Block-table width of a decode graph: the pages of the longest request, to a power of two."""
+    width = 16
+    while width < pages:
+        width *= 2
+    return width
+
+
+def context_bucket(max_context: int) -> int:
+    """The longest context rounded up by less than 256 keys or at most a quarter. The attention kernels size their
+    key partitions for the rounded value, so a coarser bucket would leave partitions empty."""
+    step = 256 if max_context <= 2048 else (512 if max_context <= 8192 else 1024)
+    return -(-max_context // step) * step
+
+
+class GraphCache:
+    """Captured decode graphs by shape key, at most `limit` of them: the one unused longest is
+    dropped when a new one comes, and with it the memory only it held. All graphs write their
+    logits into one buffer that the runner owns, so a graph keeps nothing of its own but its
+    kernels' arguments."""
+
+    def __init__(self, limit: int = 48):
+        self.limit = limit
+        self._entries: OrderedDict[tuple, tuple] = OrderedDict()
+
+    def __len__(self) -> int:
+        return len(self._entries)
+
+    def get(self, key: tuple):
+        entry = self._entries.get(key)
+        if entry is not None:
+            self._entries.move_to_end(key)
+        return entry
+
+    def put(self, key: tuple, entry: tuple) -> None:
+        self._entries[key] = entry
+        self._entries.move_to_end(key)
+        while len(self._entries) > self.limit:
+            self._entries.popitem(last=False)
+
+    def clear(self) -> None:
+        self._entries.clear()
+
+
 class ModelRunner:
     def __init__(self, model: DecoderModel, cache: CacheManager, cuda_graphs: bool = True):
         self.model, self.cache = model, cache
         self.device = model.device
         self.block_size = cache.block_size
+        # how kernels report that they could not finish (none on the CPU stand-ins of the tests)
+        self.device_status = status_for(self.device) if self.device.type == "cuda" else None
         self.views: list[CacheView | None] = [cache.entry_view(i) for i in range(len(model.schedule))]
         # Graphs replay the same kernels on new inputs; a part that updates state of its own in
         # place would be run again by capture and warm-up, so such models step eagerly.
         self.use_graphs = cuda_graphs and self.device.type == "cuda" and not cache.entry_state
         self._copy_done: torch.cuda.Event | None = None
-        self._graphs: dict[tuple, tuple] = {}
+        self._graphs = GraphCache()
         self._graph_pool = None
+        self._graph_logits: torch.Tensor | None = None  # [largest batch bucket met, vocab]: every graph's output
         # request uid -> (generation, per group a numpy copy of its block table, extended as it grows)
         self._tables: dict[int, tuple[int, list[np.ndarray]]] = {}
         # decode steps: per group a host matrix [state slot, page] of the live requests' block tables,
@@ -297,51 +358,46 @@ class ModelRunner:
         self._bind(groups)
         return self.model.forward(ctx, self.views)
 
-    GRAPH_BATCHES = (1, 2, 4, 8, 12, 16, 24, 32, 48, 64, 96, 128, 192, 256)
-
     def _step_graph(self, rows: list[Row]) -> torch.Tensor:
         """Decode-only step through a captured graph. The graph is keyed by everything that
         fixes kernel shapes and buffer offsets: requests (rounded up to a bucket and padded with
         dummy requests when every row wants its logits, as in generation), table width (rounded
         up to a power of two), wanted rows, and the bucket of the longest context (which sets
-        the key partitions). The returned logits are a view of the graph's output buffer: read
-        them before the next step."""
+        the key partitions). At most GraphCache.limit graphs are kept, and they share one pool of
+        memory and one logits buffer, [largest batch bucket, vocab] float32: 39 MB at 64 requests
+        of a 151,936-token vocabulary, 156 MB at 256. The returned logits are a view of that
+        buffer: read them before the next step."""
         bs = self.block_size
-        need_w = max(-(-(r.start + 1) // bs) for r in rows)
-        pad_w = 16
-        while pad_w < need_w:
-            pad_w *= 2
+        pad_w = width_bucket(max(-(-(r.start + 1) // bs) for r in rows))
         wanted = sum(len(r.want) for r in rows)
-        pad_r = None
-        if wanted == len(rows) and len(rows) <= self.GRAPH_BATCHES[-1]:
-            pad_r = next(b for b in self.GRAPH_BATCHES if b >= len(rows))
+        pad_r = batch_bucket(len(rows)) if wanted == len(rows) else None
         ctx, groups, key = self.prepare(rows, pad_requests=pad_r, pad_width=pad_w)
-        # the longest context rounded up by at most an eighth or so: the attention kernels size their
-        # key partitions for the rounded value, so a coarse bucket would leave partitions empty
-        step = 256 if ctx.max_context <= 2048 else (512 if ctx.max_context <= 8192 else 1024)
-        ctx_bucket = -(-ctx.max_context // step) * step
-        ctx.max_context = ctx_bucket
-        key = (*key, ctx_bucket)
+        ctx.max_context = context_bucket(ctx.max_context)
+        key = (*key, ctx.max_context)
         self._bind(groups)
+        out_rows = key[3]
+        if self._graph_logits is None or self._graph_logits.shape[0] < out_rows:
+            self._graphs.clear()  # they write into the buffer that is being replaced
+            self._graph_logits = torch.empty(out_rows, self.model.spec.vocab_size, device=self.device, dtype=torch.float32)
+        logits = self._graph_logits[:out_rows]
         entry = self._graphs.get(key)
         if entry is None:
             # warm up outside capture (lazy library initialisation must not be captured)
-            self.model.forward(ctx, self.views)
+            self.model.forward(ctx, self.views, logits)
             torch.cuda.synchronize()
             graph = torch.cuda.CUDAGraph()
             if self._graph_pool is None:
-                # one memory pool for all graphs: only one of them runs at a time, and each step's
-                # logits are read before the next step
+                # one memory pool for all graphs: only one of them runs at a time
                 self._graph_pool = torch.cuda.graph_pool_handle()
             before = launches()
             with torch.cuda.graph(graph, pool=self._graph_pool):
-                out = self.model.forward(ctx, self.views)
-            entry = (graph, out, launches() - before)
-            self._graphs[key] = entry
-        graph, out, recorded = entry
+                self.model.forward(ctx, self.views, logits)
+            entry = (graph, launches() - before)
+            self._graphs.put(key, entry)
+        graph, recorded = entry
         graph.replay()
         note_replay(recorded)  # the replay ran what the capture recorded
-        return out[:wanted]
+        return logits[:wanted]
 
 
 def rows_for(seqs, num_new_tokens: list[int]) -> list[Row]:

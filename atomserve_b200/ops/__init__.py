@@ -16,8 +16,10 @@ from atomserve_b200.ops.elementwise import (
 from atomserve_b200.ops.library import KernelLibraryError, require_device
 from atomserve_b200.ops.linear import PartialSums, interleave_gate_up, linear, linear_partial, linear_swiglu, swiglu_fusable
 from atomserve_b200.ops.sampling import argmax_rows, presence_penalty, sample_rows
+from atomserve_b200.ops.status import DeviceStatus, status_for
 
 __all__ = [
+    "DeviceStatus",
     "KernelLibraryError",
     "PartialSums",
     "argmax_rows",
@@ -38,5 +40,6 @@ __all__ = [
     "rotary",
     "sample_rows",
     "silu_mul",
+    "status_for",
     "swiglu_fusable",
 ]

@@ -18,12 +18,15 @@ import os
 import torch
 
 from atomserve_b200.ops.library import KernelLibraryError, check, dtype_code, lib, ptr, require_cuda, stream
+from atomserve_b200.ops.status import status_for
 
 
-def gemm_simt(x: torch.Tensor, w: torch.Tensor, residual: torch.Tensor | None, out_dtype: torch.dtype) -> torch.Tensor:
+def gemm_simt(x: torch.Tensor, w: torch.Tensor, residual: torch.Tensor | None, out_dtype: torch.dtype,
+              out: torch.Tensor | None = None) -> torch.Tensor:  # fmt: skip
     M, K = x.shape
     N = w.shape[0]
-    out = torch.empty(M, N, device=x.device, dtype=out_dtype)
+    if out is None:
+        out = torch.empty(M, N, device=x.device, dtype=out_dtype)
     check(lib().asb_gemm_simt(ptr(out), ptr(x), ptr(w), ptr(residual), M, N, K, dtype_code(x),
                               dtype_code(out), stream()))  # fmt: skip
     return out
@@ -34,23 +37,17 @@ def gemm_simt(x: torch.Tensor, w: torch.Tensor, residual: torch.Tensor | None, o
 # unaligned operands) go to the library either way.
 BACKEND = os.environ.get("ATOMSERVE_B200_GEMM", "tcgen05")
 
-_STATUS: dict[torch.device, torch.Tensor] = {}
-
-
 def gemm_status(device: torch.device) -> torch.Tensor:
-    """The device word the tensor-core GEMM sets if one of its pipeline waits runs out."""
-    if device not in _STATUS:
-        _STATUS[device] = torch.zeros(1, dtype=torch.int32, device=device)
-    return _STATUS[device]
+    """The device word a tcgen05 kernel sets if one of its pipeline waits runs out."""
+    return status_for(device).pipeline
 
 
 def check_gemm_status(device: torch.device | str = "cuda") -> None:
-    """Raise if any tensor-core GEMM since the last check gave up a wait (reads the device)."""
-    status = gemm_status(torch.device(device) if not isinstance(device, torch.device) else device)
-    code = int(status.item())
-    if code:
-        status.zero_()
-        raise KernelLibraryError(f"gemm_tcgen05: a pipeline wait ran out (role {code}: 1 TMA, 2 MMA, 3 epilogue)")
+    """Raise if any kernel since the last check reported through the device's status words (a
+    tcgen05 wait that ran out, a token id outside the embedding table). Reads the device."""
+    problem = status_for(device).problem()
+    if problem:
+        raise KernelLibraryError(problem)
 
 
 _WORKSPACE: dict[torch.device, torch.Tensor] = {}
@@ -81,12 +78,13 @@ _WORKSPACE_FLOATS: dict[tuple[int, int, int], int] = {}
 
 
 def gemm_tcgen05(x: torch.Tensor, w: torch.Tensor, residual: torch.Tensor | None, out_dtype: torch.dtype,
-                 swiglu: bool = False) -> torch.Tensor:  # fmt: skip
+                 swiglu: bool = False, out: torch.Tensor | None = None) -> torch.Tensor:  # fmt: skip
     """bfloat16 x [M, K] . w [N, K]^T on tcgen05 tensor cores (TMA operands, TMEM accumulator).
     swiglu: the rows of w alternate gate and up; returns silu(gate) * up, [M, N / 2]."""
     M, K = x.shape
     N = w.shape[0]
-    out = torch.empty(M, N // 2 if swiglu else N, device=x.device, dtype=out_dtype)
+    if out is None:
+        out = torch.empty(M, N // 2 if swiglu else N, device=x.device, dtype=out_dtype)
     need = _WORKSPACE_FLOATS.get((M, N, K))
     if need is None:
         query = lib().asb_gemm_tcgen05_workspace
@@ -193,8 +191,10 @@ def linear(
     w: torch.Tensor,
     residual: torch.Tensor | None = None,
     out_dtype: torch.dtype | None = None,
+    out: torch.Tensor | None = None,
 ) -> torch.Tensor:
-    require_cuda(x, w, residual)
+    """`out`, if given, is the contiguous [M, N] tensor of the output dtype that takes the result."""
+    require_cuda(x, w, residual, out)
     if x.dim() != 2 or w.dim() != 2 or x.shape[1] != w.shape[1]:
         raise KernelLibraryError(f"linear: x {tuple(x.shape)} does not match w {tuple(w.shape)}")
     if x.dtype != w.dtype or not x.is_contiguous() or not w.is_contiguous():
@@ -202,16 +202,20 @@ def linear(
     out_dtype = out_dtype or x.dtype
     if residual is not None and (residual.shape != (x.shape[0], w.shape[0]) or residual.dtype != out_dtype or not residual.is_contiguous()):
         raise KernelLibraryError("linear: residual must be [M, N], contiguous, in the output dtype")
+    if out is not None and (out.shape != (x.shape[0], w.shape[0]) or out.dtype != out_dtype or not out.is_contiguous()):
+        raise KernelLibraryError("linear: out must be [M, N], contiguous, in the output dtype")
     if x.dtype == torch.float32:
         if out_dtype != torch.float32:
             raise KernelLibraryError("linear: float32 operands give float32 results")
-        return gemm_simt(x, w, residual, torch.float32)
+        return gemm_simt(x, w, residual, torch.float32, out)
     if out_dtype == torch.float32 and residual is not None:
-        return gemm_simt(x, w, residual, torch.float32)
+        return gemm_simt(x, w, residual, torch.float32, out)
     if BACKEND == "tcgen05" and tcgen05_supported(x, w):
-        return gemm_tcgen05(x, w, residual, out_dtype)
+        return gemm_tcgen05(x, w, residual, out_dtype, out=out)
     if out_dtype == torch.float32:
-        return torch.mm(x, w.t(), out_dtype=torch.float32)  # float32 accumulator, not rounded
-    if residual is None:
-        return torch.mm(x, w.t())
-    return torch.addmm(residual, x, w.t())
+        result = torch.mm(x, w.t(), out_dtype=torch.float32)  # float32 accumulator, not rounded
+    elif residual is None:
+        result = torch.mm(x, w.t())
+    else:
+        result = torch.addmm(residual, x, w.t())
+    return result if out is None else out.copy_(result)

@@ -22,7 +22,9 @@ class TokenEmbedding(Part):
 
     def load(self, tensors: dict[str, torch.Tensor]) -> None:
         self.table = tensors[self.name]
-        self.status = torch.zeros(1, dtype=torch.int32, device=self.table.device)
+        # the device's shared status words on a GPU (the engine reads them every step)
+        self.status = (ops.status_for(self.table.device).embedding if self.table.is_cuda
+                       else torch.zeros(1, dtype=torch.int32))
 
     def forward(self, token_ids: torch.Tensor) -> torch.Tensor:
         return ops.embedding(token_ids, self.table, self.status)
@@ -43,8 +45,8 @@ class LMHead(Part):
     def tie(self, embedding: TokenEmbedding) -> None:
         self.weight = embedding.table
 
-    def forward(self, hidden: torch.Tensor) -> torch.Tensor:
-        return ops.linear(hidden, self.weight, out_dtype=torch.float32)
+    def forward(self, hidden: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
+        return ops.linear(hidden, self.weight, out_dtype=torch.float32, out=out)
 
 
 register_part("embedding", "token_embedding", TokenEmbedding)

@@ -3,6 +3,8 @@ output head (atomserve/model.py:363-385 is the reference's fixed form of this lo
 
 from __future__ import annotations
 
+import inspect
+
 import torch
 
 from atomserve_b200.parts.base import Block, CacheView, KVCacheSpec, StateSpec, StepContext, build_block, build_part
@@ -33,6 +35,7 @@ class DecoderModel:
                     raise ValueError(f"run order entry {i} must read the cache of an earlier entry that owns one")
         self.final_norm = build_part("norm", spec.final_norm, d)
         self.head = build_part("head", spec.head, d)
+        self._head_takes_out = "out" in inspect.signature(self.head.forward).parameters
         self.dtype: torch.dtype | None = None
         self.device: torch.device | None = None
 
@@ -68,8 +71,10 @@ class DecoderModel:
                 out.append((mixer.cache_spec(), mixer.state_specs()))
         return out
 
-    def forward(self, ctx: StepContext, views: list[CacheView | None]) -> torch.Tensor:
-        """Run the T tokens of the step; float32 logits [len(ctx.logits_rows), vocab]."""
+    def forward(self, ctx: StepContext, views: list[CacheView | None], logits_out: torch.Tensor | None = None) -> torch.Tensor:
+        """Run the T tokens of the step; float32 logits [len(ctx.logits_rows), vocab], written
+        into `logits_out` where the caller brings the buffer (a head whose `forward` takes no
+        `out` has its result copied there)."""
         x = self.embedding.forward(ctx.token_ids)
         normed = None  # the next block's first norm of x, where the block before it has computed it
         for i, call in enumerate(self.schedule):
@@ -80,7 +85,12 @@ class DecoderModel:
             )
         if ctx.logits_rows.shape[0] == 0:
             return torch.empty(0, self.spec.vocab_size, device=x.device, dtype=torch.float32)
-        return self.head.forward(self.final_norm.forward(x, ctx.logits_rows))
+        hidden = self.final_norm.forward(x, ctx.logits_rows)
+        if logits_out is None:
+            return self.head.forward(hidden)
+        if self._head_takes_out:
+            return self.head.forward(hidden, out=logits_out)
+        return logits_out.copy_(self.head.forward(hidden))
 
 
 def build_model(spec: ModelSpec) -> DecoderModel:

@@ -204,3 +204,50 @@ def test_engine_survives_a_failing_step(setup):
     assert list(again) == plain.greedy_generate(w, cfg, [1, 2], 3)
     eng.shutdown()
     assert eng.stats()["kv_blocks_used"] == 0
+
+
+def test_a_fault_reported_by_the_device_fails_the_step_and_not_the_engine(setup):
+    """The engine looks at the device's status words after every step: a kernel that gave up a
+    wait must not have its logits sampled and streamed as if nothing had happened."""
+    from atomserve_b200.engine.engine import DeviceFault
+
+    class Status:  # what ops.status.DeviceStatus offers the engine
+        def __init__(self):
+            self.sent, self.fault = 0, None
+
+        def send_to_host(self):
+            self.sent += 1
+
+        def problem_on_host(self):
+            fault, self.fault = self.fault, None
+            return fault
+
+    cfg, bs, w, model = setup
+    eng = engine_for(model, bs)
+    status = eng.runner.device_status = Status()
+    status.fault = "a tcgen05 kernel gave up a bounded wait (GEMM: MMA issue)"
+    eng.start()
+    handle = eng.submit([1, 2], SamplingParams(max_tokens=3, **GREEDY))
+    with pytest.raises(RuntimeError, match="engine step failed") as caught:
+        list(handle)
+    assert isinstance(caught.value.__cause__, DeviceFault) and "MMA issue" in str(caught.value.__cause__)
+    assert handle.finish_reason == "error" and handle.num_output_tokens == 0
+    again = eng.submit([1, 2], SamplingParams(max_tokens=3, **GREEDY))
+    assert list(again) == plain.greedy_generate(w, cfg, [1, 2], 3)
+    eng.shutdown()
+    assert status.sent == eng.num_steps + 1 and eng.stats()["kv_blocks_used"] == 0
+
+
+def test_status_words_name_what_went_wrong_and_clear():
+    from atomserve_b200.ops.status import DeviceStatus
+
+    status = DeviceStatus(torch.device("cpu"))
+    assert status.problem() is None and status.problem_on_host() is None
+    status.pipeline.fill_(2)
+    status.embedding.fill_(1)
+    status.send_to_host()
+    text = status.problem_on_host()
+    assert "MMA issue" in text and "outside the vocabulary" in text
+    assert status.problem() is None and status.problem_on_host() is None
+    status.pipeline.fill_(14)
+    assert "prefill attention" in status.problem() and status.words.tolist() == [0, 0, 0, 0]

@@ -83,3 +83,34 @@ def test_gemm_plans_keep_every_tile_within_its_partial_sum_slots():
             first = bisect.bisect_right(begins, tile * kb) - 1
             last = bisect.bisect_right(begins, tile * kb + kb - 1) - 1
             assert last - first + 1 <= max_slots, (M, N, K, tile)
+
+
+def test_decode_graph_keys_are_few_and_the_cache_of_graphs_is_bounded():
+    """Decode graphs are keyed by (batch bucket, table-width bucket, context bucket): over every
+    batch up to 256 and every context up to 40k the buckets stay few, each rounds up by little,
+    and the cache that holds the captured graphs never grows beyond its limit."""
+    from atomserve_b200.engine.runner import GraphCache, batch_bucket, context_bucket, width_bucket
+
+    assert batch_bucket(257) is None
+    batches = {batch_bucket(b) for b in range(1, 257)}
+    assert len(batches) <= 16 and all(batch_bucket(b) >= b for b in range(1, 257))
+    contexts = set()
+    for ctx in range(1, 40961, 7):
+        bucket = context_bucket(ctx)
+        assert ctx <= bucket and (bucket - ctx < 256 or bucket <= ctx * 1.25)
+        contexts.add(bucket)
+    assert len(contexts) <= 64
+    assert {width_bucket(p) for p in range(1, 2561)} == {16, 32, 64, 128, 256, 512, 1024, 2048, 4096}
+    cache = GraphCache(limit=48)
+    dropped = 0
+    for b in sorted(batches):
+        for ctx in sorted(contexts):
+            key = (b, b, (width_bucket(-(-ctx // 16)),), b, ctx)
+            if cache.get(key) is None:
+                cache.put(key, ("graph", 0))
+            assert len(cache) <= 48
+    assert cache.get((1, 1, (16,), 1, 256)) is None  # the oldest went first
+    recent = (256, 256, (width_bucket(40960 // 16),), 256, 40960)
+    assert cache.get(recent) is not None
+    cache.put(("x",), ("graph", 0))
+    assert cache.get(recent) is not None and len(cache) == 48
