@@ -55,16 +55,31 @@ extern "C" int asb_paged_attention_static_scratch(void* out, const void* q, cons
                                                   int NP, float scale, int dtype,
                                                   cudaStream_t stream) {
   if (num_tokens <= 0 || R <= 0) return 0;
-  if (H < 1 || hd < 1 || NP < 1) return asb::fail("static scratch attention: H=%d hd=%d NP=%d", H, hd, NP);
-  // part_m and part_l take rows * NP floats each, part_acc rows * NP * hd, rows = tokens * heads
-  const unsigned long long slots = (unsigned long long)num_tokens * (unsigned long long)H * (unsigned long long)NP;
-  const unsigned long long need = slots * (unsigned long long)(hd + 2);
-  if (need > ASB_STATIC_SCRATCH_FLOATS)
+  // the same ranges asb_paged_attention accepts, checked here first so that the product below
+  // is formed from numbers that cannot wrap it
+  if (H < 1 || H > 65535 || hd < 1 || hd > 256 || NP < 1 || NP > 65535)
+    return asb::fail("static scratch attention: heads %d (1..65535), head size %d (1..256) or partitions %d (1..65535) out of range", H, hd, NP);
+  if (NP == 1)
+    // unpartitioned: the kernel writes `out` itself and no partial result exists, so the array
+    // is neither needed nor looked up, whatever the number of tokens
+    return asb_paged_attention(out, q, k_cache, v_cache, block_tables, req_q_start, req_pos_start,
+                               nullptr, nullptr, nullptr, num_tokens, R, H, KV, hd, bs, table_width,
+                               window, PS, NP, scale, dtype, stream);
+  // part_m and part_l take rows * NP floats each, part_acc rows * NP * hd, rows = tokens * heads;
+  // each factor is checked against the capacity before the next is multiplied in
+  const unsigned long long capacity = ASB_STATIC_SCRATCH_FLOATS;
+  unsigned long long slots = (unsigned long long)num_tokens * (unsigned long long)H;  // < 2^47
+  unsigned long long need = capacity + 1;
+  if (slots <= capacity) {
+    slots *= (unsigned long long)NP;  // < 2^38
+    if (slots <= capacity) need = slots * (unsigned long long)(hd + 2);
+  }
+  if (need > capacity)
     return asb::fail(
-        "static scratch attention: %d tokens x %d heads x %d partitions x (%d + 2) = %llu floats exceed the "
+        "static scratch attention: %d tokens x %d heads x %d partitions x (%d + 2) floats exceed the "
         "built-in scratch of %u floats; use fewer partitions or tokens per call, or asb_paged_attention with "
         "caller-provided scratch",
-        num_tokens, H, NP, hd, need, (unsigned)ASB_STATIC_SCRATCH_FLOATS);
+        num_tokens, H, NP, hd, (unsigned)ASB_STATIC_SCRATCH_FLOATS);
   float* base = nullptr;
   if (int rc = scratch_address(&base)) return rc;
   float* part_m = base;

@@ -11,7 +11,7 @@
 //   int asb_paged_attention_static_scratch(... same arguments as asb_paged_attention,
 //                                           without the three scratch pointers ...)
 //
-// Same computation and same results as asb_paged_attention (attention_simt.cu): the general
+// Same computation and bit-for-bit the same results as asb_paged_attention (attention_simt.cu): the general
 // paged grouped-query attention kernel with the keys cut into NP partitions and a reduction
 // that merges them. The difference is only where the partial results (max, sum, accumulator
 // per token, head and partition) live: in a fixed array inside the library instead of buffers
@@ -20,8 +20,10 @@
 // Limits and rules
 //   * The array holds ASB_STATIC_SCRATCH_FLOATS float32 values (4 Mi = 16 MiB). Every GPU
 //     that loads the library holds those 16 MiB until the process exits, used or not.
-//     A call needs num_tokens * H * NP * (hd + 2) of them; a call that needs more is refused
-//     with an error message (asb_last_error) and launches nothing.
+//     A call with NP > 1 needs num_tokens * H * NP * (hd + 2) of them; a call that needs more
+//     is refused with an error message (asb_last_error) and launches nothing. A call with
+//     NP == 1 has no partial results: it never touches the array and has no such limit.
+//     H and NP must lie in 1..65535 and hd in 1..256, as for asb_paged_attention.
 //   * The first call on each device looks up the array's device address
 //     (cudaGetSymbolAddress, with that device current) and remembers it. Make that first call
 //     before any stream capture begins on that device.

@@ -10,6 +10,7 @@ at a time and moved to the device, so the host never holds the checkpoint whole
 
 from __future__ import annotations
 
+import json
 from contextlib import ExitStack
 from pathlib import Path
 from typing import Any
@@ -52,7 +53,11 @@ class _FileTensors:
         return t.to(device=self.device, dtype=final_dtype(self.specs[name], self.dtype))
 
 
-def check_names_and_shapes(found: dict[str, tuple[int, ...]], specs: list[TensorSpec], ignored: tuple[str, ...]) -> None:
+def check_names_and_shapes(found: dict[str, tuple[int, ...]], specs: list[TensorSpec], ignored: tuple[str, ...],
+                           duplicated: dict[str, list[str]] | None = None) -> None:  # fmt: skip
+    """One error for everything that is wrong with a checkpoint: names the model needs and the
+    files lack, names the files hold and the model does not know, shapes that differ, and names
+    that more than one file of the folder holds (`duplicated`: name -> those files)."""
     wanted = {s.name: s for s in specs}
     missing = sorted(n for n in wanted if n not in found)
     unexpected = sorted(n for n in found if n not in wanted and n not in ignored)
@@ -61,7 +66,8 @@ def check_names_and_shapes(found: dict[str, tuple[int, ...]], specs: list[Tensor
         for n, s in wanted.items()
         if n in found and tuple(found[n]) != tuple(s.shape)
     )
-    if missing or unexpected or wrong:
+    twice = sorted(f"{n} (in {', '.join(files)})" for n, files in (duplicated or {}).items())
+    if missing or unexpected or wrong or twice:
         lines = ["checkpoint does not match the model:"]
         if missing:
             lines.append(f"  missing tensors ({len(missing)}): " + ", ".join(missing))
@@ -69,20 +75,43 @@ def check_names_and_shapes(found: dict[str, tuple[int, ...]], specs: list[Tensor
             lines.append(f"  unexpected tensors ({len(unexpected)}): " + ", ".join(unexpected))
         if wrong:
             lines.append(f"  wrong shapes ({len(wrong)}): " + "; ".join(wrong))
+        if twice:
+            lines.append(f"  tensors held by more than one file ({len(twice)}): " + "; ".join(twice))
         raise WeightsError("\n".join(lines))
 
 
+def checkpoint_files(model_dir: Path) -> list[Path]:
+    """The safetensors files that make up the folder's checkpoint: those that
+    `model.safetensors.index.json` names where the folder has that index (other files lying
+    about are then not part of the model), else every `*.safetensors` file."""
+    index = model_dir / "model.safetensors.index.json"
+    if index.exists():
+        named = sorted(set(json.loads(index.read_text()).get("weight_map", {}).values()))
+        absent = [n for n in named if not (model_dir / n).exists()]
+        if absent:
+            raise FileNotFoundError(f"{index.name} names files that {model_dir} lacks: {', '.join(absent)}")
+        if named:
+            return [model_dir / n for n in named]
+    return sorted(model_dir.glob("*.safetensors"))
+
+
 def load_tensors_into(model: DecoderModel, model_dir: str | Path, dtype: torch.dtype, device: torch.device | str) -> None:
-    """Check every `*.safetensors` file of the folder against the model, then load it."""
-    shards = sorted(Path(model_dir).glob("*.safetensors"))
+    """Check the folder's safetensors files against the model, then load them."""
+    shards = checkpoint_files(Path(model_dir))
     if not shards:
         raise FileNotFoundError(f"no *.safetensors files in {model_dir}")
     specs = model.tensor_specs()
     with ExitStack() as stack:
         files = [stack.enter_context(safe_open(str(s), framework="pt", device="cpu")) for s in shards]
-        where = {name: f for f in files for name in f.keys()}  # noqa: SIM118
+        where: dict[str, Any] = {}
+        holders: dict[str, list[str]] = {}
+        for shard, f in zip(shards, files):
+            for name in f.keys():  # noqa: SIM118
+                where.setdefault(name, f)
+                holders.setdefault(name, []).append(shard.name)
         found = {name: tuple(f.get_slice(name).get_shape()) for name, f in where.items()}
-        check_names_and_shapes(found, specs, model.spec.ignored_tensors)
+        duplicated = {n: fs for n, fs in holders.items() if len(fs) > 1}
+        check_names_and_shapes(found, specs, model.spec.ignored_tensors, duplicated)
         model.load(_FileTensors(where, {s.name: s for s in specs}, dtype, torch.device(device)))
 
 
@@ -108,8 +137,6 @@ def parse_dtype(dtype: str | torch.dtype) -> torch.dtype:
 def read_eos_token_ids(model_dir: str | Path) -> frozenset[int]:
     """End-of-sequence ids from generation_config.json (`eos_token_id`: int or list), else none
     (atomserve/tokenizer.py:36-38 reads the same key)."""
-    import json
-
     path = Path(model_dir) / "generation_config.json"
     if not path.exists():
         return frozenset()

@@ -7,9 +7,9 @@ Run on a machine that has the reference checked out:
 
 The reference needs Python 3.14 only for deferred annotations, so its files are compiled
 here with the `annotations` future flag by an import hook; nothing in them is changed.
-Weights come from tests/plain_qwen3.random_checkpoint (seeded); the file stores the
-sum of their absolute values so that the test can tell a changed generator from a
-changed model. Two ways of running are stored: every position of a whole prompt
+Weights come from tests/plain_qwen3.random_checkpoint (seeded) and are stored in the file
+under `w.<tensor name>`, so that the test runs on exactly the weights the reference saw,
+whatever random numbers the torch build at hand draws. Two ways of running are stored: every position of a whole prompt
 (`whole`), and the same tokens as chunks of 7 next to single-token rows of a second
 request (`mixed`), both through the reference's runner and paged pool.
 """
@@ -133,7 +133,7 @@ def main() -> None:
             "whole": whole.contiguous(),
             "mixed_a": torch.cat(got_a).contiguous(),
             "mixed_b": torch.cat(got_b).contiguous(),
-            "weights_abs_sum": torch.stack([t.abs().sum().double() for t in w.values()]).sum()[None],
+            **{f"w.{k}": v.contiguous() for k, v in w.items()},
             "ids": torch.tensor(ids),
             "other": torch.tensor(other),
         }

@@ -57,3 +57,56 @@ def bfloat16_tolerance(w: dict, cfg: dict, prompt: list[int], ref: torch.Tensor)
     every kernel and all host logic and are held to 2e-5.)"""
     rounded = plain.forward(w, cfg, prompt, activations=torch.bfloat16)
     return max(2 * float((rounded - ref).abs().max()), 0.01 * float(ref.abs().max()))
+
+
+class Oracle:
+    """Float32 logits of a whole prompt from the plain implementation; indexing gives the rows
+    asked for, still carrying the prompt's bfloat16 allowance."""
+
+    def __init__(self, w=None, cfg=None, prompt=None, logits=None, allowance=None):
+        if logits is None:
+            logits = plain.forward(w, cfg, prompt)
+            allowance = bfloat16_tolerance(w, cfg, prompt, logits)
+        self.logits, self.allowance = logits, allowance
+
+    def __getitem__(self, rows):
+        return Oracle(logits=self.logits[rows], allowance=self.allowance)
+
+
+BF16_REPORT: list[tuple[str, float]] = []  # (what, error / allowance) of every bfloat16 check
+
+
+def check(got, oracle, dtype, what):
+    ref = oracle.logits
+    assert got.shape == ref.shape, f"{what}: shape {tuple(got.shape)} for {tuple(ref.shape)}"
+    if dtype == "float32":
+        err = rel_error(got.cpu(), ref)
+        assert err < FLOAT32_TOLERANCE, f"{what}: relative error {err:.3g}"
+        assert torch.equal(got.cpu().argmax(-1), ref.argmax(-1)), what
+    else:
+        err = float((got.cpu() - ref).abs().max())
+        assert err <= oracle.allowance, f"{what}: error {err:.3g}, allowed {oracle.allowance:.3g}"
+        BF16_REPORT.append((what, err / oracle.allowance))
+
+
+def mixed_trace(ps, rng, max_live=4, largest=20):
+    """Steps that keep up to `max_live` requests going: each live request brings a portion of
+    random size, 2 to `largest` - 1 tokens (prompt phase) or one token (its last 8 tokens), some sit a step out."""
+    steps, live, waiting, done_at = [], {}, list(range(len(ps))), {}
+    while waiting or live:
+        while waiting and len(live) < max_live:
+            live[waiting.pop(0)] = 0
+        entries, end = [], []
+        for i in list(live):
+            if len(live) > 1 and rng.random() < 0.2:
+                continue
+            at, total = live[i], len(ps[i])
+            n = 1 if at >= total - 8 else min(int(rng.integers(2, largest)), total - 8 - at) or 1
+            entries.append(dict(id=i, tokens=ps[i][at : at + n], want=list(range(n)), at=at))
+            live[i] = at + n
+            if at + n == total:
+                end.append(i)
+                del live[i]
+        if entries:
+            steps.append((entries, end))
+    return steps

@@ -77,6 +77,26 @@ def attention(
     return torch.einsum("hts,shd->thd", probs, v)
 
 
+def attention_rows(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, positions: torch.Tensor,
+                   window: int | None = None) -> torch.Tensor:  # fmt: skip
+    """`attention` for a few queries of a long sequence: q [n, H, hd] are the queries at
+    `positions` [n]; k, v [S, KV, hd] hold every key of the sequence. The same formula row by
+    row (query at p sees keys j <= p, and j > p - window with a window; head j uses kv head
+    j // group; scale head_dim^-0.5; atomserve/model.py:222-231), without the S x S scores that
+    whole long sequences would need."""
+    n, H, hd = q.shape
+    group = H // k.shape[1]
+    k = k.repeat_interleave(group, dim=1).transpose(0, 1)  # [H, S, hd]
+    v = v.repeat_interleave(group, dim=1).transpose(0, 1)
+    out = torch.empty_like(q)
+    for i in range(n):
+        p = int(positions[i])
+        first = 0 if window is None else max(0, p - window + 1)
+        scores = torch.einsum("hd,hsd->hs", q[i], k[:, first : p + 1]) * hd**-0.5
+        out[i] = torch.einsum("hs,hsd->hd", torch.softmax(scores, dim=-1), v[:, first : p + 1])
+    return out
+
+
 def _same(x: torch.Tensor) -> torch.Tensor:
     return x
 

@@ -478,60 +478,3 @@ def test_another_position_encoding_through_the_attention_part(dtype):
     view.slots = torch.tensor([table[p // bs] * bs + p % bs for p in range(T)], dtype=torch.int32, device="cuda")
     other = own.forward(h.cuda().to(dtype), res.cuda().to(dtype), step_context([T], [0]), view).float().cpu()
     assert rel_error(other, ref) > 1e-2
-
-
-def test_full_width_layers_bfloat16_against_float32():
-    """Two layers with the widths of Qwen3-8B (hidden 4096, 32 query and 8 kv heads of 128,
-    intermediate 12288; a smaller vocabulary): the bfloat16 path (tcgen05 GEMM and attention,
-    mma.sync decode attention, CUDA graphs) against the engine's own float32 path, whole, in
-    portions and token by token."""
-    from atomserve_b200.cache import CacheManager
-    from atomserve_b200.config.registry import config_from_dict
-    from atomserve_b200.engine.runner import ModelRunner, Row
-    from atomserve_b200.ops.linear import check_gemm_status
-    from atomserve_b200.weights import random_model
-
-    raw = dict(architectures=["Qwen3ForCausalLM"], vocab_size=8000, hidden_size=4096, intermediate_size=12288,
-               num_hidden_layers=2, num_attention_heads=32, num_key_value_heads=8, head_dim=128, rms_norm_eps=1e-6,
-               rope_theta=1e6, tie_word_embeddings=False, max_position_embeddings=4096)  # fmt: skip
-    _, config = config_from_dict(raw)
-    ids = prompts(raw, [300], seed=5)[0]
-    logits = {}
-    for dtype in ("bfloat16", "float32"):
-        model = random_model(config, seed=3, dtype=dtype, device="cuda")
-        if dtype == "float32":  # the same values the bfloat16 model holds
-            reference = random_model(config, seed=3, dtype="bfloat16", device="cuda")
-            for blk, ref in zip(model.blocks, reference.blocks):
-                blk.mixer.qkv_proj, blk.mixer.o_proj = ref.mixer.qkv_proj.float(), ref.mixer.o_proj.float()
-                gate_up = ref.feed_forward.gate_up_proj.float()
-                if ref.feed_forward.fused:  # rows alternate gate, up there; the float32 path stacks them
-                    pairs = gate_up.view(-1, 2, gate_up.shape[1])
-                    gate_up = torch.cat([pairs[:, 0], pairs[:, 1]]).contiguous()
-                blk.feed_forward.gate_up_proj, blk.feed_forward.down_proj = gate_up, ref.feed_forward.down_proj.float()
-            model.embedding.table, model.head.weight = reference.embedding.table.float(), reference.head.weight.float()
-            del reference
-        runs = {}
-        for name, portions in (("whole", [300]), ("cut", [130, 9, 2, 100, 59]), ("decode", [268] + [1] * 32)):
-            cache = CacheManager(model.cache_requirements(), 16, 64, 4, model.dtype, "cuda")
-            runner = ModelRunner(model, cache)
-            rc = cache.new_request()
-            cache.admit(rc)
-            at, got = 0, []
-            for n in portions:
-                assert cache.reserve(rc, at, n)
-                got.append(runner.step([Row(ids[at : at + n], at, rc, list(range(n)))]).float().cpu())
-                at += n
-            runs[name] = torch.cat(got)
-        logits[dtype] = runs
-        del model
-    check_gemm_status()
-    ref = logits["float32"]["whole"]
-    assert rel_error(logits["float32"]["cut"], ref) < 1e-4 and rel_error(logits["float32"]["decode"][268:], ref[268:]) < 1e-4
-    scale = float(ref.abs().max())
-    for name in ("whole", "cut"):
-        err = float((logits["bfloat16"][name] - ref).abs().max())
-        assert err < 0.03 * scale, f"bfloat16 {name}: {err:.4g} against logits up to {scale:.4g}"
-    err = float((logits["bfloat16"]["decode"][268:] - ref[268:]).abs().max())
-    assert err < 0.03 * scale, f"bfloat16 decode: {err:.4g}"
-    # the cuttings of the bfloat16 path agree with one another much more closely than with float32
-    assert rel_error(logits["bfloat16"]["cut"], logits["bfloat16"]["whole"]) < 0.02

@@ -295,6 +295,118 @@ def test_attention_window_edge(ops, dtype):
                 assert close == seen, (hd, where, n)
 
 
+@pytest.mark.parametrize("prefill_kernel", ["tcgen05", "mma"])
+@pytest.mark.parametrize("window", [100, 108])
+def test_attention_window_edge_head_128(ops, monkeypatch, prefill_kernel, window):
+    """The served head size, through the tensor-core kernels: a single decoded token (the mma
+    decode kernel), the last row of a short portion and of a 200-token portion (the tcgen05
+    kernel, then the mma prefill kernel). With 300 keys the window of 100 begins at key 200, inside
+    a 64-key tile and inside a page; the window of 108 begins at key 192, the first key of a tile
+    and of a page, so the unseen key is the last of the tile and page before."""
+    import atomserve_b200.ops.attention as A
+
+    monkeypatch.setattr(A, "PREFILL_KERNEL", prefill_kernel)
+    H, KV, hd, bs, ctx = 8, 2, 128, 16, 300
+    p = ctx - 1
+    for where, seen in ((p - window + 1, True), (p - window, False)):
+        for n in (1, 12, 200):
+            dev, dense, qs = paged_setup([ctx], [n], H, KV, hd, bs, torch.bfloat16, seed=5, special=(0, where))
+            out = ops.paged_attention(**dev, num_requests=1, max_context=ctx, window=window, scale=hd**-0.5,
+                                      host_q_lens=[n])  # fmt: skip
+            expect = dense[0][1][where].repeat_interleave(H // KV, dim=0)
+            close = torch.allclose(out[-1].float().cpu(), expect, atol=2e-2, rtol=2e-2)
+            assert close == seen, (prefill_kernel, window, where, n)
+            ref = attention_reference(qs, dense, [ctx], [n], window)  # and every other row of the portion
+            assert torch.allclose(out.float().cpu(), ref, atol=2e-2, rtol=2e-2), (prefill_kernel, window, where, n)
+    from atomserve_b200.ops.linear import check_gemm_status
+
+    check_gemm_status()
+
+
+def long_context_setup(ctx_lens, q_lens, H, KV, hd, bs, seed, special=None):
+    """Long requests without per-position Python loops: one pool of random pages on the device,
+    shared by all requests, each request reading it through a shuffled block table of its own (so
+    every request sees other keys in another order). Returns the device inputs and, per request,
+    its keys and values in position order as float32 on the CPU. `special` = (request, position):
+    that key matches the request's last query strongly."""
+    g = torch.Generator().manual_seed(seed)
+    pages = max(-(-c // bs) for c in ctx_lens)
+    pool = pages + 5
+    kc = (torch.randn(pool, KV, bs, hd, generator=g) * 0.5).bfloat16()
+    vc = torch.randn(pool, KV, bs, hd, generator=g).bfloat16()
+    tables = torch.stack([torch.randperm(pool, generator=g)[:pages] for _ in ctx_lens]).to(torch.int32)
+    q = torch.randn(sum(q_lens), H, hd, generator=g).bfloat16()
+    q_start = torch.tensor([0] + list(torch.tensor(q_lens).cumsum(0)), dtype=torch.int32)
+    if special is not None:
+        r, where = special
+        u = torch.randn(hd, generator=g)
+        u = (u / u.norm() * math.sqrt(hd) * 4).bfloat16()
+        kc[tables[r, where // bs], :, where % bs] = u
+        q[int(q_start[r + 1]) - 1] = u
+    dense = []
+    for r, c in enumerate(ctx_lens):
+        mine = tables[r].long()
+        k = kc[mine].permute(0, 2, 1, 3).reshape(-1, KV, hd)[:c].float()
+        v = vc[mine].permute(0, 2, 1, 3).reshape(-1, KV, hd)[:c].float()
+        dense.append((k, v))
+    pos_start = torch.tensor([c - n for c, n in zip(ctx_lens, q_lens)], dtype=torch.int32)
+    dev = dict(q=q.cuda(), k_cache=kc.cuda(), v_cache=vc.cuda(), block_tables=tables.cuda(),
+               req_q_start=q_start.cuda(), req_pos_start=pos_start.cuda())  # fmt: skip
+    return dev, dense, q.float()
+
+
+def long_context_reference(q, dense, ctx_lens, q_lens, window=None):
+    outs, at = [], 0
+    for (k, v), c, n in zip(dense, ctx_lens, q_lens):
+        outs.append(plain.attention_rows(q[at : at + n], k, v, torch.arange(c - n, c), window))
+        at += n
+    return torch.cat(outs)
+
+
+@pytest.mark.parametrize("context", [8192, 32768])
+@pytest.mark.parametrize("batch", [1, 8, 64])
+def test_decode_attention_at_long_contexts(ops, batch, context):
+    """Single decoded tokens over 8k and 32k keys with the key partitions that the planner picks
+    for 1, 8 and 64 requests, against the plain attention; the requests' contexts differ, the
+    longest being `context`, and in request 0 one far key carries nearly all the weight."""
+    from atomserve_b200.ops.attention import plan_decode_partitions
+
+    H, KV, hd, bs = 8, 2, 128, 16
+    ctx_lens = [context - (37 * r) % (context // 2) for r in range(batch)]
+    where = context // 3 + 5
+    dev, dense, q = long_context_setup(ctx_lens, [1] * batch, H, KV, hd, bs, seed=batch, special=(0, where))
+    size, parts = plan_decode_partitions(batch, KV, H // KV, context, 0, hd)
+    assert parts > 1 and size * parts >= context and size % 64 == 0
+    out = ops.paged_attention(**dev, num_requests=batch, max_context=context, window=None, scale=hd**-0.5,
+                              host_q_lens=[1] * batch).float().cpu()  # fmt: skip
+    ref = long_context_reference(q, dense, ctx_lens, [1] * batch)
+    assert torch.allclose(out, ref, atol=2e-2, rtol=2e-2), float((out - ref).abs().max())
+    expect = dense[0][1][where].repeat_interleave(H // KV, dim=0)
+    assert torch.allclose(out[0], expect, atol=2e-2, rtol=2e-2)
+    general = ops.paged_attention(**dev, num_requests=batch, max_context=context, window=None, scale=hd**-0.5,
+                                  host_q_lens=[1] * batch, generic=True).float().cpu()  # fmt: skip
+    assert torch.allclose(general, ref, atol=2e-2, rtol=2e-2)
+
+
+@pytest.mark.parametrize("prefill_kernel", ["tcgen05", "mma"])
+@pytest.mark.parametrize("ctx,n", [(8192, 8192), (8192, 512)])
+def test_prefill_attention_at_long_contexts(ops, monkeypatch, prefill_kernel, ctx, n):
+    """One prompt of 8,192 tokens in one step, and a portion of 512 tokens behind 7,680 cached
+    ones, against the plain attention row by row."""
+    import atomserve_b200.ops.attention as A
+    from atomserve_b200.ops.linear import check_gemm_status
+
+    monkeypatch.setattr(A, "PREFILL_KERNEL", prefill_kernel)
+    H, KV, hd, bs = 4, 1, 128, 16
+    dev, dense, q = long_context_setup([ctx], [n], H, KV, hd, bs, seed=n, special=(0, 100))
+    out = ops.paged_attention(**dev, num_requests=1, max_context=ctx, window=None, scale=hd**-0.5,
+                              host_q_lens=[n]).float().cpu()  # fmt: skip
+    check_gemm_status()
+    ref = long_context_reference(q, dense, [ctx], [n])
+    assert torch.allclose(out, ref, atol=2e-2, rtol=2e-2), float((out - ref).abs().max())
+    assert torch.allclose(out[-1], dense[0][1][100].repeat_interleave(H // KV, dim=0), atol=2e-2, rtol=2e-2)
+
+
 def test_sampling_greedy_and_support(ops):
     logits = torch.tensor([[0.1, 3.0, 0.2, 3.0], [5.0, 1.0, 0.0, -1.0]], device="cuda")
     assert ops.argmax_rows(logits).tolist() == [1, 0]  # lowest id among equals

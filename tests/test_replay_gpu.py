@@ -10,7 +10,7 @@ import pytest
 import torch
 
 import plain_qwen3 as plain
-from helpers import FLOAT32_TOLERANCE, bfloat16_tolerance, checkpoint, prompts, rel_error, write_folder
+from helpers import BF16_REPORT, Oracle, check, checkpoint, mixed_trace, prompts, write_folder
 from tiny_configs import TINY
 
 pytestmark = pytest.mark.gpu
@@ -31,40 +31,10 @@ def models(tmp_path_factory):
     return out
 
 
-class Oracle:
-    """Float32 logits of a whole prompt from the plain implementation; indexing gives the rows
-    asked for, still carrying the prompt's bfloat16 allowance."""
-
-    def __init__(self, w=None, cfg=None, prompt=None, logits=None, allowance=None):
-        if logits is None:
-            logits = plain.forward(w, cfg, prompt)
-            allowance = bfloat16_tolerance(w, cfg, prompt, logits)
-        self.logits, self.allowance = logits, allowance
-
-    def __getitem__(self, rows):
-        return Oracle(logits=self.logits[rows], allowance=self.allowance)
-
-
-BF16_REPORT: list[tuple[str, float]] = []  # (what, error / allowance) of every bfloat16 check
-
-
 def replayer(folder, dtype, bs, max_tokens, graphs=True, **more):
     from atomserve_b200.engine.replay import TraceReplayer
 
     return TraceReplayer(folder, dtype, max_tokens, bs, cuda_graphs=graphs, **more)
-
-
-def check(got, oracle, dtype, what):
-    ref = oracle.logits
-    assert got.shape == ref.shape, f"{what}: shape {tuple(got.shape)} for {tuple(ref.shape)}"
-    if dtype == "float32":
-        err = rel_error(got.cpu(), ref)
-        assert err < FLOAT32_TOLERANCE, f"{what}: relative error {err:.3g}"
-        assert torch.equal(got.cpu().argmax(-1), ref.argmax(-1)), what
-    else:
-        err = float((got.cpu() - ref).abs().max())
-        assert err <= oracle.allowance, f"{what}: error {err:.3g}, allowed {oracle.allowance:.3g}"
-        BF16_REPORT.append((what, err / oracle.allowance))
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
@@ -108,29 +78,6 @@ def test_portions_of_changing_size(models, name, dtype):
             logits = rp.step([dict(id=i, tokens=p[at : at + n], want=list(range(n)))], end=[i] if last else [])
             check(logits, ref[at : at + n], dtype, f"{name} request {i} portion {at}:{at + n}")
             at += n
-
-
-def mixed_trace(ps, rng, max_live=4):
-    """Steps that keep up to `max_live` requests going: each live request brings a portion of
-    random size (prompt phase) or one token (its last 8 tokens), some sit a step out."""
-    steps, live, waiting, done_at = [], {}, list(range(len(ps))), {}
-    while waiting or live:
-        while waiting and len(live) < max_live:
-            live[waiting.pop(0)] = 0
-        entries, end = [], []
-        for i in list(live):
-            if len(live) > 1 and rng.random() < 0.2:
-                continue
-            at, total = live[i], len(ps[i])
-            n = 1 if at >= total - 8 else min(int(rng.integers(2, 20)), total - 8 - at) or 1
-            entries.append(dict(id=i, tokens=ps[i][at : at + n], want=list(range(n)), at=at))
-            live[i] = at + n
-            if at + n == total:
-                end.append(i)
-                del live[i]
-        if entries:
-            steps.append((entries, end))
-    return steps
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
@@ -193,6 +140,41 @@ def test_many_requests_decode_together(models, name, live, dtype):
         for i, ref in refs.items():
             at = lengths[i] + k
             check(logits[i : i + 1], ref[at : at + 1], dtype, f"{name} {live} live, request {i} position {at}")
+
+
+LONG = dict(
+    architectures=["Qwen3ForCausalLM"], vocab_size=300, hidden_size=128, intermediate_size=320,
+    num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=1, head_dim=128,
+    rms_norm_eps=1e-6, rope_theta=1000000.0, tie_word_embeddings=True,
+    max_position_embeddings=16384, hidden_act="silu",
+)  # fmt: skip
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_decoding_across_the_graph_context_buckets(tmp_path, dtype):
+    """One request of 8,210 tokens: decoded token by token from 2,040 to 2,060 and from 8,185 to
+    the end, which takes the decode graphs over the context buckets at 2,048 (then 2,560) and at
+    8,192 (then 9,216), each with another plan of key partitions; between them a portion of
+    6,125 tokens behind 2,060 cached ones. Every wanted row against the plain implementation."""
+    w = checkpoint(LONG, seed=5)
+    folder = write_folder(LONG, w, tmp_path / "long")
+    p = prompts(LONG, [8210], seed=1)[0]
+    ref = Oracle(w, LONG, p)
+    rp = replayer(folder, dtype, 16, 8256)
+    assert rp.runner.use_graphs
+
+    def run(at, n, want):
+        logits = rp.step([dict(id="x", tokens=p[at : at + n], want=want)], end=[])
+        check(logits, ref[[at + j for j in want]], dtype, f"long request, {n} tokens at {at}")
+
+    run(0, 2040, [0, 1000, 2039])
+    for at in range(2040, 2060):
+        run(at, 1, [0])
+    run(2060, 6125, [0, 5, 3000, 6124])
+    for at in range(8185, 8210):
+        run(at, 1, [0])
+    buckets = sorted({key[-1] for key in rp.runner._graphs._entries})
+    assert buckets == [2048, 2560, 8192, 9216], buckets
 
 
 def test_window_pages_are_given_back(models):

@@ -93,3 +93,27 @@ def test_random_model_folder_is_seeded_and_loadable(tmp_path):
     from atomserve_b200.weights.loader import read_eos_token_ids
 
     assert read_eos_token_ids(a) == frozenset({3}) and read_eos_token_ids(b) == frozenset()
+
+
+def test_a_tensor_held_by_two_files_is_an_error_and_an_index_decides_what_belongs(tmp_path):
+    """A stale shard left in the folder must not change the weights silently: a name in two files
+    is reported with the rest; where the folder has an index, only the files it names count."""
+    w = plain.random_checkpoint(TINY_A, 2)
+    names = sorted(w)
+    (tmp_path / "config.json").write_text(json.dumps(TINY_A))
+    save_file({n: w[n] for n in names[::2]}, str(tmp_path / "model-00001-of-00002.safetensors"))
+    save_file({n: w[n] for n in names[1::2]}, str(tmp_path / "model-00002-of-00002.safetensors"))
+    stale = {names[0]: w[names[0]] + 1, names[1]: w[names[1]] + 1}
+    save_file(stale, str(tmp_path / "stale.safetensors"))
+    with pytest.raises(WeightsError) as e:
+        load_model(tmp_path, "float32", "cpu")
+    text = str(e.value)
+    assert "more than one file (2)" in text and f"{names[0]} (in model-00001-of-00002.safetensors, stale.safetensors)" in text
+    index = {"weight_map": {n: f"model-0000{1 + i % 2}-of-00002.safetensors" for i, n in enumerate(names)}}
+    (tmp_path / "model.safetensors.index.json").write_text(json.dumps(index))
+    _, _, model = load_model(tmp_path, "float32", "cpu")
+    assert torch.equal(model.final_norm.gain, w["model.norm.weight"])
+    index["weight_map"]["x"] = "gone.safetensors"
+    (tmp_path / "model.safetensors.index.json").write_text(json.dumps(index))
+    with pytest.raises(FileNotFoundError, match="gone.safetensors"):
+        load_model(tmp_path, "float32", "cpu")

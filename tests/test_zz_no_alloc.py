@@ -5,9 +5,12 @@ GPU's memory away at start-up, or it cannot afford cudaMalloc's synchronisation,
 foreign runtime with only raw pointers to offer. For them the library exports
 `asb_paged_attention_static_scratch`, which keeps the split-key partial results in an array of
 its own (atomserve_b200/csrc/attention_noalloc.h). This test calls it twice in a row on
-different inputs and compares each result with the ordinary entry point's, which takes its
-scratch from the caller. The file is named to be collected last, so that a run which stops at
-the first failure has run every other test before it.
+different inputs and holds each result to two things: the ordinary entry point's result, which
+takes its scratch from the caller and must agree bit for bit (same kernels, same order of
+additions), and the plain attention of tests/plain_qwen3.py on the gathered keys and values.
+A call that needs no partitions must go through however many tokens it brings. The file is named
+to be collected last, so that a run which stops at the first failure has run every other test
+before it.
 """
 
 import ctypes
@@ -15,7 +18,23 @@ import ctypes
 import pytest
 import torch
 
+import plain_qwen3 as plain
+
 pytestmark = pytest.mark.gpu
+
+
+def plain_decode_attention(q, kc, vc, tables, ctx_lens, bs):
+    """Each request's last-position output by the plain implementation: its keys and values
+    gathered from the pages in position order, the query placed at the last position."""
+    outs = []
+    for r, n in enumerate(ctx_lens):
+        pages = tables[r, : -(-n // bs)].long().cpu()
+        k = kc.float().cpu()[pages].permute(0, 2, 1, 3).reshape(-1, kc.shape[1], kc.shape[3])[:n]
+        v = vc.float().cpu()[pages].permute(0, 2, 1, 3).reshape(-1, vc.shape[1], vc.shape[3])[:n]
+        qq = torch.zeros(n, q.shape[1], q.shape[2])
+        qq[-1] = q[r].float().cpu()
+        outs.append(plain.attention(qq, k, v)[-1])
+    return torch.stack(outs)
 
 
 def entry_point():
@@ -64,8 +83,38 @@ def test_static_scratch_entry_point_matches_the_allocating_one(dtype):
                 hd**-0.5, dtype_code(q), torch.cuda.current_stream().cuda_stream)  # fmt: skip
         assert rc == 0, handle.asb_last_error().decode()
         torch.cuda.synchronize()
+        assert torch.equal(out, expect)  # the same kernels on other scratch: the same bits
         tol = dict(atol=2e-5, rtol=1e-4) if dtype == torch.float32 else dict(atol=2e-2, rtol=2e-2)
-        assert torch.allclose(out.float(), expect.float(), **tol)
+        oracle = plain_decode_attention(q, kc, vc, tables, ctx_lens, bs)
+        assert torch.allclose(out.float().cpu(), oracle, **tol)
+
+
+def test_static_scratch_is_not_asked_of_a_call_without_partitions():
+    """2,048 tokens of 32 heads would need 8.5 Mi floats if they were partitioned; with one
+    partition the kernel writes its output directly, so the call must pass."""
+    from atomserve_b200 import ops
+    from atomserve_b200.ops.library import dtype_code
+
+    handle, fn = entry_point()
+    H, KV, hd, bs, T = 32, 8, 64, 16, 2048
+    g = torch.Generator().manual_seed(3)
+    pages = T // bs
+    tables = torch.randperm(pages + 3, generator=g)[:pages].reshape(1, pages).to(torch.int32).cuda()
+    kc = torch.randn(pages + 3, KV, bs, hd, generator=g).cuda()
+    vc = torch.randn(pages + 3, KV, bs, hd, generator=g).cuda()
+    q = torch.randn(T, H, hd, generator=g).cuda()
+    q_start = torch.tensor([0, T], dtype=torch.int32).cuda()
+    pos_start = torch.zeros(1, dtype=torch.int32).cuda()
+    assert T * H * (hd + 2) > handle.asb_static_scratch_floats()
+    expect = ops.paged_attention(q, kc, vc, tables, q_start, pos_start, num_requests=1, max_context=T, window=None,
+                                 scale=hd**-0.5, partitions=(1 << 30, 1), generic=True)  # fmt: skip
+    out = torch.empty_like(q)
+    rc = fn(out.data_ptr(), q.data_ptr(), kc.data_ptr(), vc.data_ptr(), tables.data_ptr(), q_start.data_ptr(),
+            pos_start.data_ptr(), T, 1, H, KV, hd, bs, pages, 0, 1 << 30, 1, hd**-0.5, dtype_code(q),
+            torch.cuda.current_stream().cuda_stream)  # fmt: skip
+    assert rc == 0, handle.asb_last_error().decode()
+    torch.cuda.synchronize()
+    assert torch.equal(out, expect)
 
 
 def test_static_scratch_refuses_what_does_not_fit():
@@ -80,3 +129,8 @@ def test_static_scratch_refuses_what_does_not_fit():
     assert rc != 0
     message = handle.asb_last_error().decode()
     assert "exceed the built-in scratch" in message and str(capacity) in message
+    # numbers whose product would wrap 64 bits are refused by range, not by a wrapped product
+    rc = fn(None, q.data_ptr(), kc.data_ptr(), vc.data_ptr(), tables.data_ptr(), q_start.data_ptr(),
+            pos_start.data_ptr(), 2**31 - 1, 1, 2**31 - 1, 2, hd, 16, tables.shape[1], 0, 64, 2**31 - 1, 1.0, 0,
+            torch.cuda.current_stream().cuda_stream)  # fmt: skip
+    assert rc != 0 and "out of range" in handle.asb_last_error().decode()
