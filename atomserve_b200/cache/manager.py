@@ -2,9 +2,9 @@
 group, and per-request state slots.
 
 Entries of the model's run order that own a cache are sorted into groups by what they need:
-(kv heads, head size, window). Each group has its own pool of pages
-`[entries, num_blocks, kv_heads, block_size, head_dim]` for keys and for values, its own
-allocator and, per request, its own block table. Position p of a request lives in page
+the tensors a page holds (for attention: keys and values of kv heads x head size) and the
+window. Each group has, per tensor, its own pool `[entries, num_blocks, heads, block_size,
+width]`, and its own allocator and, per request, its own block table. Position p of a request lives in page
 `table[p // block_size]` at offset `p % block_size`; the slot written is
 `page * block_size + offset` (atomserve/kv_cache.py:9-14). Pools start zeroed so that no read
 can meet a NaN (atomserve/kv_cache.py:112-118).
@@ -27,7 +27,7 @@ import torch
 
 from atomserve_b200.cache.block_allocator import BlockAllocator, block_hash, blocks_for_tokens
 from atomserve_b200.cache.state_slots import StateSlots
-from atomserve_b200.parts.base import CacheView, KVCacheSpec, StateSpec
+from atomserve_b200.parts.base import CacheView, PageSpec, StateSpec
 
 
 @dataclass
@@ -47,11 +47,19 @@ class RequestCache:
 
 @dataclass
 class CacheGroup:
-    spec: KVCacheSpec
+    spec: PageSpec
     entries: list[int]  # run-order indices whose pages live here, in pool order
     allocator: BlockAllocator
-    k: torch.Tensor | None = None  # [len(entries), num_blocks, KV, block_size, hd]
-    v: torch.Tensor | None = None
+    # per tensor of the spec: [len(entries), num_blocks, heads, block_size, width]
+    pools: dict[str, torch.Tensor] = field(default_factory=dict)
+
+    @property
+    def k(self) -> torch.Tensor | None:
+        return self.pools.get("k")
+
+    @property
+    def v(self) -> torch.Tensor | None:
+        return self.pools.get("v")
 
     @property
     def window(self) -> int | None:
@@ -61,7 +69,7 @@ class CacheGroup:
 class CacheManager:
     def __init__(
         self,
-        requirements: list[tuple[KVCacheSpec | None, list[StateSpec]]],
+        requirements: list[tuple[PageSpec | None, list[StateSpec]]],
         block_size: int,
         num_blocks: int,
         num_state_slots: int,
@@ -76,7 +84,7 @@ class CacheManager:
         self.entry_group: dict[int, tuple[int, int]] = {}  # run-order index -> (group, index in group)
         self.entry_state: dict[int, dict[str, torch.Tensor]] = {}
         self.state = StateSlots(num_state_slots, self.device or "cpu")
-        by_key: dict[KVCacheSpec, int] = {}
+        by_key: dict[PageSpec, int] = {}
         for i, (kv, states) in enumerate(requirements):
             if kv is not None:
                 if kv not in by_key:
@@ -92,17 +100,17 @@ class CacheManager:
         self._windowed = any(g.window is not None for g in self.groups)  # only windows release pages early
         if self.device is not None:
             for g in self.groups:
-                shape = (len(g.entries), num_blocks, g.spec.num_kv_heads, block_size, g.spec.head_dim)
-                g.k = torch.zeros(shape, dtype=dtype, device=self.device)
-                g.v = torch.zeros(shape, dtype=dtype, device=self.device)
+                for t in g.spec.tensors:
+                    shape = (len(g.entries), num_blocks, t.heads, block_size, t.width)
+                    g.pools[t.name] = torch.zeros(shape, dtype=dtype, device=self.device)
 
     # ---- sizes --------------------------------------------------------------------------------
 
     @staticmethod
-    def bytes_per_block(requirements: list[tuple[KVCacheSpec | None, list[StateSpec]]], block_size: int, dtype: torch.dtype) -> int:
-        """Memory that one page id costs across all groups, keys and values
+    def bytes_per_block(requirements: list[tuple[PageSpec | None, list[StateSpec]]], block_size: int, dtype: torch.dtype) -> int:
+        """Memory that one page id costs across all entries and the tensors of their pages
         (atomserve/kv_cache.py:129-135)."""
-        per_token = sum(2 * kv.num_kv_heads * kv.head_dim for kv, _ in requirements if kv is not None)
+        per_token = sum(spec.values_per_token for spec, _ in requirements if spec is not None)
         return per_token * block_size * dtype.itemsize
 
     @property
@@ -220,7 +228,7 @@ class CacheManager:
         view = CacheView(block_size=self.block_size)
         if entry in self.entry_group:
             g, j = self.entry_group[entry]
-            view.k, view.v = self.groups[g].k[j], self.groups[g].v[j]
+            view.pages = {name: pool[j] for name, pool in self.groups[g].pools.items()}
         if entry in self.entry_state:
             view.state = self.entry_state[entry]
         if entry not in self.entry_group and entry not in self.entry_state:

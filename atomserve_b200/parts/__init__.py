@@ -2,9 +2,12 @@ from atomserve_b200.parts.base import (
     Block,
     CacheView,
     FeedForward,
+    FusedRotary,
     KVCacheSpec,
     Mixer,
     Norm,
+    PageSpec,
+    PageTensor,
     Part,
     PositionEncoding,
     StateSpec,
@@ -17,7 +20,7 @@ from atomserve_b200.parts.model import DecoderModel, build_model
 from atomserve_b200.parts.spec import LayerCall, LayerSpec, ModelSpec, PartSpec, TensorSpec
 
 __all__ = [
-    "Block", "CacheView", "DecoderModel", "FeedForward", "KVCacheSpec", "LayerCall", "LayerSpec",
-    "Mixer", "ModelSpec", "Norm", "Part", "PartSpec", "PositionEncoding", "StateSpec",
+    "Block", "CacheView", "DecoderModel", "FeedForward", "FusedRotary", "KVCacheSpec", "LayerCall", "LayerSpec",
+    "Mixer", "ModelSpec", "Norm", "PageSpec", "PageTensor", "Part", "PartSpec", "PositionEncoding", "StateSpec",
     "StepContext", "TensorSpec", "build_block", "build_model", "build_part", "register_part",
 ]  # fmt: skip

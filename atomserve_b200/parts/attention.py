@@ -7,7 +7,7 @@ from __future__ import annotations
 import torch
 
 from atomserve_b200 import ops
-from atomserve_b200.parts.base import CacheView, KVCacheSpec, Mixer, Norm, StepContext, build_part, register_part
+from atomserve_b200.parts.base import CacheView, KVCacheSpec, Mixer, Norm, PageSpec, StepContext, build_part, register_part
 from atomserve_b200.parts.spec import PartSpec, TensorSpec
 
 
@@ -34,7 +34,7 @@ class GQAttention(Mixer):
         self.position = build_part("position", position, hidden_size) if position else None
         self.qkv_proj = self.o_proj = self.q_gain = self.k_gain = None
 
-    def cache_spec(self) -> KVCacheSpec:
+    def cache_spec(self) -> PageSpec:
         return KVCacheSpec(self.num_kv_heads, self.head_dim, self.window)
 
     def tensor_specs(self) -> list[TensorSpec]:
@@ -77,28 +77,57 @@ class GQAttention(Mixer):
     def attend(self, h: torch.Tensor, ctx: StepContext, cache: CacheView | None, write_cache: bool) -> torch.Tensor:
         """The heads' outputs side by side, [T, H * hd], before the output projection."""
         H, KV, hd = self.num_heads, self.num_kv_heads, self.head_dim
-        pos = self.position
-        # reading another entry's keys and values, only queries are projected
-        weight, kv_heads = (self.qkv_proj, KV) if write_cache else (self.qkv_proj[: H * hd], 0)
-        qkv = None
-        if ops.qk_norm_rope_store_takes_partial(hd, pos.rotary_dim if pos else None):
-            # with few tokens the product stays as the GEMM's partial sums and the next kernel adds them up
-            qkv = ops.linear_partial(h, weight)
-        if qkv is None:
-            qkv = ops.linear(h, weight)
-        q = ops.qk_norm_rope_store(
-            qkv, H, kv_heads, hd, ctx.positions,
-            q_gain=self.q_gain, k_gain=self.k_gain, eps=self.qk_norm_eps or 0.0,
-            inv_freq=pos.inv_freq if pos else None, rotary_dim=pos.rotary_dim if pos else 0,
-            slots=cache.slots if write_cache else None,
-            k_cache=cache.k if write_cache else None, v_cache=cache.v if write_cache else None,
-        )  # fmt: skip
+        # the position encoding says how it is applied: by the fused kernel below (a rotation by
+        # position x frequency), or by its own `encode` on the normalised queries and keys
+        rotary = self.position.fused_rotary() if self.position is not None else None
+        if self.position is not None and rotary is None:
+            q = self._project_encode_store(h, ctx, cache, write_cache)
+        else:
+            # reading another entry's keys and values, only queries are projected
+            weight, kv_heads = (self.qkv_proj, KV) if write_cache else (self.qkv_proj[: H * hd], 0)
+            qkv = None
+            if ops.qk_norm_rope_store_takes_partial(hd, rotary.rotary_dim if rotary else None):
+                # with few tokens the product stays as the GEMM's partial sums and the next kernel adds them up
+                qkv = ops.linear_partial(h, weight)
+            if qkv is None:
+                qkv = ops.linear(h, weight)
+            q = ops.qk_norm_rope_store(
+                qkv, H, kv_heads, hd, ctx.positions,
+                q_gain=self.q_gain, k_gain=self.k_gain, eps=self.qk_norm_eps or 0.0,
+                inv_freq=rotary.inv_freq if rotary else None, rotary_dim=rotary.rotary_dim if rotary else 0,
+                slots=cache.slots if write_cache else None,
+                k_cache=cache.k if write_cache else None, v_cache=cache.v if write_cache else None,
+            )  # fmt: skip
         out = ops.paged_attention(
             q, cache.k, cache.v, cache.block_tables, ctx.req_q_start, ctx.req_pos_start,
             num_requests=ctx.num_requests, max_context=ctx.max_context, window=self.window,
             scale=self.scale, host_q_lens=ctx.host_q_lens or None,
         )  # fmt: skip
         return out.view(-1, H * hd)
+
+
+    def _project_encode_store(self, h: torch.Tensor, ctx: StepContext, cache: CacheView | None, write_cache: bool) -> torch.Tensor:
+        """The path for an encoding that is no fused rotation: the same kernel normalises q and k
+        without turning or storing them, the encoding's `encode` works the positions in, and a
+        second pass of the kernel (no norm, no rotation) writes keys and values to their pages."""
+        H, KV, hd = self.num_heads, self.num_kv_heads, self.head_dim
+        T = h.shape[0]
+        kv_heads = KV if write_cache else 0
+        qkv = ops.linear(h, self.qkv_proj if write_cache else self.qkv_proj[: H * hd])
+        normed = qkv
+        if self.qk_norm_eps is not None:
+            heads = qkv.view(T, H + 2 * kv_heads, hd)
+            q = ops.rms_norm(heads[:, :H].reshape(T * H, hd), self.q_gain, self.qk_norm_eps).view(T, H, hd)
+            k = ops.rms_norm(heads[:, H : H + kv_heads].reshape(T * kv_heads, hd), self.k_gain, self.qk_norm_eps).view(T, kv_heads, hd) if kv_heads else None
+        else:
+            heads = qkv.view(T, H + 2 * kv_heads, hd)
+            q, k = heads[:, :H].contiguous(), (heads[:, H : H + kv_heads].contiguous() if kv_heads else None)
+        q, k = self.position.encode(q, k, ctx)
+        if not write_cache:
+            return q.contiguous()
+        normed = torch.cat([q.reshape(T, H * hd), k.reshape(T, KV * hd), qkv[:, (H + KV) * hd :]], dim=1)
+        return ops.qk_norm_rope_store(normed, H, KV, hd, ctx.positions, q_gain=None, k_gain=None, eps=0.0, inv_freq=None,
+                                      rotary_dim=0, slots=cache.slots, k_cache=cache.k, v_cache=cache.v)  # fmt: skip
 
 
 register_part("mixer", "gqa_attention", GQAttention)

@@ -6,10 +6,10 @@ checkpoint tensors it needs, receives them once, and computes on the flat batch.
 knows which model it is in or which layer it is.
 
   Norm            forward(x, rows=None) -> same width
-  PositionEncoding  what a mixer needs to encode positions (for rotary: inverse frequencies)
+  PositionEncoding  how positions enter a mixer: fused_rotary() or encode(q, k, ctx)
   Mixer           forward(h, residual, ctx, cache, write_cache) -> residual + mix(h);
-                  cache_spec() says what it keeps between steps (pages of keys and values,
-                  fixed-size state, or nothing)
+                  cache_spec() says what it keeps in pages between steps (keys and values, or
+                  any other tensors per token), state_specs() what it keeps at fixed size
   FeedForward     forward(h, residual, ctx) -> residual + ff(h)
   Block           arranges a mixer and a feed-forward with their norms around the residual
 """
@@ -28,13 +28,33 @@ from atomserve_b200.parts.spec import PartSpec, TensorSpec
 
 
 @dataclass(frozen=True)
-class KVCacheSpec:
-    """Pages of keys and values: per token `num_kv_heads * head_dim` of each. `window`: only the
-    last `window` positions are ever read, so older pages can be given back early."""
+class PageTensor:
+    """One of the tensors a cache page holds: per token, `heads` vectors of `width` values. The
+    pool of it is [entries, num_blocks, heads, block_size, width] in the cache dtype."""
 
-    num_kv_heads: int
-    head_dim: int
+    name: str
+    heads: int
+    width: int
+
+
+@dataclass(frozen=True)
+class PageSpec:
+    """What a mixer keeps in pages: the tensors each page holds, and `window`: only the last
+    `window` positions are ever read, so older pages can be given back early. Entries of the run
+    order with equal specs share a group of pools, an allocator and the requests' block tables."""
+
+    tensors: tuple[PageTensor, ...]
     window: int | None = None
+
+    @property
+    def values_per_token(self) -> int:
+        return sum(t.heads * t.width for t in self.tensors)
+
+
+def KVCacheSpec(num_kv_heads: int, head_dim: int, window: int | None = None) -> PageSpec:
+    """The usual pages: keys and values, `num_kv_heads * head_dim` of each per token, as tensors
+    "k" and "v"."""
+    return PageSpec((PageTensor("k", num_kv_heads, head_dim), PageTensor("v", num_kv_heads, head_dim)), window)
 
 
 @dataclass(frozen=True)
@@ -46,21 +66,41 @@ class StateSpec:
     dtype: torch.dtype = torch.float32
 
 
-@dataclass
 class CacheView:
     """What one entry of the run order sees of the cache during a step.
 
-    For paged keys/values: `k`, `v` are [num_blocks, KV, block_size, head_dim]; `slots` [T] int32
-    says where each new token is written; `block_tables` [R, W] int32 where each request's
-    positions live. For state: `state[name]` is [num_slots, *shape], indexed by ctx.state_slots.
+    `pages[name]` is [num_blocks, heads, block_size, width] for each tensor of the entry's
+    PageSpec (`k` and `v` are shorthands for the pages of those names); `slots` [T] int32 says
+    where each new token is written; `block_tables` [R, W] int32 where each request's positions
+    live. For state: `state[name]` is [num_slots, *shape], indexed by ctx.state_slots.
     """
 
-    k: torch.Tensor | None = None
-    v: torch.Tensor | None = None
-    slots: torch.Tensor | None = None
-    block_tables: torch.Tensor | None = None
-    block_size: int = 0
-    state: dict[str, torch.Tensor] = field(default_factory=dict)
+    def __init__(self, k: torch.Tensor | None = None, v: torch.Tensor | None = None, slots: torch.Tensor | None = None,
+                 block_tables: torch.Tensor | None = None, block_size: int = 0,
+                 state: dict[str, torch.Tensor] | None = None, pages: dict[str, torch.Tensor] | None = None):  # fmt: skip
+        self.pages: dict[str, torch.Tensor] = dict(pages or {})
+        if k is not None:
+            self.pages["k"] = k
+        if v is not None:
+            self.pages["v"] = v
+        self.slots, self.block_tables, self.block_size = slots, block_tables, block_size
+        self.state: dict[str, torch.Tensor] = state if state is not None else {}
+
+    @property
+    def k(self) -> torch.Tensor | None:
+        return self.pages.get("k")
+
+    @k.setter
+    def k(self, pages: torch.Tensor) -> None:
+        self.pages["k"] = pages
+
+    @property
+    def v(self) -> torch.Tensor | None:
+        return self.pages.get("v")
+
+    @v.setter
+    def v(self, pages: torch.Tensor) -> None:
+        self.pages["v"] = pages
 
 
 # ---- the step's batch as parts see it -------------------------------------------------------
@@ -109,15 +149,47 @@ class Norm(Part):
     # hands it to the norm that follows, which may then run both in one kernel.
 
 
+@dataclass(frozen=True)
+class FusedRotary:
+    """An encoding that a mixer's fused kernel can apply by itself: each head's first
+    `rotary_dim` dimensions are turned, pair (i, i + rotary_dim / 2) by the angle
+    position * inv_freq[i] (`inv_freq`: float32 [rotary_dim / 2] on the device)."""
+
+    inv_freq: torch.Tensor
+    rotary_dim: int
+
+
 class PositionEncoding(Part):
-    """How positions enter a mixer. `prepare(device)` builds its tables once."""
+    """How positions enter a mixer. The encoding owns how it is applied; a mixer asks it, in
+    this order:
+
+      fused_rotary()      a `FusedRotary` if the encoding is a rotation by position * frequency:
+                          the mixer's fused kernel then applies it on the way to the cache;
+      encode(q, k, ctx)   otherwise: the queries [T, H, hd] and keys [T, KV, hd] (after their
+                          norm, before the keys are stored) with the positions of the step's
+                          tokens worked in, by whatever rule. The default changes nothing (an
+                          encoding that acts elsewhere, or none).
+
+    `prepare(device)` builds its tables once."""
 
     def prepare(self, device: torch.device) -> None:
         pass
 
+    def fused_rotary(self) -> FusedRotary | None:
+        # encodings written against the older convention carry the two fields themselves
+        inv_freq, rotary_dim = getattr(self, "inv_freq", None), getattr(self, "rotary_dim", None)
+        if inv_freq is not None and rotary_dim:
+            return FusedRotary(inv_freq, rotary_dim)
+        return None
+
+    def encode(self, q: torch.Tensor, k: torch.Tensor | None, ctx: "StepContext") -> tuple[torch.Tensor, torch.Tensor | None]:
+        return q, k
+
 
 class Mixer(Part):
-    def cache_spec(self) -> KVCacheSpec | None:
+    def cache_spec(self) -> PageSpec | None:
+        """The pages this mixer keeps (`KVCacheSpec(...)` for keys and values; any other list of
+        tensors as a `PageSpec`), or None."""
         return None
 
     def state_specs(self) -> list[StateSpec]:

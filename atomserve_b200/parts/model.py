@@ -7,7 +7,7 @@ import inspect
 
 import torch
 
-from atomserve_b200.parts.base import Block, CacheView, KVCacheSpec, StateSpec, StepContext, build_block, build_part
+from atomserve_b200.parts.base import Block, CacheView, PageSpec, StateSpec, StepContext, build_block, build_part
 from atomserve_b200.parts.spec import ModelSpec, TensorSpec
 
 
@@ -59,7 +59,7 @@ class DecoderModel:
         self.dtype = self.embedding.table.dtype
         self.device = self.embedding.table.device
 
-    def cache_requirements(self) -> list[tuple[KVCacheSpec | None, list[StateSpec]]]:
+    def cache_requirements(self) -> list[tuple[PageSpec | None, list[StateSpec]]]:
         """For each entry of the run order: the pages and state it owns (none if it reads
         another entry's)."""
         out = []

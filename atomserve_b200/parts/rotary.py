@@ -7,7 +7,7 @@ from __future__ import annotations
 import torch
 
 from atomserve_b200 import ops
-from atomserve_b200.parts.base import PositionEncoding, register_part
+from atomserve_b200.parts.base import FusedRotary, PositionEncoding, register_part
 
 
 class Rotary(PositionEncoding):
@@ -22,6 +22,9 @@ class Rotary(PositionEncoding):
     def prepare(self, device: torch.device) -> None:
         exponents = torch.arange(0, self.rotary_dim, 2, dtype=torch.float32) / self.rotary_dim
         self.inv_freq = (1.0 / (self.theta**exponents)).to(device)
+
+    def fused_rotary(self) -> FusedRotary:
+        return FusedRotary(self.inv_freq, self.rotary_dim)
 
     def apply(self, x: torch.Tensor, positions: torch.Tensor) -> torch.Tensor:
         """Rotate x [T, heads, head_dim] by its tokens' positions (the encoding on its own)."""

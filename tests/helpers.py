@@ -110,3 +110,16 @@ def mixed_trace(ps, rng, max_live=4, largest=20):
         if entries:
             steps.append((entries, end))
     return steps
+
+
+def assert_near_best_tokens(w: dict, cfg: dict, prompt: list[int], out: list[int], what: str = "") -> None:
+    """Judge greedy tokens of a bfloat16 engine: bfloat16 may break near-ties differently, so
+    each chosen token is held against the oracle run on the engine's own sequence: its logit must
+    lie within twice the bfloat16 allowance of the best one at that position."""
+    full = list(prompt) + list(out)
+    ref = plain.forward(w, cfg, full)
+    allowance = bfloat16_tolerance(w, cfg, full, ref)
+    for i, token in enumerate(out):
+        row = ref[len(prompt) + i - 1]
+        gap = float(row.max() - row[token])
+        assert gap <= 2 * allowance, f"{what} token {i} ({token}) lies {gap:.3g} below the best, allowed {2 * allowance:.3g}"

@@ -251,3 +251,63 @@ def test_status_words_name_what_went_wrong_and_clear():
     assert status.problem() is None and status.problem_on_host() is None
     status.pipeline.fill_(14)
     assert "prefill attention" in status.problem() and status.words.tolist() == [0, 0, 0, 0]
+
+
+def test_a_mixer_whose_pages_hold_one_tensor():
+    """The cache manager builds its pools from the tensors a mixer's PageSpec lists: here one
+    narrow latent per token instead of keys and values, beside an ordinary attention layer (two
+    groups, two kinds of pages). Whole, cut into portions and against the mixer's longhand."""
+    from atomserve_b200.parts import LayerCall, LayerSpec, ModelSpec, PartSpec, build_model
+
+    cfg, bs = TINY["a"]
+    d, eps, hd, rank = cfg["hidden_size"], cfg["rms_norm_eps"], cfg["head_dim"], 12
+    w = checkpoint(cfg, seed=14, bf16_exact=False)
+    g = torch.Generator().manual_seed(4)
+    for n, shape in (("down", (rank, d)), ("query", (rank, d)), ("up", (d, rank))):
+        w[f"model.layers.1.latent.{n}.weight"] = torch.randn(shape, generator=g) * 0.3
+    attn = PartSpec("torch_attention", dict(num_heads=4, num_kv_heads=2, head_dim=hd, eps=eps, theta=cfg["rope_theta"]),
+                    "model.layers.0.self_attn.")  # fmt: skip
+    layers = []
+    for i, mixer in enumerate([attn, PartSpec("latent_mixer", dict(rank=rank), "model.layers.1.latent.")]):
+        p = f"model.layers.{i}."
+        layers.append(LayerSpec("pre_norm", mixer, PartSpec("torch_swiglu", dict(intermediate_size=cfg["intermediate_size"]), p + "mlp."),
+                                PartSpec("torch_rms_norm", dict(eps=eps), p + "input_layernorm."),
+                                PartSpec("torch_rms_norm", dict(eps=eps), p + "post_attention_layernorm.")))  # fmt: skip
+    spec = ModelSpec(hidden_size=d, vocab_size=cfg["vocab_size"], max_positions=512,
+                     embedding=PartSpec("torch_embedding", dict(vocab_size=cfg["vocab_size"]), "model.embed_tokens."),
+                     layers=tuple(layers), schedule=(LayerCall(0), LayerCall(1)),
+                     final_norm=PartSpec("torch_rms_norm", dict(eps=eps), "model.norm."),
+                     head=PartSpec("torch_head", dict(vocab_size=cfg["vocab_size"], tied=True), "lm_head."))  # fmt: skip
+    model = build_model(spec)
+    wanted = {s.name for s in model.tensor_specs()}
+    model.load({k: v for k, v in w.items() if k in wanted})
+    requirements = model.cache_requirements()
+    cache = CacheManager(requirements, bs, 16, 4, torch.float32, "cpu")
+    assert [sorted(g.pools) for g in cache.groups] == [["k", "v"], ["latent"]]
+    assert cache.groups[1].pools["latent"].shape == (1, 16, 1, bs, rank)
+    assert CacheManager.bytes_per_block(requirements, bs, torch.float32) == (2 * 2 * hd + rank) * bs * 4
+    assert not cache.supports_prefix_caching  # two groups
+    ids = prompts(cfg, [37], seed=2)[0]
+    results = []
+    for portions in ([37], [5, 2, 13, 1, 1, 15]):
+        cache = CacheManager(requirements, bs, 16, 4, torch.float32, "cpu")
+        runner = ModelRunner(model, cache)
+        rc = cache.new_request()
+        cache.admit(rc)
+        at, got = 0, []
+        for n in portions:
+            assert cache.reserve(rc, at, n)
+            got.append(runner.step([Row(ids[at : at + n], at, rc, list(range(n)))]))
+            at += n
+        results.append(torch.cat(got))
+        cache.free(rc)
+        assert all(g.allocator.num_free == 16 for g in cache.groups)
+    assert torch.allclose(results[0], results[1], atol=1e-5)
+    mixer = model.blocks[1].mixer
+    h = torch.randn(11, d, generator=g)
+    view = cache.entry_view(1)
+    view.block_tables, view.slots = torch.tensor([[3]], dtype=torch.int32), torch.arange(3 * bs, 3 * bs + 11, dtype=torch.int32)
+    ctx = type("Ctx", (), dict(host_q_lens=[11], host_pos_start=[0]))()
+    y = mixer.forward(h, torch.zeros_like(h), ctx, view)
+    ref = toy_parts.latent_mixer_reference(h, *(w[f"model.layers.1.latent.{n}.weight"] for n in ("down", "query", "up")))
+    assert torch.allclose(y.double(), ref, atol=1e-5)

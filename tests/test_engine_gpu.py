@@ -10,7 +10,7 @@ import torch
 
 import plain_qwen3 as plain
 import toy_parts
-from helpers import FLOAT32_TOLERANCE, bfloat16_tolerance, checkpoint, prompts, rel_error, write_folder
+from helpers import FLOAT32_TOLERANCE, assert_near_best_tokens, checkpoint, prompts, rel_error, write_folder
 from tiny_configs import TINY
 
 pytestmark = pytest.mark.gpu
@@ -71,12 +71,73 @@ def test_greedy_generation_bfloat16_picks_near_best_tokens(folders, name):
     outs = engine_for(folder, "bfloat16", bs).generate(ps, SamplingParams(max_tokens=8, **GREEDY))
     for p, out in zip(ps, outs):
         assert len(out) == 8
-        full = p + out
-        ref = plain.forward(w, cfg, full)
-        allowance = bfloat16_tolerance(w, cfg, full, ref)
-        for i, token in enumerate(out):
-            row = ref[len(p) + i - 1]
-            assert float(row.max() - row[token]) <= 2 * allowance
+        assert_near_best_tokens(w, cfg, p, out, f"{name} batched")
+    # in portions under a small budget, and with so few pages that requests are preempted
+    chunked = engine_for(folder, "bfloat16", bs, max_num_batched_tokens=8, max_num_seqs=4)
+    for p, out in zip(ps, chunked.generate(ps, SamplingParams(max_tokens=8, **GREEDY))):
+        assert len(out) == 8
+        assert_near_best_tokens(w, cfg, p, out, f"{name} chunked")
+    assert chunked.num_steps > 8 + 3
+    short = engine_for(folder, "bfloat16", bs, num_blocks=7, max_model_len=7 * bs, enable_prefix_caching=False)
+    n = bs + 8
+    ps2 = prompts(cfg, [bs + 3, bs + 5, 2 * bs - 1], seed=5)
+    for p, out in zip(ps2, short.generate(ps2, SamplingParams(max_tokens=n, **GREEDY))):
+        assert len(out) == n
+        assert_near_best_tokens(w, cfg, p, out, f"{name} preempted")
+    assert short.stats()["preemptions"] > 0 and short.stats()["kv_blocks_used"] == 0
+
+
+@pytest.mark.parametrize("name", ["a", "b", "d"])
+def test_prefix_cache_hits_on_the_gpu(folders, name):
+    """Two prompts that share three full pages, one after the other through one engine: the
+    second takes the first's pages (`cached_prompt_tokens`), and both get the plain
+    implementation's tokens in float32; in bfloat16 tokens near the best."""
+    from atomserve_b200.engine.sequence import SamplingParams
+
+    cfg, bs, w, folder = folders[name]
+    shared = prompts(cfg, [3 * bs + 2], seed=6)[0]
+    ps = [shared + [1, 2, 3], shared + [4]]
+    params = SamplingParams(max_tokens=6, **GREEDY)
+    eng = engine_for(folder, "float32", bs)
+    assert eng.scheduler.prefix_caching
+    got = [eng.generate([p], params)[0] for p in ps]
+    assert got == [plain.greedy_generate(w, cfg, p, 6) for p in ps]
+    assert eng.stats()["cached_prompt_tokens"] == 3 * bs and eng.stats()["kv_blocks_cached"] >= 3
+    eng = engine_for(folder, "bfloat16", bs)
+    for p in ps:
+        assert_near_best_tokens(w, cfg, p, eng.generate([p], params)[0], f"{name} prefix")
+    assert eng.stats()["cached_prompt_tokens"] == 3 * bs
+
+
+def test_four_client_threads_on_the_gpu(folders):
+    """The engine thread owns the device; four client threads submit and iterate their handles
+    (the reference's tests/test_engine.py:27-71 in this engine's terms); one request is aborted."""
+    import threading
+
+    from atomserve_b200.engine.sequence import SamplingParams
+
+    cfg, bs, w, folder = folders["b"]
+    eng = engine_for(folder, "float32", bs)
+    eng.start()
+    ps = prompts(cfg, [4, 9, 14, 6], seed=7)
+    expect = [plain.greedy_generate(w, cfg, p, 5) for p in ps]
+    results = [None] * 4
+
+    def client(i):
+        results[i] = list(eng.submit(ps[i], SamplingParams(max_tokens=5, **GREEDY)))
+
+    threads = [threading.Thread(target=client, args=(i,)) for i in range(4)]
+    [t.start() for t in threads]
+    [t.join(timeout=120) for t in threads]
+    assert results == expect
+    handle = eng.submit(ps[2], SamplingParams(max_tokens=4000, **GREEDY))
+    it = iter(handle)
+    next(it)
+    handle.abort()
+    list(it)
+    assert handle.finish_reason == "abort" and handle.ttft is not None
+    eng.shutdown()
+    assert eng.stats()["kv_blocks_used"] == 0 and eng.stats()["running"] == 0
 
 
 def test_sampled_generation_is_seeded_and_in_support(folders):
@@ -478,3 +539,95 @@ def test_another_position_encoding_through_the_attention_part(dtype):
     view.slots = torch.tensor([table[p // bs] * bs + p % bs for p in range(T)], dtype=torch.int32, device="cuda")
     other = own.forward(h.cuda().to(dtype), res.cuda().to(dtype), step_context([T], [0]), view).float().cpu()
     assert rel_error(other, ref) > 1e-2
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_a_position_encoding_that_is_no_rotation_by_frequency(dtype):
+    """The package's attention with an encoding that has no fused form (angle = sqrt(position) x
+    frequency): the part normalises q and k, lets the encoding's own `encode` work the positions
+    in, then stores. Two portions through its cache equal the longhand in float64."""
+    from atomserve_b200.parts import CacheView, PartSpec, build_part
+
+    d, H, KV, hd, bs, T, theta, eps = 64, 4, 2, 32, 4, 21, 2e3, 1e-5
+    g = torch.Generator().manual_seed(9)
+    names = {"q_proj": (H * hd, d), "k_proj": (KV * hd, d), "v_proj": (KV * hd, d), "o_proj": (d, H * hd)}
+    w = {n: (torch.randn(s, generator=g) * 0.1).bfloat16().float() for n, s in names.items()}
+    gains = {n: 1 + 0.1 * torch.randn(hd, generator=g) for n in ("q_norm", "k_norm")}
+    part = build_part("mixer", PartSpec("gqa_attention", dict(
+        num_heads=H, num_kv_heads=KV, head_dim=hd, qk_norm_eps=eps,
+        position=PartSpec("toy_sqrt_rotation", dict(head_dim=hd, theta=theta))), "a."), d)  # fmt: skip
+    assert part.position.fused_rotary() is None
+    part.load({**{f"a.{n}.weight": v.cuda().to(dtype) for n, v in w.items()},
+               **{f"a.{n}.weight": v.cuda() for n, v in gains.items()}})  # fmt: skip
+    h = torch.randn(T, d, generator=g).bfloat16().float()
+    res = torch.randn(T, d, generator=g).bfloat16().float()
+
+    pos = torch.arange(T)
+    q = plain.rms_norm((h @ w["q_proj"].T).view(T, H, hd).double(), gains["q_norm"].double(), eps)
+    k = plain.rms_norm((h @ w["k_proj"].T).view(T, KV, hd).double(), gains["k_norm"].double(), eps)
+    q, k = toy_parts.sqrt_rotation_reference(q, pos, theta), toy_parts.sqrt_rotation_reference(k, pos, theta)
+    v = (h @ w["v_proj"].T).view(T, KV, hd).double()
+    ref = (res.double() + plain.attention(q, k, v).reshape(T, H * hd) @ w["o_proj"].double().T).float()
+
+    view = CacheView(k=torch.zeros(8, KV, bs, hd, device="cuda", dtype=dtype), block_size=bs)
+    view.v = torch.zeros_like(view.k)
+    table = [4, 1, 6, 0, 3, 7]
+    view.block_tables = torch.tensor([table], dtype=torch.int32, device="cuda")
+    outs = []
+    for start, n in ((0, 13), (13, 8)):
+        view.slots = torch.tensor([table[p // bs] * bs + p % bs for p in range(start, start + n)], dtype=torch.int32, device="cuda")
+        outs.append(part.forward(h[start : start + n].cuda().to(dtype), res[start : start + n].cuda().to(dtype),
+                                 step_context([n], [start]), view))  # fmt: skip
+    got = torch.cat(outs).float().cpu()
+    assert rel_error(got, ref) < (1e-5 if dtype == torch.float32 else 2e-2)
+    # the rule matters: with plain positions instead of their square roots the result differs
+    q2 = plain.apply_rope(q.float(), plain.rope_angles(pos, hd, theta))
+    assert (q2.double() - q).abs().max() > 1e-2
+
+
+def test_a_toy_mixer_whose_pages_hold_one_tensor_runs_beside_the_packages_attention():
+    """Layer 0 is the package's attention (pages of keys and values), layer 1 the test's latent
+    mixer (pages of one narrow tensor): two cache groups of different page contents in one model,
+    stepped by the package's runner on the GPU, whole and cut into portions, mixed with a second
+    request; the result is the CPU model's of torch parts."""
+    from atomserve_b200.cache import CacheManager
+    from atomserve_b200.parts import LayerCall, LayerSpec, ModelSpec, PartSpec
+
+    cfg = {**TINY["a"][0], "num_hidden_layers": 2}
+    d, eps, hd, rank, bs = cfg["hidden_size"], cfg["rms_norm_eps"], cfg["head_dim"], 12, 16
+    w = checkpoint(cfg, seed=14)
+    g = torch.Generator().manual_seed(4)
+    for k in [k for k in w if k.startswith("model.layers.1.self_attn.")]:
+        del w[k]
+    for n, shape in (("down", (rank, d)), ("query", (rank, d)), ("up", (d, rank))):
+        w[f"model.layers.1.latent.{n}.weight"] = (torch.randn(shape, generator=g) * 0.3).bfloat16().float()
+
+    def spec(kinds):
+        t = "" if kinds == "cuda" else "torch_"
+        if kinds == "cuda":
+            attn = PartSpec("gqa_attention", dict(num_heads=4, num_kv_heads=2, head_dim=hd, qk_norm_eps=eps,
+                            position=PartSpec("rotary", dict(head_dim=hd, theta=cfg["rope_theta"]))), "model.layers.0.self_attn.")  # fmt: skip
+        else:
+            attn = PartSpec("torch_attention", dict(num_heads=4, num_kv_heads=2, head_dim=hd, eps=eps, theta=cfg["rope_theta"]),
+                            "model.layers.0.self_attn.")  # fmt: skip
+        layers = []
+        for i, mixer in enumerate([attn, PartSpec("latent_mixer", dict(rank=rank), "model.layers.1.latent.")]):
+            p = f"model.layers.{i}."
+            layers.append(LayerSpec("pre_norm", mixer, PartSpec(t + "swiglu", dict(intermediate_size=cfg["intermediate_size"]), p + "mlp."),
+                                    PartSpec(t + "rms_norm", dict(eps=eps), p + "input_layernorm."),
+                                    PartSpec(t + "rms_norm", dict(eps=eps), p + "post_attention_layernorm.")))  # fmt: skip
+        return ModelSpec(hidden_size=d, vocab_size=cfg["vocab_size"], max_positions=512,
+                         embedding=PartSpec("token_embedding" if kinds == "cuda" else "torch_embedding", dict(vocab_size=cfg["vocab_size"]), "model.embed_tokens."),
+                         layers=tuple(layers), schedule=(LayerCall(0), LayerCall(1)),
+                         final_norm=PartSpec(t + "rms_norm", dict(eps=eps), "model.norm."),
+                         head=PartSpec("lm_head" if kinds == "cuda" else "torch_head", dict(vocab_size=cfg["vocab_size"], tied=True), "lm_head."))  # fmt: skip
+
+    ids = prompts(cfg, [37], seed=2)[0]
+    cuts = [5, 2, 13, 1, 1, 15]
+    ref_whole, ref_cut = run_whole_and_cut(custom_model(spec("torch"), w, "cpu", torch.float32), bs, ids, cuts, "cpu")
+    assert rel_error(ref_cut, ref_whole) < 1e-5
+    model = custom_model(spec("cuda"), w, "cuda", torch.float32)
+    cache = CacheManager(model.cache_requirements(), bs, 8, 2, torch.float32, "cuda")
+    assert [sorted(g.pools) for g in cache.groups] == [["k", "v"], ["latent"]]
+    whole, cut = run_whole_and_cut(model, bs, ids, cuts, "cuda")
+    assert rel_error(whole, ref_whole) < FLOAT32_TOLERANCE and rel_error(cut, ref_whole) < FLOAT32_TOLERANCE

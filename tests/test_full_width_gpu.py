@@ -88,7 +88,7 @@ def test_mixed_requests_reusing_pages(wide, dtype):
     mixed step holds anything from a handful of tokens to several hundred."""
     folder, ps, oracle = wide
     ps3, oracle3 = ps * 3, oracle * 3
-    rp = replayer(folder, dtype, pool_for(ps, 4))
+    rp = replayer(folder, dtype, pool_for(ps3, 4))  # any four of them fit: 2,432 of the 3,405 tokens
     rng = np.random.default_rng(17)
     step_sizes = []
     for entries, end in mixed_trace(ps3, rng, largest=300):

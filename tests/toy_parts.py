@@ -4,10 +4,13 @@ Two uses. (1) Every hot part again in plain torch (`torch_*` kinds and the archi
 "ToyTorchLM"), reading and writing the paged cache through the same CacheView: with these
 the scheduler, cache manager, runner and engine run whole on the CPU. (2) `ema_mixer`, a mixer
 with state of its own (one vector per request, kept in the state slots), to show that such a
-part is registered, built and stepped without touching the package; `toy_top1_experts`, a
-feed-forward that routes each token to one of a few small experts; and
-`toy_interpolated_rotary`, another position encoding (positions compressed by a factor, only a
-part of the head rotated) that the package's attention takes in place of its own.
+part is registered, built and stepped without touching the package; `latent_mixer`, a mixer
+whose cache pages hold one tensor (a narrow latent per token) instead of keys and values;
+`toy_top1_experts`, a feed-forward that routes each token to one of a few small experts;
+`toy_interpolated_rotary`, another rotary position encoding (positions compressed by a factor,
+only a part of the head rotated) that the package's attention runs through its fused kernel; and
+`toy_sqrt_rotation`, an encoding that is no rotation by position x frequency and so applies
+itself (`encode`) between the attention part's norm and its cache write.
 
 They follow the package's interfaces and nothing else of it; the oracle stays plain_qwen3.
 """
@@ -21,7 +24,7 @@ import torch
 import plain_qwen3 as plain
 from atomserve_b200.config.registry import register_architecture
 from atomserve_b200.parts import (
-    CacheView, FeedForward, KVCacheSpec, LayerCall, LayerSpec, Mixer, ModelSpec, Norm, Part,
+    CacheView, FeedForward, KVCacheSpec, LayerCall, LayerSpec, Mixer, ModelSpec, Norm, PageSpec, PageTensor, Part,
     PartSpec, PositionEncoding, StateSpec, StepContext, TensorSpec, register_part,
 )  # fmt: skip
 
@@ -173,6 +176,52 @@ class EmaMixer(Mixer):
         return residual + out.to(h.dtype)
 
 
+class LatentMixer(Mixer):
+    """A mixer whose pages hold a single tensor: per token one latent vector c_t = W_down x_t of
+    width `rank` (one "head"), which serves as key and as value. Output y_t = W_up sum_s
+    softmax_s(q_t . c_s / sqrt(rank)) c_s over s <= t, with q_t = W_q x_t."""
+
+    def __init__(self, hidden_size, prefix, rank):
+        self.d, self.p, self.rank = hidden_size, prefix, rank
+
+    def cache_spec(self):
+        return PageSpec((PageTensor("latent", 1, self.rank),))
+
+    def tensor_specs(self):
+        return [TensorSpec(self.p + "down.weight", (self.rank, self.d)), TensorSpec(self.p + "query.weight", (self.rank, self.d)),
+                TensorSpec(self.p + "up.weight", (self.d, self.rank))]  # fmt: skip
+
+    def load(self, tensors):
+        self.w = {n: tensors[self.p + n + ".weight"] for n in ("down", "query", "up")}
+
+    def forward(self, h, residual, ctx, cache, write_cache=True):
+        bs, pages = cache.block_size, cache.pages["latent"]  # [blocks, 1, block_size, rank]
+        c, q = h @ self.w["down"].T, (h @ self.w["query"].T).float()
+        if write_cache:
+            slots = cache.slots.long()
+            pages[slots // bs, 0, slots % bs] = c.to(pages.dtype)
+        out = torch.empty(h.shape[0], self.rank, dtype=torch.float32, device=h.device)
+        row = 0
+        for r, (n, start) in enumerate(zip(ctx.host_q_lens, ctx.host_pos_start)):
+            pos = torch.arange(start + n, device=h.device)
+            latents = pages[cache.block_tables[r].long()[pos // bs], 0, pos % bs].float()  # [start + n, rank]
+            scores = q[row : row + n] @ latents.T * self.rank**-0.5
+            visible = pos[None, :] <= torch.arange(start, start + n, device=h.device)[:, None]
+            out[row : row + n] = scores.masked_fill(~visible, float("-inf")).softmax(-1) @ latents
+            row += n
+        return residual + out.to(h.dtype) @ self.w["up"].T
+
+
+def latent_mixer_reference(h: torch.Tensor, down, query, up) -> torch.Tensor:
+    """LatentMixer on one whole sequence, in float64, without a cache."""
+    h, down, query, up = (t.double() for t in (h, down, query, up))
+    c, q = h @ down.T, h @ query.T
+    T = h.shape[0]
+    scores = (q @ c.T) * down.shape[0] ** -0.5
+    scores = scores.masked_fill(torch.arange(T)[None, :] > torch.arange(T)[:, None], float("-inf"))
+    return (scores.softmax(-1) @ c) @ up.T
+
+
 def ema_reference(u: torch.Tensor, decay: float) -> torch.Tensor:
     s, out = torch.zeros_like(u[0]), []
     for t in range(u.shape[0]):
@@ -231,6 +280,30 @@ class InterpolatedRotary(PositionEncoding):
         self.inv_freq = (1.0 / (self.theta**exponents) / self.factor).to(device)
 
 
+class SqrtRotation(PositionEncoding):
+    """An encoding that is not "angle = position x frequency": pair i of the whole head turns by
+    sqrt(position) * theta^(-2i/head_dim). It has no fused form, so the attention part hands it
+    the normalised queries and keys (`encode`) and stores what comes back."""
+
+    def __init__(self, hidden_size, prefix, head_dim, theta):
+        self.head_dim, self.theta = head_dim, float(theta)
+
+    def encode(self, q, k, ctx):
+        turn = lambda x: sqrt_rotation_reference(x, ctx.positions.cpu(), self.theta).to(x.device, x.dtype)  # noqa: E731
+        return turn(q), (turn(k) if k is not None else None)
+
+
+def sqrt_rotation_reference(x, positions, theta):
+    """x [T, heads, head_dim] turned as SqrtRotation says, in float64."""
+    hd = x.shape[-1]
+    x = x.double().cpu()
+    inv = 1.0 / (theta ** (torch.arange(0, hd, 2, dtype=torch.float64) / hd))
+    angle = positions.double().sqrt()[:, None] * inv[None, :]
+    cos, sin = angle.cos()[:, None, :], angle.sin()[:, None, :]
+    a, b = x[..., : hd // 2], x[..., hd // 2 :]
+    return torch.cat([a * cos - b * sin, b * cos + a * sin], dim=-1)
+
+
 def interpolated_rotary_reference(x, positions, theta, factor, rotary_dim):
     """x [T, heads, head_dim] rotated as InterpolatedRotary says, in float64."""
     x = x.double()
@@ -250,6 +323,8 @@ register_part("head", "torch_head", TorchHead)
 register_part("feed_forward", "torch_swiglu", TorchSwiGLU)
 register_part("mixer", "torch_attention", TorchAttention)
 register_part("mixer", "ema_mixer", EmaMixer)
+register_part("mixer", "latent_mixer", LatentMixer)
+register_part("position", "toy_sqrt_rotation", SqrtRotation)
 
 
 @dataclass(frozen=True)
