@@ -23,7 +23,7 @@ def describe(words: list[int]) -> str | None:
     parts = []
     if words[PIPELINE]:
         code = words[PIPELINE]
-        who = _ROLES.get(code, f"prefill attention, wait {code}" if 10 <= code <= 29 else f"wait {code}")
+        who = _ROLES.get(code, f"prefill attention, wait {code}" if 10 <= code <= 29 else ("the self-test" if code == 90 else f"wait {code}"))
         parts.append(f"a tcgen05 kernel gave up a bounded wait ({who}); its output is incomplete")
     if words[EMBEDDING]:
         parts.append("the embedding met a token id outside the vocabulary")
@@ -62,6 +62,27 @@ class DeviceStatus:
         if text:
             self.words.zero_()
         return text
+
+
+def bounded_wait_selftest(device: torch.device | str = "cuda", polls: int = 4096) -> str | None:
+    """Run the kernel that makes a bounded wait run out on purpose (csrc/wait_selftest.cu): it
+    waits `polls` polls on a barrier that nothing arrives at, reports through the device's status
+    word, frees its tensor memory and returns. Gives back the report that the status words then
+    hold (and clears it), or raises if the block did not come back the expected way."""
+    import ctypes
+
+    from atomserve_b200.ops.library import KernelLibraryError, check, lib, ptr, stream
+
+    status = status_for(device)
+    fn = lib().asb_bounded_wait_selftest
+    fn.argtypes, fn.restype = [ctypes.c_void_p, ctypes.c_int, ctypes.c_void_p, ctypes.c_void_p], ctypes.c_int
+    freed = torch.zeros(1, dtype=torch.int32, device=status.device)
+    check(fn(ptr(status.pipeline), polls, ptr(freed), stream()))
+    outcome = int(freed.item())
+    report = status.problem()
+    if outcome != 1:
+        raise KernelLibraryError(f"bounded-wait self-test: the block ended with outcome {outcome} (1 expected), report {report!r}")
+    return report
 
 
 _BY_DEVICE: dict[torch.device, DeviceStatus] = {}

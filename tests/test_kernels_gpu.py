@@ -698,3 +698,23 @@ def test_captured_gemm_survives_workspace_growth(ops):
     assert torch.equal(out, expect)
     del junk
     L.check_gemm_status()
+
+
+def test_a_wait_that_runs_out_reports_frees_tensor_memory_and_returns(ops):
+    """The give-up path of the tcgen05 kernels, executed on purpose by a kernel that waits (a few
+    thousand polls) on a barrier nothing arrives at: the status word names it, the block frees its
+    tensor memory and ends, the context stays usable, and a GEMM that needs all of an SM's tensor
+    memory runs right afterwards. The engine's step would fail with this report."""
+    from atomserve_b200.ops.linear import check_gemm_status, gemm_tcgen05
+    from atomserve_b200.ops.status import bounded_wait_selftest, status_for
+
+    check_gemm_status()
+    for _ in range(3):  # repeatedly: tensor memory that was not freed would run out or stall
+        report = bounded_wait_selftest("cuda", polls=2048)
+        assert report is not None and "self-test" in report and "gave up a bounded wait" in report
+    assert status_for("cuda").problem() is None  # cleared by the read
+    x = torch.randn(128, 512, device="cuda").bfloat16()
+    w = torch.randn(384, 512, device="cuda").bfloat16()
+    out = gemm_tcgen05(x, w, None, torch.float32)
+    check_gemm_status()
+    assert torch.allclose(out.double().cpu(), x.double().cpu() @ w.double().cpu().T, atol=2e-2, rtol=1e-3)
