@@ -46,7 +46,8 @@ namespace {
 using asb::block_of;
 using asb::range_begin;
 
-constexpr int kMaxThreads = 192 + 32;
+constexpr int kMaxLoaders = 1;
+constexpr int kMaxThreads = 192 + 32 + 32 * (kMaxLoaders - 1);
 constexpr int BM = 128;   // P rows per tile = TMEM lanes
 constexpr int BK = 64;    // K elements per stage: 128 bytes, one swizzle atom
 constexpr int UMMA_K = 16;
@@ -68,6 +69,8 @@ struct GemmParams {
   int stream;            // 0: whole tiles round-robin; 1: equal contiguous ranges of K blocks
   int max_slots;         // workspace slots per tile
   int bn;                // Q rows per tile actually used (<= the kernel's BN; narrower tiles of unswapped weights)
+  int stages;            // pipeline stages in use (a narrower tile leaves room for more of them)
+  int stage_size;        // bytes from one stage's slot to the next: the P tile, then bn rows of Q, to a multiple of 1024
   // Optional timeline for profiling, null in normal use: %globaltimer stamps in rows of 8 words, 7
   // used per block (entry, set-up done, dependency wait over, first stage complete, last MMA
   // issued, last accumulator complete, epilogue done) and a row after the blocks for the reduction
@@ -140,12 +143,21 @@ struct Config {
   static constexpr int kTileP = BM * BK * 2;   // 16 KB
   static constexpr int kTileQ = BN * BK * 2;
   static constexpr int kStage = kTileP + kTileQ;
-  static constexpr int kStages = BN >= 256 ? 4 : (BN >= 128 ? 6 : 8);
+  static constexpr int kStages = BN >= 256 ? 4 : (BN >= 128 ? 6 : 8);   // with tiles of the full BN rows of Q
   static constexpr int kIssuers = BN <= 128 ? 2 : 1;            // threads that issue MMAs, an accumulator each
-  static constexpr int kThreads = 192 + 32 * (kIssuers - 1);
+  // Threads that request operands, a warp each (warp 0 and the warps after the issuing ones).
+  // One thread's chain of wait, announcement and two TMA requests takes about 700 cycles per K
+  // block whatever the boxes' sizes (714 with one thread, 353 with four, MMAs switched off), but
+  // so does the chain of the thread that issues the MMAs, which is the one that bounds this
+  // kernel: two or four loaders changed no shape's time here, so there is one.
+  static constexpr int kLoaders = kMaxLoaders;
+  static constexpr int kThreads = 192 + 32 * (kIssuers - 1) + 32 * (kLoaders - 1);
   static constexpr int kAccCols = kIssuers * BN;                // tensor-memory columns of one buffer
   static constexpr int kTmemCols = 2 * kAccCols < 32 ? 32 : 2 * kAccCols;   // two buffers
-  static constexpr int kSmem = kStages * kStage + 1024 /* alignment slack */ + 256 /* barriers */;
+  // the 256-row kernel also runs narrower tiles, of which more stages fit: it takes all an SM has
+  static constexpr int kStageRoom = BN >= 256 ? 227 * 1024 - 1024 - 256 : kStages * kStage;
+  static constexpr int kSmem = kStageRoom + 1024 /* alignment slack */ + 256 /* barriers */;
+  static constexpr int kMaxStages = 12;   // the barriers' 256 bytes hold 2 * 12 + 4 of them and the tensor-memory slot
 };
 
 // SwiGLU on a (gate, up) pair of float32 sums (atomserve/kernels.py:437-449).
@@ -163,12 +175,16 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_cons
   extern __shared__ unsigned char smem_raw[];
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;   // swizzle atoms need 1024-byte alignment
   unsigned char* aligned = smem_raw + (base - smem_u32(smem_raw));
-  const uint32_t bars = base + C::kStages * C::kStage;
+  // the 256-column kernel takes both from the plan (narrower tiles leave room for more stages);
+  // the others keep them as constants, which the one thread that issues their MMAs has no time to compute
+  const int stages = BN >= 256 ? p.stages : C::kStages;
+  const uint32_t stage_size = BN >= 256 ? (uint32_t)p.stage_size : (uint32_t)C::kStage;
+  const uint32_t bars = base + stages * stage_size;
   auto full_bar = [&](int s) { return bars + 8u * s; };
-  auto empty_bar = [&](int s) { return bars + 8u * (C::kStages + s); };
-  auto acc_full = [&](int b) { return bars + 8u * (2 * C::kStages + b); };
-  auto acc_empty = [&](int b) { return bars + 8u * (2 * C::kStages + 2 + b); };
-  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(aligned + C::kStages * C::kStage + 8 * (2 * C::kStages + 4));
+  auto empty_bar = [&](int s) { return bars + 8u * (stages + s); };
+  auto acc_full = [&](int b) { return bars + 8u * (2 * stages + b); };
+  auto acc_empty = [&](int b) { return bars + 8u * (2 * stages + 2 + b); };
+  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(aligned + stages * stage_size + 8 * (2 * stages + 4));
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int bn = p.bn;                                               // Q rows per tile: BN unless the plan narrowed it
@@ -176,7 +192,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_cons
 
   if (threadIdx.x == 0) {
     stamp(p, 0);
-    for (int s = 0; s < C::kStages; ++s) {
+    for (int s = 0; s < stages; ++s) {
       mbar_init(full_bar(s), 1);
       mbar_init(empty_bar(s), 1);
     }
@@ -200,53 +216,66 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_cons
   // pdl_wait() before it first reads that kernel's output; the TMA warp first fills the pipeline
   // with the weight operand, which no kernel writes.
 
-  if (warp == 0) {
+  constexpr int kFirstExtraLoader = 6 + C::kIssuers - 1;  // warps 0 and kFirstExtraLoader.. load
+  if (warp == 0 || warp >= kFirstExtraLoader) {
     if (lane == 0) {
-      // The weights are operand P when swapped, Q otherwise. Before waiting for the previous
-      // kernel, fill the first kStages stages with the weight half; the activation half follows.
+      // Loader `me` of kLoaders brings every kLoaders-th K block of the block's sequence. The
+      // weights are operand P when swapped, Q otherwise. Before waiting for the previous kernel,
+      // the first `stages` stages are filled with the weight half; the activation half follows.
+      const uint32_t me = warp == 0 ? 0u : (uint32_t)(warp - kFirstExtraLoader + 1);
       {
         SegmentWalk ahead(p);
         uint32_t it = 0;
-        while (it < (uint32_t)C::kStages && ahead.next()) {
+        while (it < (uint32_t)stages && ahead.next()) {
           const int p0 = (ahead.tile % p.tiles_p) * BM, q0 = (ahead.tile / p.tiles_p) * bn;
-          for (int kb = ahead.kb0; kb < ahead.kb1 && it < (uint32_t)C::kStages; ++kb, ++it) {
+          for (int kb = ahead.kb0; kb < ahead.kb1 && it < (uint32_t)stages; ++kb, ++it) {
+            if (it % C::kLoaders != me) continue;
             mbar_expect_tx(full_bar(it), stage_bytes);
-            if (p.swap) tma_load_2d(base + it * C::kStage, &map_p, full_bar(it), kb * BK, p0);
-            else tma_load_2d(base + it * C::kStage + C::kTileP, &map_q, full_bar(it), kb * BK, q0);
+            if (p.swap) tma_load_2d(base + it * stage_size, &map_p, full_bar(it), kb * BK, p0);
+            else tma_load_2d(base + it * stage_size + C::kTileP, &map_q, full_bar(it), kb * BK, q0);
           }
         }
       }
       asb::pdl_wait();
-      stamp(p, 2);
-      asb::pdl_launch_dependents();
+      if (me == 0) {
+        stamp(p, 2);
+        asb::pdl_launch_dependents();
+      }
       SegmentWalk walk(p);
-      uint32_t it = 0;  // K blocks loaded so far by this block, across segments
+      uint32_t it = 0;  // K blocks of this block so far, across segments
+      uint32_t turn = 0;    // it % kLoaders: whose K block this is
+      int s = 0;            // the stage K block `it` goes to, and the phase of its barriers:
+      uint32_t phase = 0;   // it % stages and (it / stages) & 1, kept by counting
       bool ok = true;
       while (ok && walk.next()) {
         const int p0 = (walk.tile % p.tiles_p) * BM, q0 = (walk.tile / p.tiles_p) * bn;
         for (int kb = walk.kb0; kb < walk.kb1; ++kb, ++it) {
-          const int s = it % C::kStages;
-          if (it < (uint32_t)C::kStages) {  // the weight half is already on its way
-            if (p.swap) tma_load_2d(base + s * C::kStage + C::kTileP, &map_q, full_bar(s), kb * BK, q0);
-            else tma_load_2d(base + s * C::kStage, &map_p, full_bar(s), kb * BK, p0);
-            continue;
+          if (turn == me) {
+            if (it < (uint32_t)stages) {  // the weight half is already on its way
+              if (p.swap) tma_load_2d(base + s * stage_size + C::kTileP, &map_q, full_bar(s), kb * BK, q0);
+              else tma_load_2d(base + s * stage_size, &map_p, full_bar(s), kb * BK, p0);
+            } else {
+              ok = mbar_wait(empty_bar(s), phase ^ 1u, p.status, 1);
+              if (!ok) break;
+              mbar_expect_tx(full_bar(s), stage_bytes);
+              tma_load_2d(base + s * stage_size, &map_p, full_bar(s), kb * BK, p0);
+              tma_load_2d(base + s * stage_size + C::kTileP, &map_q, full_bar(s), kb * BK, q0);
+            }
           }
-          const uint32_t phase = (it / C::kStages) & 1u;
-          ok = mbar_wait(empty_bar(s), phase ^ 1u, p.status, 1);
-          if (!ok) break;
-          mbar_expect_tx(full_bar(s), stage_bytes);
-          tma_load_2d(base + s * C::kStage, &map_p, full_bar(s), kb * BK, p0);
-          tma_load_2d(base + s * C::kStage + C::kTileP, &map_q, full_bar(s), kb * BK, q0);
+          if (++turn == (uint32_t)C::kLoaders) turn = 0;
+          if (++s == stages) { s = 0; phase ^= 1u; }
         }
       }
     }
-  } else if (warp == 1 || warp >= 6) {
+  } else if (warp == 1 || (warp >= 6 && warp < kFirstExtraLoader)) {
     asb::pdl_wait();
     if (lane == 0) {
       const int me = warp == 1 ? 0 : warp - 5;  // which of the kIssuers issuing threads
       const uint32_t idesc = instr_desc(BM, bn);
       SegmentWalk walk(p);
       uint32_t it = 0, seg = 0;
+      int s = -1;           // the stage of K block `it`, it % stages, and its barriers' phase,
+      uint32_t phase = 0;   // (it / stages) & 1: advanced at the top of every K block
       bool ok = true;
       while (ok && walk.next()) {
         const uint32_t buf = seg & 1u;
@@ -256,15 +285,14 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_cons
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         const uint32_t tmem_acc = tmem_base + buf * C::kAccCols + me * BN;
         for (int kb = walk.kb0; kb < walk.kb1; ++kb, ++it) {
+          if (++s == stages) { s = 0; phase ^= 1u; }
           if (C::kIssuers > 1 && (kb - walk.kb0) % C::kIssuers != me) continue;
-          const int s = it % C::kStages;
-          const uint32_t phase = (it / C::kStages) & 1u;
           ok = mbar_wait(full_bar(s), phase, p.status, 2);
           if (!ok) break;
           if (it == 0) stamp(p, 3);
           asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-          const uint64_t da = smem_desc(base + s * C::kStage);
-          const uint64_t db = smem_desc(base + s * C::kStage + C::kTileP);
+          const uint64_t da = smem_desc(base + s * stage_size);
+          const uint64_t db = smem_desc(base + s * stage_size + C::kTileP);
 #pragma unroll
           for (int k = 0; k < BK / UMMA_K; ++k)  // 32 bytes further along K inside the swizzle atom
             umma(tmem_acc, da + (uint64_t)(k * UMMA_K * 2 >> 4), db + (uint64_t)(k * UMMA_K * 2 >> 4), idesc,
@@ -528,8 +556,23 @@ unsigned long long* g_stamps = nullptr;  // asb_gemm_tcgen05_timeline
 
 struct Plan {
   int swap, bn, bn_kernel, tiles_p, tiles_q, kb_per_tile, stream, blocks, max_slots;
+  int stages, stage_size;
+  int pair;             // 0, or the weight rows (128 or 256) of the tiles that pairs of SMs compute (gemm_tcgen05_pair.cu)
   long long workspace;  // float32 elements
 };
+
+// Tuning aid (asb_gemm_tcgen05_tune): orientation and tile width forced for the calls that follow.
+int g_force_swap = -1, g_force_bn = 0;
+
+int stage_room(int bn_kernel) {
+  switch (bn_kernel) {
+    case 16: return Config<16>::kStageRoom;
+    case 32: return Config<32>::kStageRoom;
+    case 64: return Config<64>::kStageRoom;
+    case 128: return Config<128>::kStageRoom;
+    default: return Config<256>::kStageRoom;
+  }
+}
 
 // How a shape is run. One block runs per SM. Operands swap (weights fill the 128-row MMA, tokens
 // are its N = 16..256) for up to 32 tokens always, and for up to 256 tokens where the unswapped
@@ -549,21 +592,53 @@ Plan make_plan(int M, int N, int K) {
   pl.swap = M <= 32 || (M <= 256 && 2 * unswapped_tiles < sm_count()) ||
             (M <= 512 && kb_per_tile >= 128 && 1.4 * unswapped_tiles < sm_count()) ? 1 : 0;
   pl.bn = pl.swap ? (M <= 16 ? 16 : (M <= 32 ? 32 : (M <= 64 ? 64 : (M <= 128 ? 128 : 256)))) : (N <= 128 ? 128 : 256);
+  if (g_force_swap >= 0) pl.swap = g_force_swap == 1 ? 1 : 0;
+  if (g_force_swap >= 0 && pl.swap) pl.bn = M <= 16 ? 16 : (M <= 32 ? 32 : (M <= 64 ? 64 : (M <= 128 ? 128 : 256)));
   pl.bn_kernel = pl.bn;
-  if (!pl.swap && pl.bn == 256) {
-    // An SM's time per K block goes with the bytes it takes in, the tokens' box (16 KB) and bn
-    // weight rows, so where 256-row tiles leave SMs idle (one row of tiles over few tokens, or
-    // few weight rows under a few hundred tokens), narrower tiles that spread the weight rows over
-    // more SMs are faster as long as they need no further wave; the 256-column kernel runs them.
+  if (!pl.swap && N > 128) {
+    // Unswapped tiles are 128 tokens by bn weight rows, bn a multiple of 32 from 64 to 256. An
+    // SM's time per K block goes with the bytes it takes in, the tokens' box (16 KB) and bn weight
+    // rows, so where 256-row tiles leave SMs idle (one row of tiles over few tokens, or few weight
+    // rows under a few hundred tokens), narrower tiles that spread the weight rows over more SMs
+    // are faster as long as they need no further wave. Tiles of up to 128 rows run in the
+    // 128-column kernel (six stages; o at 512 tokens 26.3 -> 21.5 us against the 256-column
+    // kernel's four), wider ones in the 256-column kernel with as many stages as fit beside them
+    // (which by itself gains nothing: 224 rows on five stages run like 256 on four, measured).
     const int sms_now = sm_count();
     const int token_tiles = (M + BM - 1) / BM;
     double best = 1e30;
-    for (int bn = 256; bn >= 128; bn -= 32) {  // multiples of 32: the epilogue reads 32 columns at a time
+    for (int bn = 256; bn >= 64; bn -= 32) {  // multiples of 32: the epilogue reads 32 columns at a time
       const int tiles = token_tiles * ((N + bn - 1) / bn);
       const double cost = (double)((tiles + sms_now - 1) / sms_now) * (128 + bn);
-      if (cost < best) { best = cost; pl.bn = bn; }
+      if (cost < best) { best = cost; pl.bn = bn; pl.bn_kernel = bn <= 128 ? 128 : 256; }
     }
+    if (g_force_bn && g_force_swap != 2) { pl.bn = g_force_bn; pl.bn_kernel = g_force_bn <= 128 ? 128 : 256; }
   }
+  // More than 128 tokens can also run on pairs of SMs: tiles of 256 tokens by 128 or 256 weight
+  // rows, each SM bringing its half (gemm_tcgen05_pair.cu). Microseconds per K block and SM,
+  // measured on the 8B shapes at 512 to 4,096 tokens: 0.39 for a single SM's 128 x 256 tile (0.355
+  // for 192 rows), 0.20 for tiles of up to 128 rows in the
+  // 128-column kernel; 0.33 for a pair's 256 x 256 tile, 0.225 for 256 x 128. The pair's tile is
+  // twice the arithmetic, so with enough tiles to fill the device it wins (gate/up at 2,048 tokens:
+  // 339 -> 268 us, the vendor library 284); with few tiles the narrow single tiles that occupy
+  // more SMs do.
+  pl.pair = 0;
+  if (!pl.swap && M > BM) {
+    const int sms_now = sm_count(), kb = (K + BK - 1) / BK;
+    const int single_tiles = ((M + BM - 1) / BM) * ((N + pl.bn - 1) / pl.bn);
+    const double single_kb = pl.bn_kernel == 128 ? 0.20 * (128 + pl.bn) / 256.0 : 0.25 + 0.14 * pl.bn / 256.0;
+    double best = (double)((single_tiles + sms_now - 1) / sms_now) * kb * single_kb;
+    for (int bn = 256; bn >= 128; bn -= 128) {
+      const int tiles = ((M + 255) / 256) * ((N + bn - 1) / bn), pairs = sms_now / 2;
+      const double cost = (double)((tiles + pairs - 1) / pairs) * kb * (bn == 256 ? 0.33 : 0.225);
+      if (cost < best * 0.97) { best = cost; pl.pair = bn; }
+    }
+    if (g_force_swap == 0) pl.pair = 0;
+  }
+  if (g_force_swap == 2 && M > BM) { pl.swap = 0; pl.pair = g_force_bn == 128 ? 128 : 256; }
+  pl.stage_size = BM * BK * 2 + ((pl.bn * BK * 2 + 1023) / 1024) * 1024;
+  pl.stages = stage_room(pl.bn_kernel) / pl.stage_size;
+  if (pl.stages > Config<256>::kMaxStages) pl.stages = Config<256>::kMaxStages;
   const int p_rows = pl.swap ? N : M, q_rows = pl.swap ? M : N;
   pl.tiles_p = (p_rows + BM - 1) / BM;
   pl.tiles_q = (q_rows + pl.bn - 1) / pl.bn;
@@ -585,6 +660,7 @@ Plan make_plan(int M, int N, int K) {
   // device without cutting K; many tiles in nearly whole waves are best left whole)
   pl.stream = pl.swap && stream_cost < whole_cost * 0.97 ? 1 : 0;
   pl.blocks = pl.stream ? stream_blocks : whole_blocks;
+  if (pl.pair) pl.stream = 0;
   pl.max_slots = 0;
   pl.workspace = 0;
   if (pl.stream) {
@@ -611,6 +687,10 @@ int launch(const CUtensorMap& mp, const CUtensorMap& mq, const GemmParams& p, co
 
 }  // namespace
 
+// The form for many tokens on pairs of SMs (gemm_tcgen05_pair.cu).
+extern "C" int asb_gemm_tcgen05_pair(void* out, const void* x, const void* w, const void* residual, int M, int N,
+                                     int K, int mode, int bn, int* status, cudaStream_t stream);
+
 // Float32 workspace elements a call needs (0 when every tile is computed whole).
 extern "C" long long asb_gemm_tcgen05_workspace(int M, int N, int K, int* stream_out) {
   if (M <= 0 || N <= 0 || K <= 0) return 0;
@@ -623,15 +703,27 @@ extern "C" long long asb_gemm_tcgen05_workspace(int M, int N, int K, int* stream
 // memory of (blocks + 1) * 8 64-bit words that the caller zeroes; null switches it off again.
 extern "C" void asb_gemm_tcgen05_timeline(void* buffer) { g_stamps = (unsigned long long*)buffer; }
 
-// How a shape is run: out7 = {cuts K (1) or whole tiles (0), swapped operands, workspace slots per
-// tile, token columns per tile, K blocks per tile, tiles, thread blocks}. A shape that cuts K with
+// Tuning aid: force the orientation (swap 0: unswapped on single SMs, 1: swapped, 2: pairs of
+// SMs; -1 automatic) and, for unswapped tiles, the weight rows per tile (single SMs: a multiple of
+// 32 from 64 to 256; pairs: 128 or 256; 0 automatic) of the calls that follow.
+extern "C" void asb_gemm_tcgen05_tune(int swap, int bn) { g_force_swap = swap; g_force_bn = bn; }
+
+// How a shape is run: out8 = {cuts K (1) or whole tiles (0), swapped operands, workspace slots per
+// tile, token columns (swapped) or weight rows (unswapped) per tile, K blocks per tile, tiles,
+// thread blocks, weight rows of the tiles of pairs of SMs (0: single SMs)}. With pairs, a tile is
+// 256 tokens by that many weight rows and two thread blocks share it. A shape that cuts K with
 // swapped operands can leave its product as partial sums (mode 3 of asb_gemm_tcgen05), which
 // csrc/gemm_partials.cuh describes.
-extern "C" int asb_gemm_tcgen05_plan(int M, int N, int K, int* out7) {
+extern "C" int asb_gemm_tcgen05_plan(int M, int N, int K, int* out8) {
   if (M <= 0 || N <= 0 || K <= 0) return asb::fail("gemm_tcgen05_plan: empty shape");
   const Plan pl = make_plan(M, N, K);
-  out7[0] = pl.stream; out7[1] = pl.swap; out7[2] = pl.max_slots; out7[3] = pl.bn;
-  out7[4] = pl.kb_per_tile; out7[5] = pl.tiles_p * pl.tiles_q; out7[6] = pl.blocks;
+  out8[0] = pl.stream; out8[1] = pl.swap; out8[2] = pl.max_slots; out8[3] = pl.bn;
+  out8[4] = pl.kb_per_tile; out8[5] = pl.tiles_p * pl.tiles_q; out8[6] = pl.blocks;
+  out8[7] = pl.pair;
+  if (pl.pair) {
+    const int tiles = ((M + 255) / 256) * ((N + pl.pair - 1) / pl.pair), pairs = sm_count() / 2;
+    out8[3] = pl.pair; out8[5] = tiles; out8[6] = 2 * (tiles < pairs ? tiles : pairs);
+  }
   return 0;
 }
 
@@ -659,6 +751,8 @@ extern "C" int asb_gemm_tcgen05(void* out, const void* x, const void* w, const v
   const Plan pl = make_plan(M, N, K);
   if (mode == 3 && !(pl.stream && pl.swap && pl.tiles_q == 1))
     return asb::fail("gemm_tcgen05: [%d, %d] x [%d, %d] does not run with partial sums", M, K, N, K);
+  if (pl.pair && mode != 3)
+    return asb_gemm_tcgen05_pair(out, x, w, residual, M, N, K, mode, pl.pair, status, stream);
   if (pl.workspace > 0 && !workspace) return asb::fail("gemm_tcgen05: this shape needs a workspace of %lld floats", pl.workspace);
 
   GemmParams p;
@@ -677,6 +771,8 @@ extern "C" int asb_gemm_tcgen05(void* out, const void* x, const void* w, const v
   p.stream = pl.stream;
   p.max_slots = pl.max_slots;
   p.bn = pl.bn;
+  p.stages = pl.stages;
+  p.stage_size = pl.stage_size;
   p.stamps = g_stamps;
   alignas(64) CUtensorMap mp, mq;
   if (int rc = make_map(&mp, pl.swap ? w : x, p.p_rows, K, BM)) return rc;

@@ -44,6 +44,22 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int* st
   return false;
 }
 
+// One probe of the phase with the given parity: non-zero if it has completed. It never suspends
+// the thread (test_wait, not try_wait). The answer takes a couple of hundred cycles to arrive; a
+// thread that asks early and looks at the answer only after it has issued other work does not
+// stand still for them.
+__device__ __forceinline__ uint32_t mbar_try(uint32_t bar, uint32_t parity) {
+  uint32_t done;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(done)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return done;
+}
+
 // TMA tile loads (no multicast). Coordinates are element offsets, innermost first; the innermost
 // must be a multiple of 16 bytes.
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y) {
@@ -57,6 +73,11 @@ __device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map
       "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
       ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y), "r"(z)
       : "memory");
+}
+
+// The same box requested into L2 only: no shared memory, no barrier, nothing to wait for.
+__device__ __forceinline__ void tma_prefetch_2d(const CUtensorMap* map, int x, int y) {
+  asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global.tile [%0, {%1, %2}];" ::"l"(map), "r"(x), "r"(y) : "memory");
 }
 
 // Shared-memory matrix descriptors for tiles in the 128-byte swizzle, rows of 128 bytes (64

@@ -126,7 +126,7 @@ PARTIAL_SUMS = os.environ.get("ATOMSERVE_B200_PARTIAL_SUMS", "1") != "0"
 def _plan(M: int, N: int, K: int) -> tuple[int, ...]:
     plan = _PLANS.get((M, N, K))
     if plan is None:
-        out = (ctypes.c_int * 7)()
+        out = (ctypes.c_int * 8)()
         check(lib().asb_gemm_tcgen05_plan(M, N, K, out))
         plan = _PLANS[(M, N, K)] = tuple(out)
     return plan
@@ -142,7 +142,7 @@ def linear_partial(x: torch.Tensor, w: torch.Tensor) -> PartialSums | None:
     if not tcgen05_supported(x, w):
         return None
     (M, K), N = x.shape, w.shape[0]
-    cuts_k, swapped, max_slots, tile_tokens, k_blocks, tiles, blocks = _plan(M, N, K)
+    cuts_k, swapped, max_slots, tile_tokens, k_blocks, tiles, blocks, _pair = _plan(M, N, K)
     if not (cuts_k and swapped) or tiles * 128 < N or M > tile_tokens:
         return None
     workspace = gemm_workspace(x.device, tiles * max_slots * 128 * tile_tokens)

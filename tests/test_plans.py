@@ -54,7 +54,7 @@ def test_gemm_plans_keep_every_tile_within_its_partial_sum_slots():
         pytest.skip(f"the kernel library is not available: {error}")
     plan.argtypes = [ctypes.c_int] * 3 + [ctypes.POINTER(ctypes.c_int)]
     plan.restype = None
-    out = (ctypes.c_int * 7)()
+    out = (ctypes.c_int * 8)()
     rng = random.Random(1)
     shapes = [(8, 4096, 4096), (1, 151936, 4096), (512, 4096, 12288), (2048, 24576, 4096), (300, 5120, 17408)]
     for _ in range(3000):
@@ -63,11 +63,15 @@ def test_gemm_plans_keep_every_tile_within_its_partial_sum_slots():
                        rng.choice([8, 64, 72, 128, 1000, 4096, 8192, 12288, 17408])))  # fmt: skip
     for M, N, K in shapes:
         plan(M, N, K, out)
-        cuts_k, swap, max_slots, bn, kb, tiles, blocks = list(out)
+        cuts_k, swap, max_slots, bn, kb, tiles, blocks, pair = list(out)
         assert kb == -(-K // 64) and 1 <= blocks <= 148, (M, N, K)
+        if pair:  # tiles of 256 tokens by `pair` weight rows, two blocks (a pair of SMs) on each
+            assert pair in (128, 256) and bn == pair and not swap and not cuts_k and M > 128, (M, N, K)
+            assert tiles == -(-M // 256) * -(-N // pair) and blocks == 2 * min(tiles, 74), (M, N, K)
+            continue
         p_rows, q_rows = (N, M) if swap else (M, N)
         assert tiles == -(-p_rows // 128) * -(-q_rows // bn), (M, N, K)
-        assert bn in (16, 32, 64, 128, 256) if swap else (bn % 32 == 0 and 128 <= bn <= 256), (M, N, K, bn)
+        assert bn in (16, 32, 64, 128, 256) if swap else (bn % 32 == 0 and 64 <= bn <= 256), (M, N, K, bn)
         if swap:
             assert bn >= min(M, 256) or M > 256, (M, N, K, bn)
         if not cuts_k:
