@@ -14,7 +14,9 @@
 // CTA and counts both CTAs' arrivals and bytes (the odd CTA's TMA completes there through the
 // cluster address); empty[s] and acc_full[b] exist in both CTAs and are signalled in both by one
 // tcgen05.commit with a multicast of the arrival (not of any load); acc_empty[b] lives in the
-// even CTA and takes one arrival per epilogue warp of either CTA. Every wait is bounded
+// even CTA and takes one arrival per epilogue warp of either CTA. Before a CTA leaves, its first
+// loader waits for the last use of every stage to be handed back, so that no commit is still on
+// its way into a CTA that has gone. Every wait is bounded
 // (tcgen05.cuh); a wait that runs out sets the status word, the roles wind down, both CTAs meet at
 // a cluster barrier, tensor memory is freed and the kernel returns.
 #include <cuda.h>
@@ -209,6 +211,17 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid
 #pragma unroll
         for (int j = 0; j < C::kSub; ++j) tma_load_2d_pair(dst + j * C::kA, &map_x, bar, (ks * C::kSub + j) * BK, x0);
         advance(C::kLoaders);
+      }
+      if (me == 0) {
+        // Nobody has waited for the last use of each slot to be handed back, and the commits that
+        // hand them back arrive in both CTAs on their own, after the MMAs, not as part of any
+        // thread's work: a CTA that left before the last of them had landed could have its shared
+        // memory, by then perhaps another kernel's, written by the pair's other half. So one
+        // thread of each CTA sees every slot's last use complete before the CTA goes on to leave.
+        for (int slot = 0; slot < C::kStages && (uint32_t)slot < total; ++slot) {
+          const uint32_t last = (uint32_t)slot + (uint32_t)C::kStages * ((total - 1u - (uint32_t)slot) / (uint32_t)C::kStages);
+          if (!mbar_wait(empty_bar(slot), (last / (uint32_t)C::kStages) & 1u, p.status, 38)) break;
+        }
       }
     }
   } else if (warp == 1) {
