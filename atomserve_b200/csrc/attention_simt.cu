@@ -218,6 +218,10 @@ __global__ void attention_reduce_kernel(T* __restrict__ out, const float* __rest
   float denom = 0.f;
   for (int i = 0; i < NP; ++i)
     if (pl[i] > 0.f) denom += pl[i] * expf(pm[i] - mx);
+  // A row no partition wrote anything for (its sums zeroed by the caller) is not this kernel's:
+  // in a step that mixes prompt portions with single tokens, the portions' rows were stored by
+  // their own kernel and only the single tokens' rows have partial results.
+  if (!(denom > 0.f)) return;
   const int e = threadIdx.x;  // the launch gives hd <= blockDim.x a thread per element, else strides
   float a[2] = {0.f, 0.f};    // up to two elements per thread (head sizes to 512 with 256 threads)
   for (int i0 = 0; i0 < NP; i0 += kReduceChunk) {

@@ -156,12 +156,24 @@ def _paged_attention_mma(q, out, k_cache, v_cache, block_tables, req_q_start, re
             ptr(gemm_status(q.device)), stream()))  # fmt: skip
         if not has_short:
             return out
-        # what is left for the decode kernel: the short rows, unpartitioned (the reduction over
-        # partitions covers every row of the step, and the long rows have no partial results)
+        # What is left for the decode kernel: the short rows, with the key partitions their number
+        # and context call for (a decoding request beside a prompt portion has as long a context
+        # as in a step of its own). The merge runs over every row of the step and leaves alone the
+        # rows that have no partial results: their sums are zeroed here, and the portions' rows
+        # were stored by the kernel above.
+        ps, np_ = partitions or plan_decode_partitions(short_rows, KV, H // KV, max_context, win, hd)
+        part_m = part_l = part_acc = None
+        if np_ > 1:
+            part_m = torch.empty(T * H * np_, device=q.device, dtype=torch.float32)
+            part_l = torch.zeros(T * H * np_, device=q.device, dtype=torch.float32)
+            part_acc = torch.empty(T * H * np_ * hd, device=q.device, dtype=torch.float32)
         check(lib().asb_paged_attention_mma(
             ptr(out), ptr(q), ptr(k_cache), ptr(v_cache), ptr(block_tables), ptr(req_q_start),
-            ptr(req_pos_start), None, None, None, T, num_requests, H, KV, hd, bs,
-            block_tables.shape[1], win, 1 << 30, 1, float(scale), 1, 0, 0, stream()))  # fmt: skip
+            ptr(req_pos_start), ptr(part_m), ptr(part_l), ptr(part_acc), T, num_requests, H, KV, hd, bs,
+            block_tables.shape[1], win, ps, np_, float(scale), 1, 0, 0, stream()))  # fmt: skip
+        if np_ > 1:
+            check(lib().asb_attention_reduce(ptr(out), ptr(part_m), ptr(part_l), ptr(part_acc), T * H, np_, hd,
+                                             dtype_code(q), stream()))  # fmt: skip
         return out
     ps, np_ = 1 << 30, 1
     if has_short and not has_long:

@@ -242,6 +242,9 @@ ATTN_CASES = [
     (16, 4, 128, 16, [600, 200], [600, 8], 100),
     (6, 3, 64, 4, [200, 77, 24, 25], [1, 30, 24, 2], 24),
     (8, 8, 128, 16, [130], [130], None),
+    # prompt portions beside single tokens of long requests: the single tokens keep their key partitions
+    (8, 2, 128, 16, [2065, 1000, 300, 3000], [1, 1, 200, 1], None),
+    (8, 2, 128, 16, [3000, 64, 2500], [1, 64, 3], 700),
 ]
 
 
@@ -257,7 +260,7 @@ def test_paged_attention(ops, dtype, case):
     for generic in (True, False):  # the general kernel, then whichever kernel serving would pick
         out = ops.paged_attention(**dev, **common, generic=generic, host_q_lens=q_lens)
         assert torch.allclose(out.float().cpu(), ref, **t), f"generic={generic}"
-        if generic or max(q_lens) <= 8:
+        if generic or max(q_lens) <= 8 or (dtype == torch.bfloat16 and hd == 128 and min(q_lens) <= 8):
             out2 = ops.paged_attention(**dev, **common, generic=generic, host_q_lens=q_lens, partitions=parts)
             assert torch.allclose(out2.float().cpu(), ref, **t), f"generic={generic} partitioned"
     out3 = ops.paged_attention(**dev, **common)  # without host knowledge of the portions
