@@ -112,13 +112,16 @@ class Scheduler:
 
     def _resident_pass(self, plan: SchedulerOutput, budget: int) -> int:
         residents, reserve = self.running, self.cache.reserve
+        granted, counts = plan.seqs.append, plan.num_new_tokens.append
         # Evictions only ever shorten the list behind the sequence whose turn it is (or remove that
         # sequence itself, which is then the last), so walking by index meets each survivor once.
         turn = 0
         while turn < len(residents):
             seq = residents[turn]
             turn += 1
-            ask = min(len(seq.token_ids) - seq.num_computed_tokens, budget)
+            ask = len(seq.token_ids) - seq.num_computed_tokens
+            if ask > budget:
+                ask = budget
             if ask <= 0:
                 continue  # the budget is spent: it keeps what it holds and waits a step
             while not reserve(seq.cache, seq.num_computed_tokens, ask):
@@ -127,7 +130,8 @@ class Scheduler:
                 if victim is seq:
                     break
             else:
-                plan.grant(seq, ask)
+                granted(seq)
+                counts(ask)
                 budget -= ask
         return budget
 
