@@ -364,7 +364,7 @@ class ModelRunner:
         dummy requests when every row wants its logits, as in generation), table width (rounded
         up to a power of two), wanted rows, and the bucket of the longest context (which sets
         the key partitions). At most GraphCache.limit graphs are kept, and they share one pool of
-        memory and one logits buffer, [largest batch bucket, vocab] float32: 39 MB at 64 requests
+        memory and one logits buffer, [the batch bucket of the engine's sequence limit, vocab] float32: 39 MB at 64 requests
         of a 151,936-token vocabulary, 156 MB at 256. The returned logits are a view of that
         buffer: read them before the next step."""
         bs = self.block_size
@@ -377,8 +377,11 @@ class ModelRunner:
         self._bind(groups)
         out_rows = key[3]
         if self._graph_logits is None or self._graph_logits.shape[0] < out_rows:
+            # once, for the largest batch the state slots allow (a batch that grows step by step
+            # would otherwise replace the buffer, and with it every graph, at each new bucket)
+            largest = batch_bucket(min(self.cache.state.num_slots, GRAPH_BATCHES[-1])) or GRAPH_BATCHES[-1]
             self._graphs.clear()  # they write into the buffer that is being replaced
-            self._graph_logits = torch.empty(out_rows, self.model.spec.vocab_size, device=self.device, dtype=torch.float32)
+            self._graph_logits = torch.empty(max(out_rows, largest), self.model.spec.vocab_size, device=self.device, dtype=torch.float32)
         logits = self._graph_logits[:out_rows]
         entry = self._graphs.get(key)
         if entry is None:

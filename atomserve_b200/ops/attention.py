@@ -13,6 +13,7 @@ from atomserve_b200.ops.library import KernelLibraryError, check, dtype_code, li
 KEY_TILE = 32
 TARGET_BLOCKS = 296  # two blocks for each of the 148 SMs before the key range is split
 SHORT_ROWS = 8  # requests with at most this many new tokens run row by row in the decode kernel
+MIXED_SCRATCH_BYTES = 128 << 20  # most that a mixed step's partial results may take (see _paged_attention_mma)
 
 
 # Which kernel serves prompt portions in bfloat16 with head size 128: "tcgen05" (scores and output
@@ -162,6 +163,12 @@ def _paged_attention_mma(q, out, k_cache, v_cache, block_tables, req_q_start, re
         # rows that have no partial results: their sums are zeroed here, and the portions' rows
         # were stored by the kernel above.
         ps, np_ = partitions or plan_decode_partitions(short_rows, KV, H // KV, max_context, win, hd)
+        # The partial results are indexed by the step's rows, portions' rows included, so their
+        # size goes with the whole step: where a large portion would make them large (a portion of
+        # 8,192 tokens of 64 heads: 270 MB a partition), the single tokens run unpartitioned, as
+        # they do in any step whose portions fill the device by themselves.
+        if partitions is None and T * H * np_ * (hd + 2) * 4 > MIXED_SCRATCH_BYTES:
+            ps, np_ = 1 << 30, 1
         part_m = part_l = part_acc = None
         if np_ > 1:
             part_m = torch.empty(T * H * np_, device=q.device, dtype=torch.float32)
