@@ -7,7 +7,7 @@
 // (atomserve/model.py:199-232).
 //
 // One block per (request, tile of QT query tokens, kv head). Its 128 rows are the (token, head)
-// pairs of the tile, QT = 128 / G tokens times the G query heads of the kv head, loaded as one
+// pairs of the tile, QT = 128 / G tokens (rounded down) times the G query heads of the kv head, loaded as one
 // 3-D TMA box of q [T, H, hd]. Keys are visited in tiles of 64 at absolute multiples of 64.
 //
 //   warp 0     TMA: the Q tile once, then per key tile the pages of K and of V named by the
@@ -155,7 +155,9 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
     // The whole warp looks up the pages of a key tile (one page per lane, the loads in flight
     // together); lane 0 waits for the stage, and the lanes issue the tile's TMA loads together.
     if (lane == 0) {
-      mbar_expect_tx(q_full, kQBytes);
+      // the box is QT tokens by G heads: 128 rows when G divides 128, fewer otherwise (the rows
+      // after them are padding: never real, masked out, stored nowhere)
+      mbar_expect_tx(q_full, (uint32_t)(2 * p.QT * p.G * 128));
       tma_load_3d(q_smem, &map_q, q_full, 0, head0, row0);
       tma_load_3d(q_smem + kBlockBytes, &map_q, q_full, 64, head0, row0);
     }
@@ -296,7 +298,7 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
       // 256 in the probabilities, harmless in float32 sums and bfloat16 operands); otherwise the
       // older maximum stays and neither the sum nor the accumulator needs rescaling.
       float corr = 1.f;
-      if (tile_max > m + 8.f || m == -INFINITY) {
+      if (tile_max > m + 8.f || (m == -INFINITY && tile_max > -INFINITY)) {  // a row that has still seen nothing stays as it is
         const float m_new = fmaxf(m, tile_max);
         const float m_ref = m_new == -INFINITY ? 0.f : m_new;  // a row that has seen nothing yet
         corr = fast_exp2(m - m_ref);  // 0 when m was -inf
@@ -387,12 +389,13 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
 
 }  // namespace
 
-// 1 if the tcgen05 prefill kernel serves this shape: head size 128, a power-of-two group of at
-// most 16 query heads per kv head, pages of 8 to 256 tokens (a power of two).
+// 1 if the tcgen05 prefill kernel serves this shape: head size 128, 1 to 16 query heads per kv
+// head (a tile is 128 / group tokens, so a group that does not divide 128 leaves a few padding
+// rows), pages of 8 to 256 tokens (a power of two).
 extern "C" int asb_attention_tcgen05_supported(int hd, int group, int block_size) {
-  const bool pow2_group = group >= 1 && group <= 16 && (group & (group - 1)) == 0;
+  const bool group_ok = group >= 1 && group <= 16;
   const bool pow2_page = block_size >= 8 && block_size <= 256 && (block_size & (block_size - 1)) == 0;
-  return hd == 128 && pow2_group && pow2_page ? 1 : 0;
+  return hd == 128 && group_ok && pow2_page ? 1 : 0;
 }
 
 // Attention for every request that brings more than 8 tokens in this step (others are left

@@ -540,6 +540,10 @@ TCGEN05_ATTN_CASES = [
     (16, 2, 64, [1000], [333], 200),
     (16, 1, 128, [300, 150], [100, 150], 64),
     (8, 2, 16, [2048], [2048], None),
+    # groups that do not divide 128: 25, 42 and 18 tokens a tile, the last rows of a tile padding
+    (40, 8, 16, [700, 90, 300], [300, 90, 1], None),
+    (6, 2, 16, [500], [500], 130),
+    (7, 1, 32, [333, 64], [200, 64], None),
 ]
 
 
