@@ -41,6 +41,9 @@
 #include "gemm_partials.cuh"
 #include "tcgen05.cuh"
 
+// How the pair kernel cuts its last round of tiles along K (gemm_tcgen05_pair.cu).
+extern "C" long long asb_gemm_tcgen05_pair_cut(int M, int N, int K, int bn, int* out3);
+
 namespace {
 
 using asb::block_of;
@@ -574,68 +577,94 @@ int stage_room(int bn_kernel) {
   }
 }
 
-// How a shape is run. One block runs per SM. Operands swap (weights fill the 128-row MMA, tokens
-// are its N = 16..256) for up to 32 tokens always, and for up to 256 tokens where the unswapped
-// tiles of 128 x 256 would leave over half of the SMs idle (few weight rows: qkv, o, down); where
-// they fill the machine (gate/up, the head) whole unswapped tiles win from 33 tokens on (measured
-// on the 8B and 14B shapes). Up to 512 tokens the operands also swap where K is long (128 K blocks
-// or more: down) and the unswapped tiles would fill under 70 % of the SMs: the partial sums of a
-// 128 x 256 tile then cost less than the idle SMs (down at 300-512 tokens: 68 to 47-52 us on the 8B
-// shape); with K of 64-80 blocks they cost more (qkv: 27 to 35 us). With swapped operands, whole tiles are dealt round-robin unless
-// cutting the flattened K-block sequence into equal ranges shortens the busiest SM's share of the
-// operand stream by more than the partial sums cost to write and read back; unswapped tiles are
-// never cut (their partial sums, 128 KB a tile, cost more than the idle SMs: measured).
+// How a shape is run. One block runs per SM (or one pair of blocks per pair of SMs).
+//
+// Up to 128 tokens the operands swap (weights fill the 128-row MMA, tokens are its N = 16..256)
+// always for up to 32 tokens, and beyond where the unswapped tiles of 128 x 256 would leave over
+// half of the SMs idle (few weight rows: qkv, o, down); where they fill the machine (gate/up, the
+// head) whole unswapped tiles win from 33 tokens on (measured on the 8B and 14B shapes).
+//
+// With more than 128 tokens the forms are compared by an estimate of their time in microseconds,
+// a fixed part plus rounds of tiles times K blocks times the form's time per K block, with
+// constants fitted to the twelve projection shapes of Qwen3-8B, -14B and -32B at 200 to 2,048
+// tokens (over those 84 cases the estimate's choice is within 0.1 % of the best form's time
+// summed, and never more than 3.2 % behind it on one):
+//   unswapped tiles of 128 tokens by bn weight rows, bn a multiple of 32 from 64 to 256 (the
+//     epilogue reads 32 columns at a time): up to 128 rows in the 128-column kernel (six stages),
+//     wider ones in the 256-column kernel with as many stages as fit; an SM's time per K block
+//     goes with the bytes it takes in, so narrower tiles that occupy more SMs win where wide
+//     ones leave SMs idle, as long as they need no further round;
+//   tiles of 256 tokens by 128 or 256 weight rows on pairs of SMs (gemm_tcgen05_pair.cu), whose
+//     last round can be cut along K: twice the arithmetic per byte taken in, so with enough
+//     tiles to fill the device the 256-row tile wins (gate/up at 2,048 tokens: 339 -> 268 us, the
+//     vendor library 284), and the 128-row tile where there are few weight rows and a few
+//     hundred tokens (o at 512 tokens on the 14B shape: 34.5 -> 27.6 us);
+//   swapped operands with the flattened K-block sequence cut into equal ranges, up to 512 tokens:
+//     the partial sums cost about 14 us, which only long K over few tokens repays (down at 200).
+// With swapped operands, whole tiles are dealt round-robin unless cutting the flattened K-block
+// sequence into equal ranges shortens the busiest SM's share of the operand stream by more than
+// the partial sums cost to write and read back; unswapped single-SM tiles are never cut.
 Plan make_plan(int M, int N, int K) {
   Plan pl;
+  const int sms_now = sm_count();
   const int unswapped_tiles = ((M + BM - 1) / BM) * ((N + 255) / 256);
   const int kb_per_tile = (K + BK - 1) / BK;
-  pl.swap = M <= 32 || (M <= 256 && 2 * unswapped_tiles < sm_count()) ||
-            (M <= 512 && kb_per_tile >= 128 && 1.4 * unswapped_tiles < sm_count()) ? 1 : 0;
-  pl.bn = pl.swap ? (M <= 16 ? 16 : (M <= 32 ? 32 : (M <= 64 ? 64 : (M <= 128 ? 128 : 256)))) : (N <= 128 ? 128 : 256);
-  if (g_force_swap >= 0) pl.swap = g_force_swap == 1 ? 1 : 0;
-  if (g_force_swap >= 0 && pl.swap) pl.bn = M <= 16 ? 16 : (M <= 32 ? 32 : (M <= 64 ? 64 : (M <= 128 ? 128 : 256)));
+  pl.pair = 0;
+  pl.swap = M <= 32 || (M <= BM && 2 * unswapped_tiles < sms_now) ? 1 : 0;
+  pl.bn = pl.swap ? (M <= 16 ? 16 : (M <= 32 ? 32 : (M <= 64 ? 64 : 128))) : (N <= 128 ? 128 : 256);
   pl.bn_kernel = pl.bn;
-  if (!pl.swap && N > 128) {
-    // Unswapped tiles are 128 tokens by bn weight rows, bn a multiple of 32 from 64 to 256. An
-    // SM's time per K block goes with the bytes it takes in, the tokens' box (16 KB) and bn weight
-    // rows, so where 256-row tiles leave SMs idle (one row of tiles over few tokens, or few weight
-    // rows under a few hundred tokens), narrower tiles that spread the weight rows over more SMs
-    // are faster as long as they need no further wave. Tiles of up to 128 rows run in the
-    // 128-column kernel (six stages; o at 512 tokens 26.3 -> 21.5 us against the 256-column
-    // kernel's four), wider ones in the 256-column kernel with as many stages as fit beside them
-    // (which by itself gains nothing: 224 rows on five stages run like 256 on four, measured).
-    const int sms_now = sm_count();
-    const int token_tiles = (M + BM - 1) / BM;
+  if (M <= BM && !pl.swap && N > 128) {
+    // one row of unswapped tiles: the narrowest tiles that need no further round (time per K
+    // block goes with the bytes taken in, the tokens' box and bn weight rows)
     double best = 1e30;
-    for (int bn = 256; bn >= 64; bn -= 32) {  // multiples of 32: the epilogue reads 32 columns at a time
-      const int tiles = token_tiles * ((N + bn - 1) / bn);
+    for (int bn = 256; bn >= 64; bn -= 32) {
+      const int tiles = (N + bn - 1) / bn;
       const double cost = (double)((tiles + sms_now - 1) / sms_now) * (128 + bn);
       if (cost < best) { best = cost; pl.bn = bn; pl.bn_kernel = bn <= 128 ? 128 : 256; }
     }
-    if (g_force_bn && g_force_swap != 2) { pl.bn = g_force_bn; pl.bn_kernel = g_force_bn <= 128 ? 128 : 256; }
   }
-  // More than 128 tokens can also run on pairs of SMs: tiles of 256 tokens by 128 or 256 weight
-  // rows, each SM bringing its half (gemm_tcgen05_pair.cu). Microseconds per K block and SM,
-  // measured on the 8B shapes at 512 to 4,096 tokens: 0.39 for a single SM's 128 x 256 tile (0.355
-  // for 192 rows), 0.20 for tiles of up to 128 rows in the
-  // 128-column kernel; 0.33 for a pair's 256 x 256 tile, 0.225 for 256 x 128. The pair's tile is
-  // twice the arithmetic, so with enough tiles to fill the device it wins (gate/up at 2,048 tokens:
-  // 339 -> 268 us, the vendor library 284); with few tiles the narrow single tiles that occupy
-  // more SMs do.
-  pl.pair = 0;
-  if (!pl.swap && M > BM) {
-    const int sms_now = sm_count(), kb = (K + BK - 1) / BK;
-    const int single_tiles = ((M + BM - 1) / BM) * ((N + pl.bn - 1) / pl.bn);
-    const double single_kb = pl.bn_kernel == 128 ? 0.20 * (128 + pl.bn) / 256.0 : 0.25 + 0.14 * pl.bn / 256.0;
-    double best = (double)((single_tiles + sms_now - 1) / sms_now) * kb * single_kb;
-    for (int bn = 256; bn >= 128; bn -= 128) {
-      const int tiles = ((M + 255) / 256) * ((N + bn - 1) / bn), pairs = sms_now / 2;
-      const double cost = (double)((tiles + pairs - 1) / pairs) * kb * (bn == 256 ? 0.33 : 0.225);
-      if (cost < best * 0.97) { best = cost; pl.pair = bn; }
+  if (M > BM && g_force_swap < 0) {
+    const double kb = kb_per_tile;
+    const int token_tiles = (M + BM - 1) / BM, pairs = sms_now / 2;
+    double best = 1e30;
+    if (N > 128) {
+      for (int bn = 256; bn >= 64; bn -= 32) {
+        const int tiles = token_tiles * ((N + bn - 1) / bn);
+        const double per_kb = bn <= 128 ? 0.175 + 0.0655 * bn / 128.0 : 0.2353 + 0.1835 * bn / 256.0;
+        const double cost = 4.07 + (double)((tiles + sms_now - 1) / sms_now) * kb * per_kb;
+        if (cost < best) { best = cost; pl.swap = 0; pl.pair = 0; pl.bn = bn; pl.bn_kernel = bn <= 128 ? 128 : 256; }
+      }
+    } else {
+      best = 4.07 + (double)((token_tiles + sms_now - 1) / sms_now) * kb * 0.2405;
+      pl.swap = 0; pl.bn = pl.bn_kernel = 128;
     }
-    if (g_force_swap == 0) pl.pair = 0;
+    for (int bn = 256; bn >= 128; bn -= 128) {
+      const int tiles = ((M + 255) / 256) * ((N + bn - 1) / bn);
+      const double per_kb = bn == 256 ? 0.3344 : 0.2;
+      double cost = (double)((tiles + pairs - 1) / pairs) * kb * per_kb;
+      int cut[3];
+      const long long floats = asb_gemm_tcgen05_pair_cut(M, N, K, bn, cut);
+      if (floats > 0)  // the last round cut along K: its pieces, and their sums written and read back
+        cost = (double)(cut[0] / pairs) * kb * per_kb + 2.0 * cut[2] * per_kb + 3.26 + 8.0 * floats / 3.107e6;
+      cost += 4.37;
+      if (cost < best) { best = cost; pl.swap = 0; pl.pair = bn; }
+    }
+    if (M <= 512) {
+      const double share = (double)((N + BM - 1) / BM) * ((M + 255) / 256) * kb / sms_now;  // K blocks per SM
+      const double cost = 14.04 + (share < 4 ? 4 : share) * 0.45;
+      if (cost < best) { best = cost; pl.swap = 1; pl.pair = 0; pl.bn = pl.bn_kernel = 256; }
+    }
   }
-  if (g_force_swap == 2 && M > BM) { pl.swap = 0; pl.pair = g_force_bn == 128 ? 128 : 256; }
+  if (g_force_swap >= 0) {  // the tuning aid's choice
+    pl.swap = g_force_swap == 1 ? 1 : 0;
+    pl.pair = g_force_swap == 2 && M > BM ? (g_force_bn == 128 ? 128 : 256) : 0;
+    if (pl.swap) pl.bn = pl.bn_kernel = M <= 16 ? 16 : (M <= 32 ? 32 : (M <= 64 ? 64 : (M <= 128 ? 128 : 256)));
+    else if (N <= 128) pl.bn = pl.bn_kernel = 128;
+    else {
+      pl.bn = g_force_bn && g_force_swap != 2 ? g_force_bn : 256;
+      pl.bn_kernel = pl.bn <= 128 ? 128 : 256;
+    }
+  }
   pl.stage_size = BM * BK * 2 + ((pl.bn * BK * 2 + 1023) / 1024) * 1024;
   pl.stages = stage_room(pl.bn_kernel) / pl.stage_size;
   if (pl.stages > Config<256>::kMaxStages) pl.stages = Config<256>::kMaxStages;
@@ -663,6 +692,10 @@ Plan make_plan(int M, int N, int K) {
   if (pl.pair) pl.stream = 0;
   pl.max_slots = 0;
   pl.workspace = 0;
+  if (pl.pair) {
+    int cut[3];
+    pl.workspace = asb_gemm_tcgen05_pair_cut(M, N, K, pl.pair, cut);
+  }
   if (pl.stream) {
     const long long shortest = total / pl.blocks;  // the shortest range
     pl.max_slots = (int)((pl.kb_per_tile + shortest - 1) / shortest) + 1;
@@ -689,7 +722,7 @@ int launch(const CUtensorMap& mp, const CUtensorMap& mq, const GemmParams& p, co
 
 // The form for many tokens on pairs of SMs (gemm_tcgen05_pair.cu).
 extern "C" int asb_gemm_tcgen05_pair(void* out, const void* x, const void* w, const void* residual, int M, int N,
-                                     int K, int mode, int bn, int* status, cudaStream_t stream);
+                                     int K, int mode, int bn, float* workspace, int* status, cudaStream_t stream);
 
 // Float32 workspace elements a call needs (0 when every tile is computed whole).
 extern "C" long long asb_gemm_tcgen05_workspace(int M, int N, int K, int* stream_out) {
@@ -711,7 +744,8 @@ extern "C" void asb_gemm_tcgen05_tune(int swap, int bn) { g_force_swap = swap; g
 // How a shape is run: out8 = {cuts K (1) or whole tiles (0), swapped operands, workspace slots per
 // tile, token columns (swapped) or weight rows (unswapped) per tile, K blocks per tile, tiles,
 // thread blocks, weight rows of the tiles of pairs of SMs (0: single SMs)}. With pairs, a tile is
-// 256 tokens by that many weight rows and two thread blocks share it. A shape that cuts K with
+// 256 tokens by that many weight rows and two thread blocks share it; how the last round of
+// tiles is cut along K, asb_gemm_tcgen05_pair_cut tells. A shape that cuts K with
 // swapped operands can leave its product as partial sums (mode 3 of asb_gemm_tcgen05), which
 // csrc/gemm_partials.cuh describes.
 extern "C" int asb_gemm_tcgen05_plan(int M, int N, int K, int* out8) {
@@ -722,7 +756,9 @@ extern "C" int asb_gemm_tcgen05_plan(int M, int N, int K, int* out8) {
   out8[7] = pl.pair;
   if (pl.pair) {
     const int tiles = ((M + 255) / 256) * ((N + pl.pair - 1) / pl.pair), pairs = sm_count() / 2;
-    out8[3] = pl.pair; out8[5] = tiles; out8[6] = 2 * (tiles < pairs ? tiles : pairs);
+    int cut[3];
+    asb_gemm_tcgen05_pair_cut(M, N, K, pl.pair, cut);  // with few tiles, cut[1] pairs share each
+    out8[3] = pl.pair; out8[5] = tiles; out8[6] = 2 * (tiles < pairs ? tiles * cut[1] : pairs);
   }
   return 0;
 }
@@ -752,7 +788,7 @@ extern "C" int asb_gemm_tcgen05(void* out, const void* x, const void* w, const v
   if (mode == 3 && !(pl.stream && pl.swap && pl.tiles_q == 1))
     return asb::fail("gemm_tcgen05: [%d, %d] x [%d, %d] does not run with partial sums", M, K, N, K);
   if (pl.pair && mode != 3)
-    return asb_gemm_tcgen05_pair(out, x, w, residual, M, N, K, mode, pl.pair, status, stream);
+    return asb_gemm_tcgen05_pair(out, x, w, residual, M, N, K, mode, pl.pair, workspace, status, stream);
   if (pl.workspace > 0 && !workspace) return asb::fail("gemm_tcgen05: this shape needs a workspace of %lld floats", pl.workspace);
 
   GemmParams p;

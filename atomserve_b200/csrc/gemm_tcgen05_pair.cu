@@ -44,6 +44,14 @@ struct PairParams {
   int epilogue;
   int tiles_m, num_tiles;  // tile t -> tokens (t % tiles_m) * 256, weight rows (t / tiles_m) * BN
   int kb_per_tile;
+  // The last, partial round of tiles can be cut along K so that every pair has a share of it:
+  // tiles [0, whole_tiles) are dealt whole, round-robin; each later tile is computed by `split`
+  // pairs, piece j taking the stages [j * piece_stages, (j + 1) * piece_stages) of the tile's K
+  // and leaving its float32 sums in workspace slot (tile - whole_tiles) * split + j, a slot being
+  // [256 tokens][BN]; tail_reduce_kernel adds the slots up and stores the result. With
+  // whole_tiles = num_tiles nothing is cut.
+  float* workspace;
+  int whole_tiles, split, piece_stages;
 };
 
 template <int BN>
@@ -150,9 +158,19 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid
   cluster_sync();  // both CTAs' barriers exist before either signals into the other
   fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
-  const int per_pair = p.num_tiles > pair ? (p.num_tiles - pair + pairs - 1) / pairs : 0;
+  // This pair's work: its whole tiles (pair, pair + pairs, ... below whole_tiles), then at most
+  // one piece of a tile of the cut round.
   const int stages_per_tile = (p.kb_per_tile + C::kSub - 1) / C::kSub;  // a K block beyond K is filled with zeros
-  const uint32_t total = (uint32_t)per_pair * (uint32_t)stages_per_tile;  // stages this pair runs
+  const int n_whole = p.whole_tiles > pair ? (p.whole_tiles - pair + pairs - 1) / pairs : 0;
+  const int cut_tiles = p.num_tiles - p.whole_tiles;
+  const bool has_piece = pair < cut_tiles * p.split;
+  const int piece_tile = p.whole_tiles + (has_piece ? pair / p.split : 0);
+  const int piece_begin = has_piece ? (pair % p.split) * p.piece_stages : 0;
+  const int piece_len = has_piece ? min(p.piece_stages, stages_per_tile - piece_begin) : 0;
+  const int n_items = n_whole + (piece_len > 0 ? 1 : 0);
+  const uint32_t total = (uint32_t)n_whole * (uint32_t)stages_per_tile + (uint32_t)piece_len;  // stages this pair runs
+  auto item_tile = [&](int i) { return i < n_whole ? pair + i * pairs : piece_tile; };
+  auto item_len = [&](int i) { return i < n_whole ? stages_per_tile : (i < n_items ? piece_len : 0x3fffffff); };
 
   if (warp == 0 || warp >= 6) {
     if (lane == 0 && (warp == 0 ? 0 : warp - 5) < C::kLoaders) {  // a spare loader warp has nothing to do
@@ -163,17 +181,20 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid
       // switched off: 714 cycles per K block with one loader, 353 with four). The tile and its
       // rows are carried along instead of being divided out of the stage count each time.
       const int me = warp == 0 ? 0 : warp - 5;
-      int t = pair, ks = 0, s = 0;   // tile, stage within the tile, slot
+      int item = 0, ks = 0, s = 0;   // work item, stage within it, slot
+      int len = item_len(0);
       uint32_t phase = 0;
-      int x0 = 0, w0 = 0;
+      int x0 = 0, w0 = 0, k0 = 0;    // the item's token rows, weight rows and first stage of K
       auto place = [&]() {
+        const int t = item_tile(item);
         x0 = (t % p.tiles_m) * 256 + (int)rank * BM;
         w0 = (t / p.tiles_m) * BN + (int)rank * (BN / 2);
+        k0 = item < n_whole ? 0 : piece_begin;
       };
       auto advance = [&](int by) {
         ks += by;
         bool moved = false;
-        while (ks >= stages_per_tile) { ks -= stages_per_tile; t += pairs; moved = true; }
+        while (ks >= len) { ks -= len; len = item_len(++item); moved = true; }
         if (moved) place();
         s += by;  // by <= kLoaders <= kStages: at most one turn of the ring
         if (s >= C::kStages) { s -= C::kStages; phase ^= 1u; }
@@ -183,17 +204,17 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid
       // the weights, which no kernel writes, fill the pipeline before the wait for the previous kernel
       const uint32_t ahead = total < (uint32_t)C::kStages ? total : (uint32_t)C::kStages;
       {
-        const int t1 = t, ks1 = ks, s1 = s;
+        const int item1 = item, ks1 = ks, s1 = s, len1 = len;
         const uint32_t phase1 = phase;
         for (uint32_t it = me; it < ahead; it += C::kLoaders) {
           const uint32_t bar = cluster_address(full_bar(s), 0);
           mbar_expect_tx_cluster(bar, C::kStage);
 #pragma unroll
           for (int j = 0; j < C::kSub; ++j)
-            tma_load_2d_pair(base + s * C::kStage + C::kSub * C::kA + j * C::kB, &map_w, bar, (ks * C::kSub + j) * BK, w0);
+            tma_load_2d_pair(base + s * C::kStage + C::kSub * C::kA + j * C::kB, &map_w, bar, ((k0 + ks) * C::kSub + j) * BK, w0);
           advance(C::kLoaders);
         }
-        t = t1; ks = ks1; s = s1; phase = phase1;
+        item = item1; ks = ks1; s = s1; len = len1; phase = phase1;
         place();
       }
       asb::pdl_wait();
@@ -206,10 +227,10 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid
           mbar_expect_tx_cluster(bar, C::kStage);
 #pragma unroll
           for (int j = 0; j < C::kSub; ++j)
-            tma_load_2d_pair(dst + C::kSub * C::kA + j * C::kB, &map_w, bar, (ks * C::kSub + j) * BK, w0);
+            tma_load_2d_pair(dst + C::kSub * C::kA + j * C::kB, &map_w, bar, ((k0 + ks) * C::kSub + j) * BK, w0);
         }
 #pragma unroll
-        for (int j = 0; j < C::kSub; ++j) tma_load_2d_pair(dst + j * C::kA, &map_x, bar, (ks * C::kSub + j) * BK, x0);
+        for (int j = 0; j < C::kSub; ++j) tma_load_2d_pair(dst + j * C::kA, &map_x, bar, ((k0 + ks) * C::kSub + j) * BK, x0);
         advance(C::kLoaders);
       }
       if (me == 0) {
@@ -228,17 +249,17 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid
     asb::pdl_wait();
     if (lane == 0 && rank == 0) {
       constexpr uint32_t idesc = instr_desc_bf16(256, BN, false);
-      uint32_t it = 0, seg = 0;
       int s = 0;
       uint32_t phase = 0;
       bool ok = true;
-      for (int t = pair; ok && t < p.num_tiles; t += pairs, ++seg) {
+      for (uint32_t seg = 0; ok && seg < (uint32_t)n_items; ++seg) {
+        const int stages_here = item_len((int)seg);
         const uint32_t buf = seg & 1u;
         ok = mbar_wait(acc_empty(buf), ((seg >> 1) & 1u) ^ 1u, p.status, 34);
         if (!ok) break;
         fence_after_sync();
         const uint32_t tmem_acc = tmem_base + buf * BN;
-        for (int ks = 0; ks < stages_per_tile; ++ks, ++it) {
+        for (int ks = 0; ks < stages_here; ++ks) {
           ok = mbar_wait(full_bar(s), phase, p.status, 32);
           if (!ok) break;
           fence_after_sync();
@@ -261,9 +282,9 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid
     // Epilogue: this warp owns lanes 32 * (warp % 4) .. + 31 of this CTA's 128 token rows.
     asb::pdl_wait();
     const int quad = warp & 3;
-    uint32_t seg = 0;
     bool ok = true;
-    for (int t = pair; ok && t < p.num_tiles; t += pairs, ++seg) {
+    for (uint32_t seg = 0; ok && seg < (uint32_t)n_items; ++seg) {
+      const int t = item_tile((int)seg);
       const uint32_t buf = seg & 1u;
       int ok_i = 1;
       if (lane == 0) ok_i = mbar_wait(acc_full(buf), (seg >> 1) & 1u, p.status, 33) ? 1 : 0;
@@ -272,6 +293,23 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid
       fence_after_sync();
       const int row = (t % p.tiles_m) * 256 + (int)rank * BM + quad * 32 + lane;  // this thread's token
       const int n0 = (t / p.tiles_m) * BN;
+      if ((int)seg >= n_whole) {
+        // a piece of a cut tile: the sums go to this pair's workspace slot as they are
+        float* slot_row = p.workspace + ((size_t)pair * 256 + (size_t)((int)rank * BM + quad * 32 + lane)) * BN;
+#pragma unroll 1
+        for (int c = 0; c < BN; c += 32) {
+          if (n0 + c >= p.N) break;  // uniform
+          uint32_t raw[32];
+          tmem_ld32(tmem_base + ((uint32_t)(quad * 32) << 16) + buf * BN + (uint32_t)c, raw);
+#pragma unroll
+          for (int j = 0; j < 32; j += 4)
+            *reinterpret_cast<uint4*>(slot_row + c + j) = make_uint4(raw[j], raw[j + 1], raw[j + 2], raw[j + 3]);
+        }
+        fence_before_sync();
+        __syncwarp();
+        if (lane == 0) mbar_arrive_cluster(cluster_address(acc_empty(buf), 0));
+        continue;
+      }
 #pragma unroll 1
       for (int c = 0; c < BN; c += 32) {
         if (n0 + c >= p.N) break;  // uniform
@@ -354,6 +392,51 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid
   }
 }
 
+// Adds up the pieces of the tiles that the GEMM cut along K and stores them as the GEMM stores
+// whole tiles. grid = (cut tiles, pieces of a tile's 256 x BN elements); a thread owns four
+// consecutive weight rows of one token.
+template <int BN>
+__global__ void tail_reduce_kernel(const PairParams p) {
+  const int cut = blockIdx.x, tile = p.whole_tiles + cut;
+  const int i = (blockIdx.y * blockDim.x + threadIdx.x) * 4;
+  const int r = i / BN, c = i % BN;
+  const int row = (tile % p.tiles_m) * 256 + r, n = (tile / p.tiles_m) * BN + c;
+  asb::pdl_wait();  // the GEMM has completed
+  asb::pdl_launch_dependents();
+  if (i >= 256 * BN || row >= p.M || n >= p.N) return;
+  const float* ws = p.workspace + ((size_t)cut * p.split * 256 + r) * BN + c;
+  float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+  for (int j0 = 0; j0 < p.split; j0 += 4) {  // four loads in flight; the sum still runs in piece order
+    float4 a[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u)
+      if (j0 + u < p.split) a[u] = *reinterpret_cast<const float4*>(ws + (size_t)(j0 + u) * 256 * BN);
+#pragma unroll
+    for (int u = 0; u < 4; ++u)
+      if (j0 + u < p.split) { v.x += a[u].x; v.y += a[u].y; v.z += a[u].z; v.w += a[u].w; }
+  }
+  const float e[4] = {v.x, v.y, v.z, v.w};
+  if (p.epilogue == kStoreSwiGLU) {
+    __nv_bfloat16* o = (__nv_bfloat16*)p.out + (size_t)row * (p.ldo / 2) + n / 2;
+#pragma unroll
+    for (int k = 0; k < 4; k += 2)
+      if (n + k + 1 < p.N) o[k / 2] = __float2bfloat16_rn(swiglu(e[k], e[k + 1]));
+    return;
+  }
+  const size_t at = (size_t)row * p.ldo + n;
+#pragma unroll
+  for (int k = 0; k < 4; ++k) {
+    if (n + k >= p.N) break;
+    float o = e[k];
+    if (p.epilogue == kStoreF32) {
+      ((float*)p.out)[at + k] = o;
+    } else {
+      if (p.epilogue == kStoreBf16Residual) o += __bfloat162float(((const __nv_bfloat16*)p.residual)[at + k]);
+      ((__nv_bfloat16*)p.out)[at + k] = __float2bfloat16_rn(o);
+    }
+  }
+}
+
 int sm_count() {
   static int count = 0;
   if (!count) {
@@ -372,7 +455,7 @@ int launch_pairs(const CUtensorMap& mx, const CUtensorMap& mw, const PairParams&
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmem);
   if (e != cudaSuccess) return asb::fail("gemm_tcgen05_pair: shared memory %d: %s", C::kSmem, cudaGetErrorString(e));
   int pairs = sm_count() / 2;
-  if (p.num_tiles < pairs) pairs = p.num_tiles;
+  if (p.num_tiles < pairs) pairs = p.num_tiles * p.split;  // (the planner keeps tiles * split within the pairs)
   cudaLaunchConfig_t config = {};
   config.gridDim = dim3(2 * pairs);
   config.blockDim = dim3(kThreads);
@@ -390,17 +473,50 @@ int launch_pairs(const CUtensorMap& mx, const CUtensorMap& mw, const PairParams&
   asb::prefer_shared_carveout((const void*)kern);
   asb::count_launch();
   cudaLaunchKernelEx(&config, kern, mx, mw, p);
-  return asb::check_launch("gemm_tcgen05_pair");
+  if (int rc = asb::check_launch("gemm_tcgen05_pair")) return rc;
+  if (p.whole_tiles < p.num_tiles) {
+    asb::launch(tail_reduce_kernel<BN>, dim3(p.num_tiles - p.whole_tiles, 256 * BN / 4 / 256), 256, 0, stream, p);
+    return asb::check_launch("gemm_tcgen05_pair tail_reduce");
+  }
+  return 0;
 }
 
 }  // namespace
+
+// Whether, and how, the pair kernel cuts the last round of tiles along K. With fewer tiles left
+// over than half the pairs, `split` pairs share each of them, a piece being at least four stages
+// (eight K blocks), as long as the K blocks that the last round so saves outweigh what the pieces'
+// float32 sums cost to write and read back (a launch and about 3 TB/s). out3 = {tiles dealt
+// whole, pairs per cut tile, stages per piece}; returns the workspace's float32 elements.
+static int g_cut_enabled = 1;
+// Tuning aid: 0 keeps every tile whole in the calls that follow, 1 (the default) lets the last round be cut.
+extern "C" void asb_gemm_tcgen05_pair_tune(int cut) { g_cut_enabled = cut; }
+
+extern "C" long long asb_gemm_tcgen05_pair_cut(int M, int N, int K, int bn, int* out3) {
+  const int tiles = ((M + 255) / 256) * ((N + bn - 1) / bn), pairs = sm_count() / 2;
+  const int stages = ((K + BK - 1) / BK + 1) / 2;
+  out3[0] = tiles; out3[1] = 1; out3[2] = stages;
+  const int left = tiles % pairs;
+  if (!g_cut_enabled || left == 0 || 2 * left > pairs || stages < 8) return 0;
+  int split = pairs / left;
+  if (split > stages / 4) split = stages / 4;
+  if (split < 2) return 0;
+  const int piece = (stages + split - 1) / split;
+  split = (stages + piece - 1) / piece;  // no empty piece
+  const double us_per_stage = 2 * (bn == 256 ? 0.33 : 0.225);
+  const double bytes = (double)left * split * 256 * bn * 4 * 2;
+  if ((stages - piece) * us_per_stage <= 3.0 + bytes / 3.0e6) return 0;
+  out3[0] = tiles - left; out3[1] = split; out3[2] = piece;
+  return (long long)left * split * 256 * bn;
+}
 
 // out = x . w^T (+ residual) on pairs of SMs, for more than 128 tokens. x [M, K] and w [N, K]
 // bfloat16, contiguous, K a multiple of 8, both bases 16-byte aligned. mode 0: out bfloat16
 // (+ residual); 1: out float32; 2: SwiGLU (rows of w alternate gate and up; out [M, N / 2]).
 // bn: weight rows per pair tile, 128 or 256.
+// workspace: float32, asb_gemm_tcgen05_pair_cut(M, N, K, bn) elements (null if that is 0).
 extern "C" int asb_gemm_tcgen05_pair(void* out, const void* x, const void* w, const void* residual, int M, int N,
-                                     int K, int mode, int bn, int* status, cudaStream_t stream) {
+                                     int K, int mode, int bn, float* workspace, int* status, cudaStream_t stream) {
   if (mode < 0 || mode > 2) return asb::fail("gemm_tcgen05_pair: unknown mode %d", mode);
   if (mode == 2 && (residual || N % 2)) return asb::fail("gemm_tcgen05_pair: the SwiGLU form takes no residual and an even N");
   if (mode == 1 && residual) return asb::fail("gemm_tcgen05_pair: the float32 result form takes no residual");
@@ -420,6 +536,13 @@ extern "C" int asb_gemm_tcgen05_pair(void* out, const void* x, const void* w, co
   p.tiles_m = (M + 255) / 256;
   p.num_tiles = p.tiles_m * ((N + bn - 1) / bn);
   p.kb_per_tile = (K + BK - 1) / BK;
+  int cut[3];
+  const long long need = asb_gemm_tcgen05_pair_cut(M, N, K, bn, cut);
+  if (need > 0 && !workspace) return asb::fail("gemm_tcgen05_pair: this shape needs a workspace of %lld floats", need);
+  p.workspace = workspace;
+  p.whole_tiles = cut[0];
+  p.split = cut[1];
+  p.piece_stages = cut[2];
   alignas(64) CUtensorMap mx, mw;
   const cuuint64_t strides[1] = {(cuuint64_t)K * 2};
   const cuuint64_t dims_x[2] = {(cuuint64_t)K, (cuuint64_t)M}, dims_w[2] = {(cuuint64_t)K, (cuuint64_t)N};

@@ -161,6 +161,23 @@ def gemm_timeline(buffer: torch.Tensor | None) -> None:
     fn(ptr(buffer))
 
 
+def gemm_tune(swap: int = -1, rows: int = 0, cut_last_round: bool = True) -> None:
+    """Tuning aid: force how the tensor-core GEMM runs the calls that follow. swap 0: unswapped
+    tiles on single SMs, 1: swapped operands, 2: tiles on pairs of SMs, -1: the planner's choice;
+    rows: weight rows per unswapped tile (single SMs: a multiple of 32 from 64 to 256; pairs: 128
+    or 256; 0: the planner's); cut_last_round: whether the pair form may cut its last round of
+    tiles along K. The plans and workspace sizes remembered per shape are forgotten, because they
+    differ between the forms."""
+    tune = lib().asb_gemm_tcgen05_tune
+    tune.argtypes, tune.restype = [ctypes.c_int, ctypes.c_int], None
+    cut = lib().asb_gemm_tcgen05_pair_tune
+    cut.argtypes, cut.restype = [ctypes.c_int], None
+    tune(swap, rows)
+    cut(1 if cut_last_round else 0)
+    _WORKSPACE_FLOATS.clear()
+    _PLANS.clear()
+
+
 def tcgen05_supported(x: torch.Tensor, w: torch.Tensor) -> bool:
     return x.dtype == torch.bfloat16 and x.shape[1] % 8 == 0 and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0
 

@@ -727,8 +727,10 @@ def test_a_wait_that_runs_out_reports_frees_tensor_memory_and_returns(ops):
     assert torch.allclose(out.double().cpu(), x.double().cpu() @ w.double().cpu().T, atol=2e-2, rtol=1e-3)
 
 
+# the last three leave a last round of few tiles, which the kernel cuts along K (for one or both tile widths)
 PAIR_SHAPES = [(300, 512, 256), (257, 1000, 520), (129, 130, 72), (2048, 4096, 4096), (700, 6144, 4160),
-               (513, 24576, 1024), (1000, 256, 64), (3000, 384, 200), (640, 4104, 8)]  # fmt: skip
+               (513, 24576, 1024), (1000, 256, 64), (3000, 384, 200), (640, 4104, 8),
+               (1000, 5000, 4160), (300, 4000, 4160), (520, 1100, 2120)]  # fmt: skip
 
 
 @pytest.mark.parametrize("rows", [128, 256])
@@ -737,29 +739,29 @@ def test_gemm_tcgen05_on_pairs_of_sms(ops, M, N, K, rows):
     """The many-token form of the GEMM (tcgen05.mma.cta_group::2: two CTAs on a tile of 256 tokens
     by 128 or 256 weight rows), forced for shapes the planner would also give to single SMs: every
     epilogue against float64; tokens, weight rows and K that end inside a tile, an odd number of K
-    blocks (the second K block of the last stage lies beyond K), one tile, many tiles per pair."""
-    import ctypes
+    blocks (the second K block of the last stage lies beyond K), one tile, many tiles per pair, a
+    last round of tiles cut along K into pieces that a second kernel adds up."""
+    from atomserve_b200.ops.linear import check_gemm_status, gemm_tcgen05, gemm_tune
 
-    from atomserve_b200.ops.library import lib
-    from atomserve_b200.ops.linear import check_gemm_status, gemm_tcgen05
-
-    tune = lib().asb_gemm_tcgen05_tune
-    tune.argtypes, tune.restype = [ctypes.c_int, ctypes.c_int], None
     g = torch.Generator().manual_seed(M + N + K)
     x = torch.randn(M, K, generator=g).bfloat16().cuda()
     w = (torch.randn(N, K, generator=g) / math.sqrt(K)).bfloat16().cuda()
     res = torch.randn(M, N, generator=g).bfloat16().cuda()
     ref = x.double().cpu() @ w.double().cpu().T
-    tune(2, rows)
+    gemm_tune(2, rows)
     try:
         full = gemm_tcgen05(x, w, None, torch.float32)
         plain_out = gemm_tcgen05(x, w, None, torch.bfloat16)
         with_res = gemm_tcgen05(x, w, res, torch.bfloat16)
         fused = gemm_tcgen05(x, w, None, torch.bfloat16, swiglu=True) if N % 2 == 0 else None
         again = gemm_tcgen05(x, w, None, torch.float32)
+        gemm_tune(2, rows, cut_last_round=False)
+        uncut = gemm_tcgen05(x, w, None, torch.float32)
     finally:
-        tune(-1, 0)
+        gemm_tune()
     check_gemm_status()
+    # cut or whole, the same products are added, in another order
+    assert torch.allclose(uncut, full, atol=1e-4, rtol=1e-4)
     assert torch.allclose(full.double().cpu(), ref, atol=2e-3, rtol=1e-3), float((full.double().cpu() - ref).abs().max())
     assert torch.equal(again, full)
     assert torch.allclose(plain_out.double().cpu(), ref, atol=3e-2, rtol=2e-2)

@@ -54,7 +54,11 @@ def test_gemm_plans_keep_every_tile_within_its_partial_sum_slots():
         pytest.skip(f"the kernel library is not available: {error}")
     plan.argtypes = [ctypes.c_int] * 3 + [ctypes.POINTER(ctypes.c_int)]
     plan.restype = None
-    out = (ctypes.c_int * 8)()
+    pair_cut, workspace = lib().asb_gemm_tcgen05_pair_cut, lib().asb_gemm_tcgen05_workspace
+    pair_cut.argtypes, pair_cut.restype = [ctypes.c_int] * 4 + [ctypes.POINTER(ctypes.c_int)], ctypes.c_longlong
+    workspace.argtypes, workspace.restype = [ctypes.c_int] * 3 + [ctypes.POINTER(ctypes.c_int)], ctypes.c_longlong
+    out, cut = (ctypes.c_int * 8)(), (ctypes.c_int * 3)()
+    cut_plans = 0
     rng = random.Random(1)
     shapes = [(8, 4096, 4096), (1, 151936, 4096), (512, 4096, 12288), (2048, 24576, 4096), (300, 5120, 17408)]
     for _ in range(3000):
@@ -67,7 +71,20 @@ def test_gemm_plans_keep_every_tile_within_its_partial_sum_slots():
         assert kb == -(-K // 64) and 1 <= blocks <= 148, (M, N, K)
         if pair:  # tiles of 256 tokens by `pair` weight rows, two blocks (a pair of SMs) on each
             assert pair in (128, 256) and bn == pair and not swap and not cuts_k and M > 128, (M, N, K)
-            assert tiles == -(-M // 256) * -(-N // pair) and blocks == 2 * min(tiles, 74), (M, N, K)
+            assert tiles == -(-M // 256) * -(-N // pair), (M, N, K)
+            # the last round of tiles may be cut along K: whole rounds first, then `split` pairs on
+            # each tile left, every piece with stages to run, one workspace slot a piece
+            floats = pair_cut(M, N, K, pair, cut)
+            whole, split, piece = list(cut)
+            stages = -(-kb // 2)
+            assert workspace(M, N, K, None) == floats == ((tiles - whole) * split * 256 * pair if split > 1 else 0), (M, N, K)
+            if split == 1:
+                assert whole == tiles and blocks == 2 * min(tiles, 74), (M, N, K)
+            else:
+                cut_plans += 1
+                assert whole % 74 == 0 and 0 < tiles - whole and (tiles - whole) * split <= 74, (M, N, K)
+                assert (split - 1) * piece < stages <= split * piece and piece >= 4, (M, N, K)
+                assert blocks == 2 * (74 if whole else tiles * split), (M, N, K)
             continue
         p_rows, q_rows = (N, M) if swap else (M, N)
         assert tiles == -(-p_rows // 128) * -(-q_rows // bn), (M, N, K)
@@ -87,6 +104,7 @@ def test_gemm_plans_keep_every_tile_within_its_partial_sum_slots():
             first = bisect.bisect_right(begins, tile * kb) - 1
             last = bisect.bisect_right(begins, tile * kb + kb - 1) - 1
             assert last - first + 1 <= max_slots, (M, N, K, tile)
+    assert cut_plans > 20
 
 
 def test_decode_graph_keys_are_few_and_the_cache_of_graphs_is_bounded():
