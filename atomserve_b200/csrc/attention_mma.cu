@@ -45,6 +45,8 @@ struct MmaParams {
   int QT;                    // prefill: tokens per 128-row tile
   int window, PS, NP;
   int all_single;            // every request brings exactly one token: request = row
+  int short_rows;            // > 0: the decode kernel's grid and the partial results count only the rows of
+                             // requests with at most kShortRows tokens (a step that also holds longer portions)
   float scale;
 };
 
@@ -285,10 +287,13 @@ decode_attention_kernel(const MmaParams p) {
   const uint32_t q_tile = smem + 4 * kTileBytes;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int row = blockIdx.x;  // flat token row
+  int row = blockIdx.x;  // flat token row
   int r;
   if (p.all_single) {
     r = row;
+  } else if (p.short_rows > 0) {
+    row = asb::nth_short_row(p.req_q_start, p.R, kShortRows, blockIdx.x, &r);
+    if (row < 0) return;
   } else {
     r = find_request(p.req_q_start, p.R, row);
     if (p.req_q_start[r + 1] - p.req_q_start[r] > kShortRows) return;  // the prefill kernel's
@@ -437,7 +442,8 @@ decode_attention_kernel(const MmaParams p) {
     if (p.NP == 1) {
       p.out[orow * HD + col] = __float2bfloat16_rn(a / den);
     } else {
-      const size_t at = orow * p.NP + blockIdx.z;
+      const size_t prow = p.short_rows > 0 ? (size_t)blockIdx.x * p.H + head0 + qr : orow;
+      const size_t at = prow * p.NP + blockIdx.z;
       p.part_acc[at * HD + col] = a;
       if (col == 0) {
         p.part_m[at] = mx;
@@ -652,7 +658,7 @@ int launch_mma(const MmaParams& p, int run_decode, int run_prefill, cudaStream_t
     auto kern = decode_attention_kernel<HD>;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) return asb::fail("decode_attention: %s", cudaGetErrorString(e));
-    dim3 grid(p.T, p.KV * p.HC, p.NP);
+    dim3 grid(p.short_rows > 0 ? p.short_rows : p.T, p.KV * p.HC, p.NP);
     asb::launch(kern, grid, kThreads, smem, stream, p);
     if (int rc = asb::check_launch("decode_attention")) return rc;
   }
@@ -705,15 +711,20 @@ extern "C" int asb_attention_mma_supported(int hd, int group) {
 // portions use NP == 1. With NP > 1 every block writes (max, sum, accumulator) to the scratch
 // and the caller runs asb_attention_reduce over it afterwards. (Letting the last block to arrive
 // merge the partitions inside this kernel was measured and was slower than the second launch.)
+// short_rows > 0 (with run_decode alone): the number of rows of requests with at most 8 tokens in
+// a step that also holds longer portions; the decode kernel then starts blocks for those rows
+// only, and the scratch is [short_rows, H, NP(, hd)], merged by asb_attention_reduce_short.
 extern "C" int asb_paged_attention_mma(void* out, const void* q, const void* k_cache,
                                        const void* v_cache, const int* block_tables,
                                        const int* req_q_start, const int* req_pos_start,
                                        float* part_m, float* part_l, float* part_acc,
                                        int num_tokens, int R, int H, int KV, int hd, int bs,
                                        int table_width, int window, int PS, int NP, float scale,
-                                       int run_decode, int run_prefill, int all_single,
+                                       int run_decode, int run_prefill, int all_single, int short_rows,
                                        cudaStream_t stream) {
   if (num_tokens == 0 || R == 0) return 0;
+  if (short_rows < 0 || short_rows > num_tokens || (short_rows > 0 && (run_prefill || all_single)))
+    return asb::fail("paged_attention_mma: %d short rows of %d tokens (decode-only launches of mixed steps)", short_rows, num_tokens);
   if (KV < 1 || H % KV) return asb::fail("paged_attention_mma: %d heads over %d kv heads", H, KV);
   if (!asb_attention_mma_supported(hd, H / KV)) return asb::fail("paged_attention_mma: head_dim %d is not 64 or 128", hd);
   if (NP < 1 || PS < kKeyTile || PS % kKeyTile) return asb::fail("paged_attention_mma: partition size %d must be a positive multiple of %d", PS, kKeyTile);
@@ -731,7 +742,7 @@ extern "C" int asb_paged_attention_mma(void* out, const void* q, const void* k_c
   p.HC = (p.G + p.GC - 1) / p.GC;
   p.QT = kPrefillRows / p.GC;
   if (p.KV * p.HC > 65535) return asb::fail("paged_attention_mma: too many head chunks");
-  p.window = window; p.PS = PS; p.NP = NP; p.all_single = all_single; p.scale = scale;
+  p.window = window; p.PS = PS; p.NP = NP; p.all_single = all_single; p.short_rows = short_rows; p.scale = scale;
   if (hd == 64) return launch_mma<64>(p, run_decode, run_prefill, stream);
   return launch_mma<128>(p, run_decode, run_prefill, stream);
 }

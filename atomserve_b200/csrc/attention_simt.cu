@@ -202,14 +202,25 @@ paged_attention_kernel(const AttentionParams p) {
 // follow are unconditional and several are in flight.
 constexpr int kReduceChunk = 64;
 
-template <typename T>
+// Short: the partial results are those of the short rows only, [short rows, H, NP(, hd)] (a step
+// that mixes prompt portions with single tokens); block b merges head b % H of short row b / H
+// into that row's place in `out`.
+template <typename T, bool Short>
 __global__ void attention_reduce_kernel(T* __restrict__ out, const float* __restrict__ part_m,
                                         const float* __restrict__ part_l,
-                                        const float* __restrict__ part_acc, int NP, int hd) {
+                                        const float* __restrict__ part_acc, int NP, int hd,
+                                        const int* __restrict__ req_q_start, int R, int limit, int H) {
   asb::pdl_wait();  // the stream's previous kernel has completed (programmatic dependent launch)
   asb::pdl_launch_dependents();
   __shared__ float weight[kReduceChunk];
   const size_t row = blockIdx.x;
+  size_t out_row = row;
+  if (Short) {
+    int request;
+    const int flat = asb::nth_short_row(req_q_start, R, limit, (int)(blockIdx.x / H), &request);
+    if (flat < 0) return;
+    out_row = (size_t)flat * H + blockIdx.x % H;
+  }
   const float* pm = part_m + row * NP;
   const float* pl = part_l + row * NP;
   float mx = -INFINITY;
@@ -248,7 +259,7 @@ __global__ void attention_reduce_kernel(T* __restrict__ out, const float* __rest
 #pragma unroll
   for (int k = 0; k < 2; ++k) {
     const int col = e + k * blockDim.x;
-    if (col < hd) out[row * hd + col] = asb::from_float<T>(a[k] / denom);
+    if (col < hd) out[out_row * hd + col] = asb::from_float<T>(a[k] / denom);
   }
 }
 
@@ -283,8 +294,8 @@ int launch(const AttentionParams& p, int num_tokens, cudaStream_t stream) {
   if (p.NP > 1) {
     int threads = 32;
     while (threads < p.hd && threads < 256) threads <<= 1;
-    asb::launch(attention_reduce_kernel<T>, num_tokens * p.H, threads, 0, stream, 
-        (T*)p.out, p.part_m, p.part_l, p.part_acc, p.NP, p.hd);
+    asb::launch(attention_reduce_kernel<T, false>, num_tokens * p.H, threads, 0, stream,
+        (T*)p.out, p.part_m, p.part_l, p.part_acc, p.NP, p.hd, (const int*)nullptr, 0, 0, 1);
     return asb::check_launch("attention_reduce");
   }
   return 0;
@@ -301,9 +312,25 @@ extern "C" int asb_attention_reduce(void* out, const float* part_m, const float*
   int threads = 32;
   while (threads < hd && threads < 256) threads <<= 1;
   ASB_DISPATCH_DTYPE(dtype, T,
-                     asb::launch(attention_reduce_kernel<T>, rows, threads, 0, stream, 
-                         (T*)out, part_m, part_l, part_acc, NP, hd));
+                     asb::launch(attention_reduce_kernel<T, false>, rows, threads, 0, stream,
+                         (T*)out, part_m, part_l, part_acc, NP, hd, (const int*)nullptr, 0, 0, 1));
   return asb::check_launch("attention_reduce");
+}
+
+// The same for partial results that cover only the rows of requests with at most `limit` tokens,
+// [short_rows, H, NP(, hd)] in request order: each is merged into its row of out [T, H, hd].
+extern "C" int asb_attention_reduce_short(void* out, const float* part_m, const float* part_l,
+                                          const float* part_acc, const int* req_q_start, int R, int limit,
+                                          int short_rows, int H, int NP, int hd, int dtype, cudaStream_t stream) {
+  if (short_rows == 0) return 0;
+  if (hd < 1 || hd > 512) return asb::fail("attention_reduce_short: head_dim %d not in 1..512", hd);
+  if (!req_q_start || R < 1 || H < 1 || short_rows < 0) return asb::fail("attention_reduce_short: no requests");
+  int threads = 32;
+  while (threads < hd && threads < 256) threads <<= 1;
+  ASB_DISPATCH_DTYPE(dtype, T,
+                     asb::launch(attention_reduce_kernel<T, true>, short_rows * H, threads, 0, stream,
+                         (T*)out, part_m, part_l, part_acc, NP, hd, req_q_start, R, limit, H));
+  return asb::check_launch("attention_reduce_short");
 }
 
 // Query tile geometry for G query heads per kv head: GC heads per block, QT tokens per tile.

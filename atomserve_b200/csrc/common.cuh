@@ -59,6 +59,21 @@ inline void launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
   cudaLaunchKernelEx(&config, kernel, std::forward<Args>(args)...);
 }
 
+// Among the rows of the requests that bring at most `limit` tokens, counted in request order,
+// the flat row of number `index` (its request in *request); -1 if there are fewer such rows.
+__device__ __forceinline__ int nth_short_row(const int* req_q_start, int R, int limit, int index, int* request) {
+  int begin = req_q_start[0];
+  for (int r = 0; r < R; ++r) {
+    const int end = req_q_start[r + 1], n = end - begin;
+    if (n <= limit) {
+      if (index < n) { *request = r; return begin + index; }
+      index -= n;
+    }
+    begin = end;
+  }
+  return -1;
+}
+
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 

@@ -21,6 +21,21 @@ MIXED_SCRATCH_BYTES = 128 << 20  # most that a mixed step's partial results may 
 PREFILL_KERNEL = os.environ.get("ATOMSERVE_B200_PREFILL_ATTENTION", "tcgen05")
 
 
+# In a step that holds prompt portions and single tokens, the two attention kernels touch disjoint
+# rows and neither fills the device (a portion of a few hundred tokens is one block per SM or
+# fewer; a few dozen single tokens are short chains of key tiles), so the single tokens' kernels
+# run on a second stream beside the portions' kernel. "0" keeps them on one stream.
+MIXED_OVERLAP = os.environ.get("ATOMSERVE_B200_MIXED_OVERLAP", "1") != "0"
+_SIDE: dict[torch.device, tuple] = {}  # device -> (second stream, fork event, join event)
+
+
+def _side_stream(device: torch.device):
+    if device not in _SIDE:
+        with torch.cuda.device(device):
+            _SIDE[device] = (torch.cuda.Stream(), torch.cuda.Event(), torch.cuda.Event())
+    return _SIDE[device]
+
+
 def attention_tile_shape(group: int) -> tuple[int, int]:
     """(tokens per query tile, query heads per block) for `group` query heads per kv head."""
     qt, gc = ctypes.c_int(), ctypes.c_int()
@@ -151,36 +166,62 @@ def _paged_attention_mma(q, out, k_cache, v_cache, block_tables, req_q_start, re
     if has_long and PREFILL_KERNEL == "tcgen05" and lib().asb_attention_tcgen05_supported(hd, H // KV, bs):
         from atomserve_b200.ops.linear import gemm_status
 
-        check(lib().asb_prefill_attention_tcgen05(
-            ptr(out), ptr(q), ptr(k_cache), ptr(v_cache), ptr(block_tables), ptr(req_q_start), ptr(req_pos_start),
-            T, num_requests, H, KV, hd, bs, k_cache.shape[0], block_tables.shape[1], win, float(scale),
-            ptr(gemm_status(q.device)), stream()))  # fmt: skip
+        def portions():
+            check(lib().asb_prefill_attention_tcgen05(
+                ptr(out), ptr(q), ptr(k_cache), ptr(v_cache), ptr(block_tables), ptr(req_q_start), ptr(req_pos_start),
+                T, num_requests, H, KV, hd, bs, k_cache.shape[0], block_tables.shape[1], win, float(scale),
+                ptr(gemm_status(q.device)), stream()))  # fmt: skip
+
         if not has_short:
+            portions()
             return out
         # What is left for the decode kernel: the short rows, with the key partitions their number
         # and context call for (a decoding request beside a prompt portion has as long a context
-        # as in a step of its own). The merge runs over every row of the step and leaves alone the
-        # rows that have no partial results: their sums are zeroed here, and the portions' rows
-        # were stored by the kernel above.
+        # as in a step of its own). When the caller says how many tokens each request brings, the
+        # kernel starts blocks for the short rows only and the partial results hold only those
+        # rows; otherwise blocks start for every row of the step and the portions' leave at once.
         ps, np_ = partitions or plan_decode_partitions(short_rows, KV, H // KV, max_context, win, hd)
-        # The partial results are indexed by the step's rows, portions' rows included, so their
-        # size goes with the whole step: where a large portion would make them large (a portion of
-        # 8,192 tokens of 64 heads: 270 MB a partition), the single tokens run unpartitioned, as
-        # they do in any step whose portions fill the device by themselves.
-        if partitions is None and T * H * np_ * (hd + 2) * 4 > MIXED_SCRATCH_BYTES:
+        compact = short_rows if host_q_lens is not None else 0
+        scratch_rows = compact or T
+        if partitions is None and scratch_rows * H * np_ * (hd + 2) * 4 > MIXED_SCRATCH_BYTES:
             ps, np_ = 1 << 30, 1
         part_m = part_l = part_acc = None
         if np_ > 1:
-            part_m = torch.empty(T * H * np_, device=q.device, dtype=torch.float32)
-            part_l = torch.zeros(T * H * np_, device=q.device, dtype=torch.float32)
-            part_acc = torch.empty(T * H * np_ * hd, device=q.device, dtype=torch.float32)
-        check(lib().asb_paged_attention_mma(
-            ptr(out), ptr(q), ptr(k_cache), ptr(v_cache), ptr(block_tables), ptr(req_q_start),
-            ptr(req_pos_start), ptr(part_m), ptr(part_l), ptr(part_acc), T, num_requests, H, KV, hd, bs,
-            block_tables.shape[1], win, ps, np_, float(scale), 1, 0, 0, stream()))  # fmt: skip
-        if np_ > 1:
-            check(lib().asb_attention_reduce(ptr(out), ptr(part_m), ptr(part_l), ptr(part_acc), T * H, np_, hd,
-                                             dtype_code(q), stream()))  # fmt: skip
+            part_m = torch.empty(scratch_rows * H * np_, device=q.device, dtype=torch.float32)
+            # (without the short rows' count the merge runs over every row of the step and leaves
+            # alone those whose sums are zero: the portions' rows, stored by their own kernel)
+            part_l = (torch.empty if compact else torch.zeros)(scratch_rows * H * np_, device=q.device, dtype=torch.float32)
+            part_acc = torch.empty(scratch_rows * H * np_ * hd, device=q.device, dtype=torch.float32)
+
+        def single_tokens():
+            check(lib().asb_paged_attention_mma(
+                ptr(out), ptr(q), ptr(k_cache), ptr(v_cache), ptr(block_tables), ptr(req_q_start),
+                ptr(req_pos_start), ptr(part_m), ptr(part_l), ptr(part_acc), T, num_requests, H, KV, hd, bs,
+                block_tables.shape[1], win, ps, np_, float(scale), 1, 0, 0, compact, stream()))  # fmt: skip
+            if np_ > 1 and compact:
+                check(lib().asb_attention_reduce_short(ptr(out), ptr(part_m), ptr(part_l), ptr(part_acc), ptr(req_q_start),
+                                                       num_requests, SHORT_ROWS, compact, H, np_, hd, dtype_code(q), stream()))  # fmt: skip
+            elif np_ > 1:
+                check(lib().asb_attention_reduce(ptr(out), ptr(part_m), ptr(part_l), ptr(part_acc), T * H, np_, hd,
+                                                 dtype_code(q), stream()))  # fmt: skip
+
+        if not MIXED_OVERLAP or torch.cuda.is_current_stream_capturing():
+            portions()
+            single_tokens()
+            return out
+        # Fork: the second stream starts from what this stream has done so far (q, the cache pages,
+        # the scratch), runs the single tokens, and this stream goes on only when both are done.
+        # The scratch is this stream's memory; it is given back after the join, so nothing that
+        # reuses it can run before the second stream has finished with it.
+        main = torch.cuda.current_stream(q.device)
+        side, fork, join = _side_stream(q.device)
+        fork.record(main)
+        portions()
+        with torch.cuda.stream(side):
+            side.wait_event(fork)
+            single_tokens()
+            join.record(side)
+        main.wait_event(join)
         return out
     ps, np_ = 1 << 30, 1
     if has_short and not has_long:
@@ -193,7 +234,7 @@ def _paged_attention_mma(q, out, k_cache, v_cache, block_tables, req_q_start, re
     check(lib().asb_paged_attention_mma(
         ptr(out), ptr(q), ptr(k_cache), ptr(v_cache), ptr(block_tables), ptr(req_q_start),
         ptr(req_pos_start), ptr(part_m), ptr(part_l), ptr(part_acc), T, num_requests, H, KV, hd, bs,
-        block_tables.shape[1], win, ps, np_, float(scale), int(has_short), int(has_long), int(all_single),
+        block_tables.shape[1], win, ps, np_, float(scale), int(has_short), int(has_long), int(all_single), 0,
         stream()))  # fmt: skip
     if np_ > 1:
         check(lib().asb_attention_reduce(ptr(out), ptr(part_m), ptr(part_l), ptr(part_acc), T * H, np_, hd,

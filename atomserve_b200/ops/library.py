@@ -32,10 +32,11 @@ _SIGNATURES = {
     "asb_silu_mul": [_P, _P, _I, _I, _I, _P],
     "asb_qk_norm_rope_store": [_P] * 9 + [_I] * 6 + [_F, _I, _P],
     "asb_paged_attention": [_P] * 10 + [_I] * 10 + [_F, _I, _P],
-    "asb_paged_attention_mma": [_P] * 10 + [_I] * 10 + [_F, _I, _I, _I, _P],
+    "asb_paged_attention_mma": [_P] * 10 + [_I] * 10 + [_F, _I, _I, _I, _I, _P],
     "asb_prefill_attention_tcgen05": [_P] * 7 + [_I] * 9 + [_F, _P, _P],
     "asb_attention_tcgen05_supported": [_I, _I, _I],
     "asb_attention_reduce": [_P, _P, _P, _P, _I, _I, _I, _I, _P],
+    "asb_attention_reduce_short": [_P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P],
     "asb_attention_mma_supported": [_I, _I],
     "asb_decode_attention_resident_blocks": [_I],
     "asb_gemm_tcgen05": [_P, _P, _P, _P, _I, _I, _I, _I, _P, _P, _P],

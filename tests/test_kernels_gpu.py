@@ -245,6 +245,8 @@ ATTN_CASES = [
     # prompt portions beside single tokens of long requests: the single tokens keep their key partitions
     (8, 2, 128, 16, [2065, 1000, 300, 3000], [1, 1, 200, 1], None),
     (8, 2, 128, 16, [3000, 64, 2500], [1, 64, 3], 700),
+    # short rows before, between and after portions, five heads a group: the decode kernel's blocks count short rows only
+    (40, 8, 128, 16, [900, 1200, 64, 700, 2100], [2, 300, 1, 8, 1], None),
 ]
 
 
