@@ -10,8 +10,9 @@
 // pairs of the tile, QT = 128 / G tokens (rounded down) times the G query heads of the kv head, loaded as one
 // 3-D TMA box of q [T, H, hd]. Keys are visited in tiles of 64 at absolute multiples of 64.
 //
-//   warp 0     TMA: the Q tile once, then per key tile the pages of K and of V named by the
-//              block table, each page as two boxes (the two 64-element halves of the head).
+//   warp 0     TMA: the Q tile once, then per key tile the pages of K named by the block table,
+//              each page as two boxes (the two 64-element halves of the head).
+//   warp 7     TMA: the pages of V, through a ring of stages of its own.
 //   warp 1     MMA: S[b] = Q K^T into score buffer b = tile & 1 (two buffers, so the next tile's
 //              scores are computed while this tile's softmax runs).
 //   warp 6     MMA: O += P V once the softmax has written P. V is consumed as an MN-major operand:
@@ -33,7 +34,7 @@ namespace {
 
 using namespace asb::t5;
 
-constexpr int kThreads = 224;
+constexpr int kThreads = 256;
 constexpr int HD = 128;
 constexpr int kRows = 128;
 constexpr int kKeys = 64;                         // keys per tile
@@ -86,13 +87,15 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
   unsigned char* p_ptr = aligned + kQBytes + kStages * kStageBytes;
   const uint32_t bars = p_smem + kPBuffers * kPBytes;
   const uint32_t q_full = bars;
-  auto kv_full = [&](int s) { return bars + 8u * (1 + s); };
-  auto kv_empty = [&](int s) { return bars + 8u * (1 + kStages + s); };
+  auto k_full = [&](int s) { return bars + 8u * (1 + s); };
+  auto k_empty = [&](int s) { return bars + 8u * (1 + kStages + s); };
+  auto v_full = [&](int s) { return bars + 8u * (8 + 2 * kStages + s); };
+  auto v_empty = [&](int s) { return bars + 8u * (8 + 3 * kStages + s); };
   auto s_full = [&](int b) { return bars + 8u * (1 + 2 * kStages + b); };
   const uint32_t p_full = bars + 8u * (3 + 2 * kStages);
   auto pv_done = [&](int b) { return bars + 8u * (4 + 2 * kStages + b); };  // one per P buffer
   auto s_empty = [&](int b) { return bars + 8u * (6 + 2 * kStages + b); };  // score buffer b has been read out
-  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(aligned + kQBytes + kStages * kStageBytes + kPBuffers * kPBytes + 8 * (8 + 2 * kStages));
+  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(aligned + kQBytes + kStages * kStageBytes + kPBuffers * kPBytes + 8 * (8 + 4 * kStages));
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   // The 1 KB beyond the tiles holds the alignment padding and, after it, the barriers.
@@ -129,8 +132,10 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1);
     for (int s = 0; s < kStages; ++s) {
-      mbar_init(kv_full(s), 1);
-      mbar_init(kv_empty(s), 1);
+      mbar_init(k_full(s), 1);
+      mbar_init(k_empty(s), 1);
+      mbar_init(v_full(s), 1);
+      mbar_init(v_empty(s), 1);
     }
     mbar_init(s_full(0), 1);
     mbar_init(s_full(1), 1);
@@ -151,10 +156,16 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
   asb::pdl_wait();
   asb::pdl_launch_dependents();
 
-  if (warp == 0) {
+  if (warp == 0 || warp == 7) {
+    // Warp 0 brings the keys, warp 7 the values, each through a ring of its own: a tile's keys
+    // are done with when its Q K^T has completed, a tile before its values are (after P V), and
+    // the next tile but one's keys are then requested that much earlier. (With keys and values in
+    // one ring, a tile's loads could only start when the P V of the tile two before had completed,
+    // and their latency, 1,500 to 2,000 cycles from L2, lay on the block's chain.)
     // The whole warp looks up the pages of a key tile (one page per lane, the loads in flight
     // together); lane 0 waits for the stage, and the lanes issue the tile's TMA loads together.
-    if (lane == 0) {
+    const bool keys = warp == 0;
+    if (keys && lane == 0) {
       // the box is QT tokens by G heads: 128 rows when G divides 128, fewer otherwise (the rows
       // after them are padding: never real, masked out, stored nowhere)
       mbar_expect_tx(q_full, (uint32_t)(2 * p.QT * p.G * 128));
@@ -179,20 +190,21 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
       }
       int ok_i = 1;
       if (lane == 0) {
-        ok_i = mbar_wait(kv_empty(s), (((uint32_t)j / kStages) & 1u) ^ 1u, p.status, 11) ? 1 : 0;
-        if (ok_i) mbar_expect_tx(kv_full(s), kStageBytes);
+        const uint32_t parity = (((uint32_t)j / kStages) & 1u) ^ 1u;
+        ok_i = mbar_wait(keys ? k_empty(s) : v_empty(s), parity, p.status, keys ? 11 : 21) ? 1 : 0;
+        if (ok_i) mbar_expect_tx(keys ? k_full(s) : v_full(s), kKVBytes);
       }
       ok = __shfl_sync(0xffffffffu, ok_i, 0) != 0;
       if (!ok) break;
-      // one box per lane: box i's four copies (K and V, the two halves of the head) go out from
-      // lanes 4i..4i+3 in one instruction instead of one after another from a single lane
+      // one box per lane pair: box i's two copies (the two halves of the head) go out from lanes
+      // 2i and 2i + 1 in one instruction instead of one after another from a single lane
       {
-        const int i = lane >> 2, which = lane & 3;
+        const int i = lane >> 1, which = lane & 1;
         const int y = __shfl_sync(0xffffffffu, row_y, i);
         if (i < boxes_per_tile) {
-          const uint32_t off = (uint32_t)(i * box_rows) * 128u + (uint32_t)(which & 1) * kKVBlockBytes;
-          if (which < 2) tma_load_2d(k_smem(s) + off, &map_k, kv_full(s), (which & 1) * 64, y);
-          else tma_load_2d(v_smem(s) + off, &map_v, kv_full(s), (which & 1) * 64, y);
+          const uint32_t off = (uint32_t)(i * box_rows) * 128u + (uint32_t)which * kKVBlockBytes;
+          if (keys) tma_load_2d(k_smem(s) + off, &map_k, k_full(s), which * 64, y);
+          else tma_load_2d(v_smem(s) + off, &map_v, v_full(s), which * 64, y);
         }
       }
     }
@@ -211,15 +223,16 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
                     (uint32_t)(ks != 0));
         }
         umma_commit(s_full(j & 1));
+        umma_commit(k_empty(s));  // the keys' stage, once this product has read it
       };
       bool ok = mbar_wait(q_full, 0, p.status, 12);
-      if (ok) ok = mbar_wait(kv_full(0), 0, p.status, 13);
+      if (ok) ok = mbar_wait(k_full(0), 0, p.status, 13);
       if (ok) {
         fence_after_sync();
         issue_qk(0);
       }
       for (int j = 0; j + 1 < num_tiles && ok; ++j) {
-        ok = mbar_wait(kv_full((j + 1) % kStages), ((uint32_t)(j + 1) / kStages) & 1u, p.status, 14);
+        ok = mbar_wait(k_full((j + 1) % kStages), ((uint32_t)(j + 1) / kStages) & 1u, p.status, 14);
         // score buffer (j + 1) & 1 held tile j - 1, the buffer's use number (j - 1) / 2: read out?
         if (ok && j >= 1) ok = mbar_wait(s_empty((j + 1) & 1), ((uint32_t)(j - 1) >> 1) & 1u, p.status, 18);
         if (!ok) break;
@@ -233,7 +246,8 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
       constexpr uint32_t idesc_pv = instr_desc_bf16(kRows, HD, true);
       bool ok = true;
       for (int j = 0; j < num_tiles && ok; ++j) {
-        ok = mbar_wait(p_full, (uint32_t)j & 1u, p.status, 15);
+        ok = mbar_wait(v_full(j % kStages), ((uint32_t)j / kStages) & 1u, p.status, 22);
+        if (ok) ok = mbar_wait(p_full, (uint32_t)j & 1u, p.status, 15);
         if (!ok) break;
         fence_after_sync();
         const int s = j % kStages;
@@ -245,8 +259,7 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
           umma_bf16(tmem_o, a, b, idesc_pv, (uint32_t)((j | ks) != 0));
         }
         umma_commit(pv_done(j % kPBuffers));
-        // (Q K^T of this tile completed before its softmax ran, so this commit frees K as well as V)
-        umma_commit(kv_empty(s));
+        umma_commit(v_empty(s));
       }
     }
   } else {
@@ -261,10 +274,13 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
     const bool real_block = nq * p.G == kRows;  // no padding rows in this block
     float m = -INFINITY, l = 0.f;
     bool ok = true;
+    uint32_t scores_there = 0;  // lane 0: the answer to an early question about this tile's scores
     for (int j = 0; j < num_tiles && ok; ++j) {
       const int kt0 = kt_begin + j * kKeys;
       int ok_i = 1;
-      if (lane == 0) ok_i = mbar_wait(s_full(j & 1), ((uint32_t)j >> 1) & 1u, p.status, 16) ? 1 : 0;
+      // (Q K^T runs a tile or two ahead, so the scores are usually there; asking takes a thread
+      // a few hundred cycles even then, which is why lane 0 asked during the previous tile.)
+      if (lane == 0 && !scores_there) ok_i = mbar_wait(s_full(j & 1), ((uint32_t)j >> 1) & 1u, p.status, 16) ? 1 : 0;
       ok = __shfl_sync(0xffffffffu, ok_i, 0) != 0;
       if (!ok) break;
       fence_after_sync();
@@ -306,6 +322,7 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
         l *= corr;
       }
       const float m_use = m == -INFINITY ? 0.f : m;
+      if (lane == 0) scores_there = j + 1 < num_tiles ? mbar_try(s_full((j + 1) & 1), ((uint32_t)(j + 1) >> 1) & 1u) : 0u;
       if (j > 0 && __any_sync(0xffffffffu, corr != 1.f)) {
         // rescale this row of O: the previous P V (tile j - 1) must have completed
         if (lane == 0) ok_i = mbar_wait(pv_done((j - 1) % kPBuffers), ((uint32_t)(j - 1) / kPBuffers) & 1u, p.status, 17) ? 1 : 0;
