@@ -15,16 +15,18 @@
 //   warp 7     TMA: the pages of V, through a ring of stages of its own.
 //   warp 1     MMA: S[b] = Q K^T into score buffer b = tile & 1 (two buffers, so the next tile's
 //              scores are computed while this tile's softmax runs).
-//   warp 6     MMA: O += P V once the softmax has written P. V is consumed as an MN-major operand:
-//              its rows in shared memory are keys, exactly as the pages hold them. (A thread of
-//              its own, because issuing the next tile's Q K^T would hold this product back.)
+//   warp 6     MMA: O += P V once the softmax has written P, which is the product's A operand in
+//              tensor memory. V is consumed as an MN-major operand: its rows in shared memory are
+//              keys, exactly as the pages hold them. (A thread of its own, because issuing the
+//              next tile's Q K^T would hold this product back.)
 //   warps 2-5  softmax: thread r owns row r (a TMEM lane), so row maxima and sums need no
 //              shuffles. It reads its scores once, rescales its row of O in tensor memory only when
-//              the maximum moved by more than a factor of 256, writes P as bfloat16 into the
-//              shared-memory P buffer in the swizzled K-major layout (once the previous P V has
-//              read it), and at the end stores O / sum.
+//              the maximum moved by more than a factor of 256, writes P as bfloat16 over the first
+//              half of the tile's score columns (a row's keys packed two to a column), and at the
+//              end stores O / sum. A score buffer is free for the tile after next when the P V
+//              that read its P has completed.
 //
-// Shared memory: Q 32 KB, two stages of (K 16 KB + V 16 KB), P 16 KB: 112 KB, so that two blocks
+// Shared memory: Q 32 KB, two stages of K and three of V, 16 KB each: 112 KB, so that two blocks
 // share an SM and one's softmax overlaps the other's MMAs. Tensor memory: two score buffers of 64
 // columns and the output accumulator of 128, 256 columns a block. All barrier waits are bounded;
 // a wait that runs out sets *status and the roles wind down to the final barrier.
@@ -42,17 +44,16 @@ constexpr int kBlockBytes = kRows * 64 * 2;       // one [128 rows][64 elements]
 constexpr int kQBytes = 2 * kBlockBytes;          // Q: the two 64-element halves of the head
 constexpr int kKVBlockBytes = kKeys * 64 * 2;     // one [kKeys rows][64 elements] block: 8 KB
 constexpr int kKVBytes = 2 * kKVBlockBytes;       // K or V of a tile: two halves of the head
-constexpr int kStageBytes = 2 * kKVBytes;         // K and V
-// Two K/V stages and one P buffer keep a block's shared memory at 112 KB, so that two blocks share
-// an SM: while one block's softmax runs, the other's MMAs do (one block per SM with five stages and
-// two P buffers left the tensor cores waiting on the softmax-to-MMA hand-offs: 112 us against
-// 103 us at 2,048 tokens, 334 against 296 us at 4,096). The MMA warp looks one tile ahead, so at
-// least two stages.
-constexpr int kStages = 2;                        // K/V tiles in flight
-constexpr int kPBuffers = 1;                      // P buffers
-static_assert(kStages >= 2, "Q K^T of the next tile is issued while this tile's K/V are still in use");
-constexpr int kPBytes = (kKeys / 64) * kBlockBytes;  // one P buffer: [128 rows][kKeys] in blocks of 64 keys
-constexpr int kSmem = kQBytes + kStages * kStageBytes + kPBuffers * kPBytes + 256;  // tiles, then barriers
+// A block's shared memory stays under 113 KB, so that two blocks share an SM: while one block's
+// softmax runs, the other's MMAs do (one block per SM with deeper rings left the tensor cores
+// waiting on the softmax-to-MMA hand-offs: 112 us against 103 us at 2,048 tokens, 334 against
+// 296 us at 4,096). Q K^T runs a tile ahead of the softmax, hence two stages of keys; a tile's
+// values are requested when the P V three tiles before has completed.
+constexpr int kKStages = 2;                       // key tiles in flight
+constexpr int kVStages = 3;                       // value tiles in flight
+static_assert(kKStages >= 2, "Q K^T of the next tile is issued while this tile's keys are still in use");
+constexpr int kSmem = kQBytes + (kKStages + kVStages) * kKVBytes + 256;  // tiles, then barriers
+constexpr int kBarriers = 7 + 2 * (kKStages + kVStages);
 constexpr uint32_t kTmemCols = 256;               // two score buffers of kKeys columns, 128 of output
 constexpr int kShortRows = 8;
 
@@ -81,21 +82,19 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
   const uint32_t base = smem_u32(smem_raw);
   unsigned char* aligned = smem_raw;
   const uint32_t q_smem = base;
-  auto k_smem = [&](int s) { return base + kQBytes + (uint32_t)s * kStageBytes; };
-  auto v_smem = [&](int s) { return base + kQBytes + (uint32_t)s * kStageBytes + kKVBytes; };
-  const uint32_t p_smem = base + kQBytes + kStages * kStageBytes;
-  unsigned char* p_ptr = aligned + kQBytes + kStages * kStageBytes;
-  const uint32_t bars = p_smem + kPBuffers * kPBytes;
+  auto k_smem = [&](int s) { return base + kQBytes + (uint32_t)s * kKVBytes; };
+  auto v_smem = [&](int s) { return base + kQBytes + (uint32_t)(kKStages + s) * kKVBytes; };
+  const uint32_t bars = base + kQBytes + (kKStages + kVStages) * kKVBytes;
   const uint32_t q_full = bars;
-  auto k_full = [&](int s) { return bars + 8u * (1 + s); };
-  auto k_empty = [&](int s) { return bars + 8u * (1 + kStages + s); };
-  auto v_full = [&](int s) { return bars + 8u * (8 + 2 * kStages + s); };
-  auto v_empty = [&](int s) { return bars + 8u * (8 + 3 * kStages + s); };
-  auto s_full = [&](int b) { return bars + 8u * (1 + 2 * kStages + b); };
-  const uint32_t p_full = bars + 8u * (3 + 2 * kStages);
-  auto pv_done = [&](int b) { return bars + 8u * (4 + 2 * kStages + b); };  // one per P buffer
-  auto s_empty = [&](int b) { return bars + 8u * (6 + 2 * kStages + b); };  // score buffer b has been read out
-  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(aligned + kQBytes + kStages * kStageBytes + kPBuffers * kPBytes + 8 * (8 + 4 * kStages));
+  auto s_full = [&](int b) { return bars + 8u * (1 + b); };
+  auto p_full = [&](int b) { return bars + 8u * (3 + b); };   // P written over score buffer b
+  auto pv_done = [&](int b) { return bars + 8u * (5 + b); };  // the P V that read score buffer b's P has completed
+  auto k_full = [&](int s) { return bars + 8u * (7 + s); };
+  auto k_empty = [&](int s) { return bars + 8u * (7 + kKStages + s); };
+  auto v_full = [&](int s) { return bars + 8u * (7 + 2 * kKStages + s); };
+  auto v_empty = [&](int s) { return bars + 8u * (7 + 2 * kKStages + kVStages + s); };
+  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(aligned + kQBytes + (kKStages + kVStages) * kKVBytes + 8 * kBarriers);
+  static_assert(8 * kBarriers + 4 <= 256, "the barriers and the tensor-memory slot have 256 bytes");
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   // The 1 KB beyond the tiles holds the alignment padding and, after it, the barriers.
@@ -131,19 +130,20 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
 
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1);
-    for (int s = 0; s < kStages; ++s) {
+    for (int s = 0; s < kKStages; ++s) {
       mbar_init(k_full(s), 1);
       mbar_init(k_empty(s), 1);
+    }
+    for (int s = 0; s < kVStages; ++s) {
       mbar_init(v_full(s), 1);
       mbar_init(v_empty(s), 1);
     }
     mbar_init(s_full(0), 1);
     mbar_init(s_full(1), 1);
-    mbar_init(p_full, 4);  // one arrival per softmax warp
+    mbar_init(p_full(0), 4);  // one arrival per softmax warp
+    mbar_init(p_full(1), 4);
     mbar_init(pv_done(0), 1);
     mbar_init(pv_done(1), 1);
-    mbar_init(s_empty(0), 4);  // one arrival per softmax warp
-    mbar_init(s_empty(1), 4);
     mbar_init_fence();
   }
   if (warp == 1) tmem_alloc(smem_u32((const void*)tmem_slot), kTmemCols);
@@ -177,8 +177,9 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
     const int last_page = (key_hi - 1) / p.bs;    // the last page this request certainly holds
     const int fallback = table[last_page];
     bool ok = true;
+    const int ring = keys ? kKStages : kVStages;
     for (int j = 0; j < num_tiles; ++j) {
-      const int s = j % kStages;
+      const int s = j % ring;
       // pages beyond the request's end, or released by the window, are masked out anyway: read a
       // page the request holds, so that shared memory never holds non-finite values
       int row_y = 0;
@@ -190,7 +191,7 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
       }
       int ok_i = 1;
       if (lane == 0) {
-        const uint32_t parity = (((uint32_t)j / kStages) & 1u) ^ 1u;
+        const uint32_t parity = (((uint32_t)j / ring) & 1u) ^ 1u;
         ok_i = mbar_wait(keys ? k_empty(s) : v_empty(s), parity, p.status, keys ? 11 : 21) ? 1 : 0;
         if (ok_i) mbar_expect_tx(keys ? k_full(s) : v_full(s), kKVBytes);
       }
@@ -214,7 +215,7 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
     if (lane == 0) {
       constexpr uint32_t idesc_qk = instr_desc_bf16(kRows, kKeys, false);
       auto issue_qk = [&](int j) {
-        const int s = j % kStages;
+        const int s = j % kKStages;
 #pragma unroll
         for (int ks = 0; ks < HD / 16; ++ks) {  // 16 head elements per MMA: 32 bytes along the swizzled row
           const uint32_t in_row = (uint32_t)(ks % 4) * 32u;
@@ -232,9 +233,10 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
         issue_qk(0);
       }
       for (int j = 0; j + 1 < num_tiles && ok; ++j) {
-        ok = mbar_wait(k_full((j + 1) % kStages), ((uint32_t)(j + 1) / kStages) & 1u, p.status, 14);
-        // score buffer (j + 1) & 1 held tile j - 1, the buffer's use number (j - 1) / 2: read out?
-        if (ok && j >= 1) ok = mbar_wait(s_empty((j + 1) & 1), ((uint32_t)(j - 1) >> 1) & 1u, p.status, 18);
+        ok = mbar_wait(k_full((j + 1) % kKStages), ((uint32_t)(j + 1) / kKStages) & 1u, p.status, 14);
+        // score buffer (j + 1) & 1 held tile j - 1's scores and then its P, the buffer's use number
+        // (j - 1) / 2: has that tile's P V read it?
+        if (ok && j >= 1) ok = mbar_wait(pv_done((j + 1) & 1), ((uint32_t)(j - 1) >> 1) & 1u, p.status, 18);
         if (!ok) break;
         fence_after_sync();
         issue_qk(j + 1);
@@ -246,19 +248,18 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
       constexpr uint32_t idesc_pv = instr_desc_bf16(kRows, HD, true);
       bool ok = true;
       for (int j = 0; j < num_tiles && ok; ++j) {
-        ok = mbar_wait(v_full(j % kStages), ((uint32_t)j / kStages) & 1u, p.status, 22);
-        if (ok) ok = mbar_wait(p_full, (uint32_t)j & 1u, p.status, 15);
+        ok = mbar_wait(v_full(j % kVStages), ((uint32_t)j / kVStages) & 1u, p.status, 22);
+        if (ok) ok = mbar_wait(p_full(j & 1), ((uint32_t)j >> 1) & 1u, p.status, 15);
         if (!ok) break;
         fence_after_sync();
-        const int s = j % kStages;
+        const int s = j % kVStages;
 #pragma unroll
-        for (int ks = 0; ks < kKeys / 16; ++ks) {  // 16 keys per MMA
-          const uint64_t a = desc_k_major(p_smem + (uint32_t)(j % kPBuffers) * kPBytes + (uint32_t)(ks / 4) * kBlockBytes + (uint32_t)(ks % 4) * 32u, 1024);
+        for (int ks = 0; ks < kKeys / 16; ++ks) {  // 16 keys per MMA: eight 32-bit columns of P
           // V: rows are keys (128 bytes each), 8-key groups 1024 bytes apart, head halves one block apart
           const uint64_t b = desc_mn_major(v_smem(s) + (uint32_t)ks * 2048u, kKVBlockBytes, 1024);
-          umma_bf16(tmem_o, a, b, idesc_pv, (uint32_t)((j | ks) != 0));
+          umma_bf16_a_tmem(tmem_o, tmem_s(j) + (uint32_t)ks * 8u, b, idesc_pv, (uint32_t)((j | ks) != 0));
         }
-        umma_commit(pv_done(j % kPBuffers));
+        umma_commit(pv_done(j & 1));
         umma_commit(v_empty(s));
       }
     }
@@ -293,22 +294,23 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
 #pragma unroll
       for (int c = 0; c < kKeys; c += 32) tmem_ld32_nowait(tmem_s(j) + lane_addr + (uint32_t)c, raw + c);
       tmem_ld_wait();
-      // the scores are in registers: the buffer may take the Q K^T of the tile after next
-      fence_before_sync();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(s_empty(j & 1));
-      float raw_max = -INFINITY;
+      // (eight running maxima, so that no comparison waits for the one before it)
+      float part_max[8];
+#pragma unroll
+      for (int u = 0; u < 8; ++u) part_max[u] = -INFINITY;
       if (inside) {
 #pragma unroll
-        for (int i = 0; i < kKeys; ++i) raw_max = fmaxf(raw_max, __uint_as_float(raw[i]));
+        for (int i = 0; i < kKeys; ++i) part_max[i & 7] = fmaxf(part_max[i & 7], __uint_as_float(raw[i]));
       } else {
 #pragma unroll
         for (int i = 0; i < kKeys; ++i) {
           const int key = kt0 + i;
           if (!(key <= pos && key >= row_lo)) raw[i] = 0xff800000u;  // -inf
-          raw_max = fmaxf(raw_max, __uint_as_float(raw[i]));
+          part_max[i & 7] = fmaxf(part_max[i & 7], __uint_as_float(raw[i]));
         }
       }
+      const float raw_max = fmaxf(fmaxf(fmaxf(part_max[0], part_max[1]), fmaxf(part_max[2], part_max[3])),
+                                  fmaxf(fmaxf(part_max[4], part_max[5]), fmaxf(part_max[6], part_max[7])));
       const float tile_max = raw_max * p.scale_log2;  // the scale is positive
       // The running maximum moves only when the new one exceeds it by more than 8 (a factor of
       // 256 in the probabilities, harmless in float32 sums and bfloat16 operands); otherwise the
@@ -325,7 +327,7 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
       if (lane == 0) scores_there = j + 1 < num_tiles ? mbar_try(s_full((j + 1) & 1), ((uint32_t)(j + 1) >> 1) & 1u) : 0u;
       if (j > 0 && __any_sync(0xffffffffu, corr != 1.f)) {
         // rescale this row of O: the previous P V (tile j - 1) must have completed
-        if (lane == 0) ok_i = mbar_wait(pv_done((j - 1) % kPBuffers), ((uint32_t)(j - 1) / kPBuffers) & 1u, p.status, 17) ? 1 : 0;
+        if (lane == 0) ok_i = mbar_wait(pv_done((j - 1) & 1), ((uint32_t)(j - 1) >> 1) & 1u, p.status, 17) ? 1 : 0;
         ok = __shfl_sync(0xffffffffu, ok_i, 0) != 0;
         if (!ok) break;
         fence_after_sync();
@@ -339,40 +341,31 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
         }
         tmem_st_wait();
       }
-      if (j >= kPBuffers) {
-        // this tile's P buffer was last read by the P V of tile j - kPBuffers
-        if (lane == 0) ok_i = mbar_wait(pv_done(j % kPBuffers), ((uint32_t)(j - kPBuffers) / kPBuffers) & 1u, p.status, 20) ? 1 : 0;
-        ok = __shfl_sync(0xffffffffu, ok_i, 0) != 0;
-        if (!ok) break;
-      }
-      // probabilities exp2(score * scale - max), their sum, and P as bfloat16 in the swizzled
-      // K-major layout (a masked score is -inf and gives 0)
+      // probabilities exp2(score * scale - max), their sum, and P as bfloat16 over the first half
+      // of the tile's score columns, a row's keys packed two to a column: the A operand of P V
+      // (a masked score is -inf and gives 0)
       const float neg_m = -m_use;
+      uint32_t packed[kKeys / 2];
+      float part_sum[4] = {0.f, 0.f, 0.f, 0.f};  // the tile's sum in four strands, added to the row's at the end
 #pragma unroll
-      for (int c = 0; c < kKeys; c += 8) {
-        uint32_t packed[4];
-#pragma unroll
-        for (int i = 0; i < 8; i += 2) {
-          const float a = fast_exp2(fmaf(__uint_as_float(raw[c + i]), p.scale_log2, neg_m));
-          const float b = fast_exp2(fmaf(__uint_as_float(raw[c + i + 1]), p.scale_log2, neg_m));
-          l += a + b;
-          __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
-          packed[i >> 1] = *reinterpret_cast<uint32_t*>(&v);
-        }
-        // keys c..c+7 of this row: one 16-byte chunk of block c / 64
-        const int chunk = ((c % 64) / 8) ^ (row & 7);
-        *reinterpret_cast<uint4*>(p_ptr + (j % kPBuffers) * kPBytes + (c / 64) * kBlockBytes + row * 128 + chunk * 16) =
-            make_uint4(packed[0], packed[1], packed[2], packed[3]);
+      for (int i = 0; i < kKeys; i += 2) {
+        const float a = fast_exp2(fmaf(__uint_as_float(raw[i]), p.scale_log2, neg_m));
+        const float b = fast_exp2(fmaf(__uint_as_float(raw[i + 1]), p.scale_log2, neg_m));
+        part_sum[(i >> 1) & 3] += a + b;
+        __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
+        packed[i >> 1] = *reinterpret_cast<uint32_t*>(&v);
       }
-      fence_async_smem();   // P is read by the tensor cores
+      l += (part_sum[0] + part_sum[1]) + (part_sum[2] + part_sum[3]);
+      tmem_st32(tmem_s(j) + lane_addr, packed);
+      tmem_st_wait();
       fence_before_sync();
       __syncwarp();
-      if (lane == 0) mbar_arrive(p_full);
+      if (lane == 0) mbar_arrive(p_full(j & 1));
     }
     // epilogue: O / sum, rounded once
     if (ok) {
       int ok_i = 1;
-      if (lane == 0) ok_i = mbar_wait(pv_done((num_tiles - 1) % kPBuffers), ((uint32_t)(num_tiles - 1) / kPBuffers) & 1u, p.status, 18) ? 1 : 0;
+      if (lane == 0) ok_i = mbar_wait(pv_done((num_tiles - 1) & 1), ((uint32_t)(num_tiles - 1) >> 1) & 1u, p.status, 18) ? 1 : 0;
       ok = __shfl_sync(0xffffffffu, ok_i, 0) != 0;
     }
     if (ok) {

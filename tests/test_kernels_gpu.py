@@ -672,7 +672,11 @@ def test_qk_norm_rope_store_from_partial_sums(ops, H, KV, hd, K, T):
         kc = torch.zeros(nblocks, max(KV, 1), bs, hd, device="cuda", dtype=torch.bfloat16)
         vc = torch.zeros_like(kc)
         qkv = ops.linear_partial(x, w) if partial else ops.linear(x, w)
-        assert qkv is not None
+        if qkv is None:
+            # beyond 128 tokens the product is left as partial sums only where K is long enough
+            # for the planner to cut it (the last shape of the list)
+            assert T > 128 and K < 12288
+            pytest.skip("this shape runs without partial sums")
         store = dict(slots=slots, k_cache=kc, v_cache=vc) if KV else dict(slots=None, k_cache=None, v_cache=None)
         q = ops.qk_norm_rope_store(qkv, H, KV, hd, pos, q_gain=qg, k_gain=kg, eps=1e-6, inv_freq=inv_freq,
                                    rotary_dim=hd, **store)  # fmt: skip
