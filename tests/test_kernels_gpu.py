@@ -648,12 +648,18 @@ def test_linear_partial_declines_what_does_not_cut_k(ops):
     assert ops.linear_partial(x[:4].float(), w.float()) is None
 
 
-@pytest.mark.parametrize("H,KV,hd,K", [(8, 2, 128, 2048), (32, 8, 128, 4096), (4, 2, 64, 1024), (6, 3, 32, 2048), (2, 1, 256, 1024), (8, 0, 128, 2048)])
-@pytest.mark.parametrize("T", [1, 6, 40, 150])
-def test_qk_norm_rope_store_from_partial_sums(ops, H, KV, hd, K, T):
+# beyond 128 tokens the planner rarely swaps the operands and cuts K (which is when the product can
+# be left as partial sums): the last shape's 150 tokens run with that form forced
+QKV_PARTIAL_SHAPES = [(8, 2, 128, 2048), (32, 8, 128, 4096), (4, 2, 64, 1024), (6, 3, 32, 2048), (2, 1, 256, 1024), (8, 0, 128, 2048),
+                      (4, 1, 128, 12288)]  # fmt: skip
+
+
+@pytest.mark.parametrize("T,H,KV,hd,K", [(T, *shape) for shape in QKV_PARTIAL_SHAPES for T in (1, 6, 40, 128, 150)
+                                         if T <= 128 or shape[3] >= 12288])  # fmt: skip
+def test_qk_norm_rope_store_from_partial_sums(ops, T, H, KV, hd, K):
     """q/k norm, rotation and the cache write reading the qkv product from the GEMM's partial
     sums: the same bits as from the reduced product (KV = 0: queries only, nothing stored)."""
-    from atomserve_b200.ops.linear import check_gemm_status
+    from atomserve_b200.ops.linear import check_gemm_status, gemm_tune
 
     _skip_without_partial_sums()
     g = torch.Generator().manual_seed(H * 100 + hd + T)
@@ -671,12 +677,13 @@ def test_qk_norm_rope_store_from_partial_sums(ops, H, KV, hd, K, T):
     for partial in (False, True):
         kc = torch.zeros(nblocks, max(KV, 1), bs, hd, device="cuda", dtype=torch.bfloat16)
         vc = torch.zeros_like(kc)
-        qkv = ops.linear_partial(x, w) if partial else ops.linear(x, w)
-        if qkv is None:
-            # beyond 128 tokens the product is left as partial sums only where K is long enough
-            # for the planner to cut it (the last shape of the list)
-            assert T > 128 and K < 12288
-            pytest.skip("this shape runs without partial sums")
+        if T > 128:
+            gemm_tune(1)  # swapped operands: tiles of 128 weight rows by 256 tokens
+        try:
+            qkv = ops.linear_partial(x, w) if partial else ops.linear(x, w)
+        finally:
+            gemm_tune()
+        assert qkv is not None
         store = dict(slots=slots, k_cache=kc, v_cache=vc) if KV else dict(slots=None, k_cache=None, v_cache=None)
         q = ops.qk_norm_rope_store(qkv, H, KV, hd, pos, q_gain=qg, k_gain=kg, eps=1e-6, inv_freq=inv_freq,
                                    rotary_dim=hd, **store)  # fmt: skip
