@@ -43,6 +43,7 @@
 
 // How the pair kernel cuts its last round of tiles along K (gemm_tcgen05_pair.cu).
 extern "C" long long asb_gemm_tcgen05_pair_cut(int M, int N, int K, int bn, int* out3);
+extern "C" double asb_gemm_tcgen05_pair_us_per_kb(int bn);
 
 namespace {
 
@@ -588,13 +589,13 @@ int stage_room(int bn_kernel) {
 // a fixed part plus rounds of tiles times K blocks times the form's time per K block, with
 // constants fitted to the twelve projection shapes of Qwen3-8B, -14B and -32B at 200 to 2,048
 // tokens (over those 84 cases the estimate's choice is within 0.1 % of the best form's time
-// summed, and never more than 3.2 % behind it on one):
+// summed, and never more than 2 % behind it on one):
 //   unswapped tiles of 128 tokens by bn weight rows, bn a multiple of 32 from 64 to 256 (the
 //     epilogue reads 32 columns at a time): up to 128 rows in the 128-column kernel (six stages),
 //     wider ones in the 256-column kernel with as many stages as fit; an SM's time per K block
 //     goes with the bytes it takes in, so narrower tiles that occupy more SMs win where wide
 //     ones leave SMs idle, as long as they need no further round;
-//   tiles of 256 tokens by 128 or 256 weight rows on pairs of SMs (gemm_tcgen05_pair.cu), whose
+//   tiles of 256 tokens by 128 to 256 weight rows (in steps of 32) on pairs of SMs (gemm_tcgen05_pair.cu), whose
 //     last round can be cut along K: twice the arithmetic per byte taken in, so with enough
 //     tiles to fill the device the 256-row tile wins (gate/up at 2,048 tokens: 339 -> 268 us, the
 //     vendor library 284), and the 128-row tile where there are few weight rows and a few
@@ -630,34 +631,34 @@ Plan make_plan(int M, int N, int K) {
     if (N > 128) {
       for (int bn = 256; bn >= 64; bn -= 32) {
         const int tiles = token_tiles * ((N + bn - 1) / bn);
-        const double per_kb = bn <= 128 ? 0.175 + 0.0655 * bn / 128.0 : 0.2353 + 0.1835 * bn / 256.0;
-        const double cost = 4.07 + (double)((tiles + sms_now - 1) / sms_now) * kb * per_kb;
+        const double per_kb = bn <= 128 ? 0.1724 + 0.0595 * bn / 128.0 : 0.26 + 0.1337 * bn / 256.0;
+        const double cost = 4.0 + (double)((tiles + sms_now - 1) / sms_now) * kb * per_kb;
         if (cost < best) { best = cost; pl.swap = 0; pl.pair = 0; pl.bn = bn; pl.bn_kernel = bn <= 128 ? 128 : 256; }
       }
     } else {
-      best = 4.07 + (double)((token_tiles + sms_now - 1) / sms_now) * kb * 0.2405;
+      best = 4.0 + (double)((token_tiles + sms_now - 1) / sms_now) * kb * 0.2319;
       pl.swap = 0; pl.bn = pl.bn_kernel = 128;
     }
-    for (int bn = 256; bn >= 128; bn -= 128) {
+    for (int bn = 256; bn >= 128; bn -= 32) {
       const int tiles = ((M + 255) / 256) * ((N + bn - 1) / bn);
-      const double per_kb = bn == 256 ? 0.3344 : 0.2;
+      const double per_kb = asb_gemm_tcgen05_pair_us_per_kb(bn);
       double cost = (double)((tiles + pairs - 1) / pairs) * kb * per_kb;
       int cut[3];
       const long long floats = asb_gemm_tcgen05_pair_cut(M, N, K, bn, cut);
       if (floats > 0)  // the last round cut along K: its pieces, and their sums written and read back
-        cost = (double)(cut[0] / pairs) * kb * per_kb + 2.0 * cut[2] * per_kb + 3.26 + 8.0 * floats / 3.107e6;
-      cost += 4.37;
+        cost = (double)(cut[0] / pairs) * kb * per_kb + 2.0 * cut[2] * per_kb + 3.0 + 8.0 * floats / 3.0e6;
+      cost += 5.98;
       if (cost < best) { best = cost; pl.swap = 0; pl.pair = bn; }
     }
     if (M <= 512) {
       const double share = (double)((N + BM - 1) / BM) * ((M + 255) / 256) * kb / sms_now;  // K blocks per SM
-      const double cost = 14.04 + (share < 4 ? 4 : share) * 0.45;
+      const double cost = 14.0 + (share < 4 ? 4 : share) * 0.457;
       if (cost < best) { best = cost; pl.swap = 1; pl.pair = 0; pl.bn = pl.bn_kernel = 256; }
     }
   }
   if (g_force_swap >= 0) {  // the tuning aid's choice
     pl.swap = g_force_swap == 1 ? 1 : 0;
-    pl.pair = g_force_swap == 2 && M > BM ? (g_force_bn == 128 ? 128 : 256) : 0;
+    pl.pair = g_force_swap == 2 && M > BM ? (g_force_bn >= 128 && g_force_bn <= 256 && g_force_bn % 32 == 0 ? g_force_bn : 256) : 0;
     if (pl.swap) pl.bn = pl.bn_kernel = M <= 16 ? 16 : (M <= 32 ? 32 : (M <= 64 ? 64 : (M <= 128 ? 128 : 256)));
     else if (N <= 128) pl.bn = pl.bn_kernel = 128;
     else {

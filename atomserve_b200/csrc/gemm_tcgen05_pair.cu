@@ -42,7 +42,8 @@ struct PairParams {
   int* status;
   int M, N, ldo;
   int epilogue;
-  int tiles_m, num_tiles;  // tile t -> tokens (t % tiles_m) * 256, weight rows (t / tiles_m) * BN
+  int bn;                  // weight rows per tile: a multiple of 32, at most the kernel's BN
+  int tiles_m, num_tiles;  // tile t -> tokens (t % tiles_m) * 256, weight rows (t / tiles_m) * bn
   int kb_per_tile;
   // The last, partial round of tiles can be cut along K so that every pair has a share of it:
   // tiles [0, whole_tiles) are dealt whole, round-robin; each later tile is computed by `split`
@@ -181,6 +182,8 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid
       // switched off: 714 cycles per K block with one loader, 353 with four). The tile and its
       // rows are carried along instead of being divided out of the stage count each time.
       const int me = warp == 0 ? 0 : warp - 5;
+      // bytes a stage brings into this CTA: its token rows and its half of the tile's weight rows
+      const uint32_t stage_bytes = (uint32_t)(C::kSub * (C::kA + (p.bn / 2) * BK * 2));
       int item = 0, ks = 0, s = 0;   // work item, stage within it, slot
       int len = item_len(0);
       uint32_t phase = 0;
@@ -188,7 +191,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid
       auto place = [&]() {
         const int t = item_tile(item);
         x0 = (t % p.tiles_m) * 256 + (int)rank * BM;
-        w0 = (t / p.tiles_m) * BN + (int)rank * (BN / 2);
+        w0 = (t / p.tiles_m) * p.bn + (int)rank * (p.bn / 2);
         k0 = item < n_whole ? 0 : piece_begin;
       };
       auto advance = [&](int by) {
@@ -208,7 +211,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid
         const uint32_t phase1 = phase;
         for (uint32_t it = me; it < ahead; it += C::kLoaders) {
           const uint32_t bar = cluster_address(full_bar(s), 0);
-          mbar_expect_tx_cluster(bar, C::kStage);
+          mbar_expect_tx_cluster(bar, stage_bytes);
 #pragma unroll
           for (int j = 0; j < C::kSub; ++j)
             tma_load_2d_pair(base + s * C::kStage + C::kSub * C::kA + j * C::kB, &map_w, bar, ((k0 + ks) * C::kSub + j) * BK, w0);
@@ -224,7 +227,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid
         const uint32_t dst = base + s * C::kStage;
         if (it >= (uint32_t)C::kStages) {
           if (!mbar_wait(empty_bar(s), phase ^ 1u, p.status, 31)) break;
-          mbar_expect_tx_cluster(bar, C::kStage);
+          mbar_expect_tx_cluster(bar, stage_bytes);
 #pragma unroll
           for (int j = 0; j < C::kSub; ++j)
             tma_load_2d_pair(dst + C::kSub * C::kA + j * C::kB, &map_w, bar, ((k0 + ks) * C::kSub + j) * BK, w0);
@@ -248,7 +251,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid
   } else if (warp == 1) {
     asb::pdl_wait();
     if (lane == 0 && rank == 0) {
-      constexpr uint32_t idesc = instr_desc_bf16(256, BN, false);
+      const uint32_t idesc = instr_desc_bf16(256, p.bn, false);
       int s = 0;
       uint32_t phase = 0;
       bool ok = true;
@@ -292,12 +295,12 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid
       if (!ok) break;
       fence_after_sync();
       const int row = (t % p.tiles_m) * 256 + (int)rank * BM + quad * 32 + lane;  // this thread's token
-      const int n0 = (t / p.tiles_m) * BN;
+      const int n0 = (t / p.tiles_m) * p.bn;
       if ((int)seg >= n_whole) {
         // a piece of a cut tile: the sums go to this pair's workspace slot as they are
         float* slot_row = p.workspace + ((size_t)pair * 256 + (size_t)((int)rank * BM + quad * 32 + lane)) * BN;
 #pragma unroll 1
-        for (int c = 0; c < BN; c += 32) {
+        for (int c = 0; c < p.bn; c += 32) {
           if (n0 + c >= p.N) break;  // uniform
           uint32_t raw[32];
           tmem_ld32(tmem_base + ((uint32_t)(quad * 32) << 16) + buf * BN + (uint32_t)c, raw);
@@ -311,7 +314,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid
         continue;
       }
 #pragma unroll 1
-      for (int c = 0; c < BN; c += 32) {
+      for (int c = 0; c < p.bn; c += 32) {
         if (n0 + c >= p.N) break;  // uniform
         uint32_t raw[32];
         tmem_ld32(tmem_base + ((uint32_t)(quad * 32) << 16) + buf * BN + (uint32_t)c, raw);
@@ -400,10 +403,10 @@ __global__ void tail_reduce_kernel(const PairParams p) {
   const int cut = blockIdx.x, tile = p.whole_tiles + cut;
   const int i = (blockIdx.y * blockDim.x + threadIdx.x) * 4;
   const int r = i / BN, c = i % BN;
-  const int row = (tile % p.tiles_m) * 256 + r, n = (tile / p.tiles_m) * BN + c;
+  const int row = (tile % p.tiles_m) * 256 + r, n = (tile / p.tiles_m) * p.bn + c;
   asb::pdl_wait();  // the GEMM has completed
   asb::pdl_launch_dependents();
-  if (i >= 256 * BN || row >= p.M || n >= p.N) return;
+  if (i >= 256 * BN || c >= p.bn || row >= p.M || n >= p.N) return;
   const float* ws = p.workspace + ((size_t)cut * p.split * 256 + r) * BN + c;
   float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
   for (int j0 = 0; j0 < p.split; j0 += 4) {  // four loads in flight; the sum still runs in piece order
@@ -489,6 +492,13 @@ int launch_pairs(const CUtensorMap& mx, const CUtensorMap& mw, const PairParams&
 // float32 sums cost to write and read back (a launch and about 3 TB/s). out3 = {tiles dealt
 // whole, pairs per cut tile, stages per piece}; returns the workspace's float32 elements.
 static int g_cut_enabled = 1;
+// Microseconds a pair takes per K block of 64 on a tile of 256 tokens by bn weight rows (fitted to
+// sweeps over the projection shapes of Qwen3-8B, -14B and -32B): at 256 rows the tensor pipe's 512
+// cycles at the clock a long GEMM runs at; at 128 the issuing thread's time for eight MMAs.
+extern "C" double asb_gemm_tcgen05_pair_us_per_kb(int bn) {
+  return bn <= 128 ? 0.2 : 0.2 + (0.3116 - 0.2) * (bn - 128) / 128.0;
+}
+static int kernel_rows(int bn) { return bn <= 128 ? 128 : 256; }  // the instantiation that runs tiles of bn weight rows
 // Tuning aid: 0 keeps every tile whole in the calls that follow, 1 (the default) lets the last round be cut.
 extern "C" void asb_gemm_tcgen05_pair_tune(int cut) { g_cut_enabled = cut; }
 
@@ -503,17 +513,18 @@ extern "C" long long asb_gemm_tcgen05_pair_cut(int M, int N, int K, int bn, int*
   if (split < 2) return 0;
   const int piece = (stages + split - 1) / split;
   split = (stages + piece - 1) / piece;  // no empty piece
-  const double us_per_stage = 2 * (bn == 256 ? 0.33 : 0.225);
+  const double us_per_stage = 2 * asb_gemm_tcgen05_pair_us_per_kb(bn);
   const double bytes = (double)left * split * 256 * bn * 4 * 2;
   if ((stages - piece) * us_per_stage <= 3.0 + bytes / 3.0e6) return 0;
   out3[0] = tiles - left; out3[1] = split; out3[2] = piece;
-  return (long long)left * split * 256 * bn;
+  return (long long)left * split * 256 * kernel_rows(bn);  // a slot is as wide as the kernel's widest tile
 }
 
 // out = x . w^T (+ residual) on pairs of SMs, for more than 128 tokens. x [M, K] and w [N, K]
 // bfloat16, contiguous, K a multiple of 8, both bases 16-byte aligned. mode 0: out bfloat16
 // (+ residual); 1: out float32; 2: SwiGLU (rows of w alternate gate and up; out [M, N / 2]).
-// bn: weight rows per pair tile, 128 or 256.
+// bn: weight rows per pair tile: 128, or a multiple of 32 from 160 to 256 (one kernel, built for 256
+// rows, runs those: narrower tiles let one round of them occupy more pairs of SMs).
 // workspace: float32, asb_gemm_tcgen05_pair_cut(M, N, K, bn) elements (null if that is 0).
 extern "C" int asb_gemm_tcgen05_pair(void* out, const void* x, const void* w, const void* residual, int M, int N,
                                      int K, int mode, int bn, float* workspace, int* status, cudaStream_t stream) {
@@ -524,7 +535,8 @@ extern "C" int asb_gemm_tcgen05_pair(void* out, const void* x, const void* w, co
   if (K < 8 || K % 8) return asb::fail("gemm_tcgen05_pair: K = %d must be a positive multiple of 8 (16-byte TMA rows)", K);
   if (((uintptr_t)x & 15) || ((uintptr_t)w & 15)) return asb::fail("gemm_tcgen05_pair: operands must be 16-byte aligned");
   if (!status) return asb::fail("gemm_tcgen05_pair: a status word is required");
-  if (bn != 128 && bn != 256) return asb::fail("gemm_tcgen05_pair: %d weight rows per tile (128 or 256)", bn);
+  if (bn != 128 && !(bn >= 160 && bn <= 256 && bn % 32 == 0))
+    return asb::fail("gemm_tcgen05_pair: %d weight rows per tile (128, or a multiple of 32 from 160 to 256)", bn);
   PairParams p;
   p.out = out;
   p.residual = residual;
@@ -533,6 +545,7 @@ extern "C" int asb_gemm_tcgen05_pair(void* out, const void* x, const void* w, co
   p.N = N;
   p.ldo = N;
   p.epilogue = mode == 2 ? kStoreSwiGLU : (mode == 1 ? kStoreF32 : (residual ? kStoreBf16Residual : kStoreBf16));
+  p.bn = bn;
   p.tiles_m = (M + 255) / 256;
   p.num_tiles = p.tiles_m * ((N + bn - 1) / bn);
   p.kb_per_tile = (K + BK - 1) / BK;

@@ -746,11 +746,11 @@ PAIR_SHAPES = [(300, 512, 256), (257, 1000, 520), (129, 130, 72), (2048, 4096, 4
                (1000, 5000, 4160), (300, 4000, 4160), (520, 1100, 2120)]  # fmt: skip
 
 
-@pytest.mark.parametrize("rows", [128, 256])
+@pytest.mark.parametrize("rows", [128, 160, 224, 256])
 @pytest.mark.parametrize("M,N,K", PAIR_SHAPES)
 def test_gemm_tcgen05_on_pairs_of_sms(ops, M, N, K, rows):
     """The many-token form of the GEMM (tcgen05.mma.cta_group::2: two CTAs on a tile of 256 tokens
-    by 128 or 256 weight rows), forced for shapes the planner would also give to single SMs: every
+    by 128 to 256 weight rows), forced for shapes the planner would also give to single SMs: every
     epilogue against float64; tokens, weight rows and K that end inside a tile, an odd number of K
     blocks (the second K block of the last stage lies beyond K), one tile, many tiles per pair, a
     last round of tiles cut along K into pieces that a second kernel adds up."""

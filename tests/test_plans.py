@@ -70,14 +70,15 @@ def test_gemm_plans_keep_every_tile_within_its_partial_sum_slots():
         cuts_k, swap, max_slots, bn, kb, tiles, blocks, pair = list(out)
         assert kb == -(-K // 64) and 1 <= blocks <= 148, (M, N, K)
         if pair:  # tiles of 256 tokens by `pair` weight rows, two blocks (a pair of SMs) on each
-            assert pair in (128, 256) and bn == pair and not swap and not cuts_k and M > 128, (M, N, K)
+            assert pair in (128, 160, 192, 224, 256) and bn == pair and not swap and not cuts_k and M > 128, (M, N, K)
             assert tiles == -(-M // 256) * -(-N // pair), (M, N, K)
             # the last round of tiles may be cut along K: whole rounds first, then `split` pairs on
             # each tile left, every piece with stages to run, one workspace slot a piece
             floats = pair_cut(M, N, K, pair, cut)
             whole, split, piece = list(cut)
             stages = -(-kb // 2)
-            assert workspace(M, N, K, None) == floats == ((tiles - whole) * split * 256 * pair if split > 1 else 0), (M, N, K)
+            slot = 256 * (128 if pair == 128 else 256)  # a slot is as wide as the widest tile of the kernel that runs it
+            assert workspace(M, N, K, None) == floats == ((tiles - whole) * split * slot if split > 1 else 0), (M, N, K)
             if split == 1:
                 assert whole == tiles and blocks == 2 * min(tiles, 74), (M, N, K)
             else:
