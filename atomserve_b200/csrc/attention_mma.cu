@@ -472,7 +472,10 @@ prefill_attention_kernel(const MmaParams p) {
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   // Which request and tile of its tokens? Only requests with more than kShortRows tokens count.
-  int tile = blockIdx.x, r = 0, q_len = 0;
+  // (blocks are numbered head chunk fastest, so that every kv head's longest block starts first)
+  const int chunks = p.KV * p.HC;
+  const int chunk = blockIdx.x % chunks;
+  int tile = blockIdx.x / chunks, r = 0, q_len = 0;
   for (; r < p.R; ++r) {
     q_len = p.req_q_start[r + 1] - p.req_q_start[r];
     if (q_len <= kShortRows) continue;
@@ -488,8 +491,8 @@ prefill_attention_kernel(const MmaParams p) {
   const int nq = min(p.QT, q_len - q0);
   const int row0 = p.req_q_start[r] + q0;
   const int pos0 = p.req_pos_start[r] + q0;
-  const int kvh = blockIdx.y / p.HC;
-  const int head0 = kvh * p.G + (blockIdx.y % p.HC) * p.GC;
+  const int kvh = chunk / p.HC;
+  const int head0 = kvh * p.G + (chunk % p.HC) * p.GC;
   const int gc = min(p.GC, kvh * p.G + p.G - head0);
   const int num_rows = nq * gc;  // tile row rr = qi * gc + g
   const int* table = p.block_tables + (size_t)r * p.table_width;
@@ -667,8 +670,9 @@ int launch_mma(const MmaParams& p, int run_decode, int run_prefill, cudaStream_t
     auto kern = prefill_attention_kernel<HD>;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) return asb::fail("prefill_attention: %s", cudaGetErrorString(e));
-    dim3 grid((p.T + p.QT - 1) / p.QT + p.R, p.KV * p.HC, 1);
-    asb::launch(kern, grid, kPrefillThreads, smem, stream, p);
+    const long long blocks = (long long)((p.T + p.QT - 1) / p.QT + p.R) * p.KV * p.HC;
+    if (blocks > 0x7fffffffLL) return asb::fail("prefill_attention: %lld blocks exceed the grid", blocks);
+    asb::launch(kern, dim3((unsigned)blocks), kPrefillThreads, smem, stream, p);
     if (int rc = asb::check_launch("prefill_attention")) return rc;
   }
   return 0;
