@@ -561,7 +561,7 @@ unsigned long long* g_stamps = nullptr;  // asb_gemm_tcgen05_timeline
 struct Plan {
   int swap, bn, bn_kernel, tiles_p, tiles_q, kb_per_tile, stream, blocks, max_slots;
   int stages, stage_size;
-  int pair;             // 0, or the weight rows (128 or 256) of the tiles that pairs of SMs compute (gemm_tcgen05_pair.cu)
+  int pair;             // 0, or the weight rows (128 to 256 in steps of 32) of the tiles that pairs of SMs compute (gemm_tcgen05_pair.cu)
   long long workspace;  // float32 elements
 };
 
@@ -739,7 +739,7 @@ extern "C" void asb_gemm_tcgen05_timeline(void* buffer) { g_stamps = (unsigned l
 
 // Tuning aid: force the orientation (swap 0: unswapped on single SMs, 1: swapped, 2: pairs of
 // SMs; -1 automatic) and, for unswapped tiles, the weight rows per tile (single SMs: a multiple of
-// 32 from 64 to 256; pairs: 128 or 256; 0 automatic) of the calls that follow.
+// 32 from 64 to 256; pairs: 128 to 256 in steps of 32; 0 automatic) of the calls that follow.
 extern "C" void asb_gemm_tcgen05_tune(int swap, int bn) { g_force_swap = swap; g_force_bn = bn; }
 
 // How a shape is run: out8 = {cuts K (1) or whole tiles (0), swapped operands, workspace slots per

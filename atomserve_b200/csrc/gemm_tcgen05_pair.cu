@@ -1,6 +1,7 @@
 // bfloat16 GEMM for many tokens on pairs of SMs: out[M, N] = x[M, K] . w[N, K]^T with
 // tcgen05.mma.cta_group::2. Two CTAs on the two SMs of a pair (a cluster of two) compute one tile
-// of 256 tokens by BN weight rows. Each CTA loads its own 128 token rows and half of the tile's
+// of 256 tokens by up to BN weight rows (the kernel built for 256 also runs tiles of 160, 192 and
+// 224 rows: narrower tiles let one round occupy more pairs). Each CTA loads its own 128 token rows and half of the tile's
 // weight rows, the pair's MMA reads both halves of the weights from the two shared memories, and
 // each CTA's tensor memory receives its 128 token rows of the result. Per unit of arithmetic an
 // SM so takes in two thirds (BN = 256) of the bytes a single CTA's 128 x 256 tile asks for, and
@@ -9,7 +10,7 @@
 // wakes, TMA request, L2 latency, barrier, MMA thread wakes) is longer than the MMAs of the other
 // three (csrc/gemm_tcgen05.cu has that kernel and the swapped, few-token forms).
 //
-// Roles per CTA: warp 0 loads (TMA, no multicast), warp 1 of the even CTA issues the pair's MMAs,
+// Roles per CTA: warps 0 and 6-8 load (TMA, no multicast), warp 1 of the even CTA issues the pair's MMAs,
 // warps 2-5 run the epilogue for the CTA's 128 token rows. Barriers: full[s] lives in the even
 // CTA and counts both CTAs' arrivals and bytes (the odd CTA's TMA completes there through the
 // cluster address); empty[s] and acc_full[b] exist in both CTAs and are signalled in both by one

@@ -164,8 +164,8 @@ def gemm_timeline(buffer: torch.Tensor | None) -> None:
 def gemm_tune(swap: int = -1, rows: int = 0, cut_last_round: bool = True) -> None:
     """Tuning aid: force how the tensor-core GEMM runs the calls that follow. swap 0: unswapped
     tiles on single SMs, 1: swapped operands, 2: tiles on pairs of SMs, -1: the planner's choice;
-    rows: weight rows per unswapped tile (single SMs: a multiple of 32 from 64 to 256; pairs: 128
-    or 256; 0: the planner's); cut_last_round: whether the pair form may cut its last round of
+    rows: weight rows per unswapped tile (a multiple of 32, single SMs from 64 to 256, pairs from
+    128 to 256; 0: the planner's); cut_last_round: whether the pair form may cut its last round of
     tiles along K. The plans and workspace sizes remembered per shape are forgotten, because they
     differ between the forms."""
     tune = lib().asb_gemm_tcgen05_tune
