@@ -15,7 +15,8 @@ from tiny_configs import TINY
 
 pytestmark = pytest.mark.gpu
 DTYPES = ["float32", "bfloat16"]
-LENGTHS = {"a": [5, 17, 33, 70], "b": [1, 9, 24, 40, 75], "c": [3, 50, 90, 41], "d": [45, 200, 9, 330]}
+LENGTHS = {"a": [5, 17, 33, 70], "b": [1, 9, 24, 40, 75], "c": [3, 50, 90, 41], "d": [45, 200, 9, 330],
+           "e": [41, 150, 12, 230]}  # fmt: skip
 
 
 @pytest.fixture(scope="module")
@@ -38,7 +39,7 @@ def replayer(folder, dtype, bs, max_tokens, graphs=True, **more):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("name", ["a", "b", "c", "d"])
+@pytest.mark.parametrize("name", ["a", "b", "c", "d", "e"])
 def test_each_request_alone_and_whole(models, name, dtype):
     cfg, bs, folder, ps, oracle = models[name]
     rp = replayer(folder, dtype, bs, max(-(-len(p) // 64) * 64 for p in ps))
@@ -48,7 +49,7 @@ def test_each_request_alone_and_whole(models, name, dtype):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("name", ["a", "b", "c", "d"])
+@pytest.mark.parametrize("name", ["a", "b", "c", "d", "e"])
 def test_prefill_then_last_32_one_by_one(models, name, dtype):
     cfg, bs, folder, ps, oracle = models[name]
     rp = replayer(folder, dtype, bs, max(-(-len(p) // 64) * 64 for p in ps))
@@ -64,7 +65,7 @@ def test_prefill_then_last_32_one_by_one(models, name, dtype):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("name", ["a", "b", "c", "d"])
+@pytest.mark.parametrize("name", ["a", "b", "c", "d", "e"])
 def test_portions_of_changing_size(models, name, dtype):
     cfg, bs, folder, ps, oracle = models[name]
     rp = replayer(folder, dtype, bs, max(-(-len(p) // 64) * 64 for p in ps))
@@ -81,7 +82,7 @@ def test_portions_of_changing_size(models, name, dtype):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("name", ["a", "b", "c", "d"])
+@pytest.mark.parametrize("name", ["a", "b", "c", "d", "e"])
 def test_mixed_requests_reusing_pages(models, name, dtype):
     """Up to four live requests, portions beside single tokens, in a pool so small that pages
     freed by finished requests are taken again by later ones; every request appears three times,
@@ -106,7 +107,7 @@ def test_mixed_requests_reusing_pages(models, name, dtype):
 @pytest.mark.parametrize("dtype", DTYPES)
 def test_long_decoding(models, dtype):
     """300 tokens one by one (across many pages and, for config c, far beyond its window)."""
-    for name in ("b", "c", "d"):
+    for name in ("b", "c", "d", "e"):
         cfg, bs, folder, _, _ = models[name]
         w = checkpoint(cfg, seed=21)
         p = prompts(cfg, [300], seed=9)[0]

@@ -1,5 +1,6 @@
 """The tiny Qwen3 configurations the tests use: A and B differ in every size and option;
-C adds a sliding window on its upper layers (cache groups of two kinds in one model)."""
+C adds a sliding window on its upper layers (cache groups of two kinds in one model); D and E
+have the served head size of 128 (E with five heads a group and a window)."""
 
 TINY_A = dict(
     architectures=["Qwen3ForCausalLM"], vocab_size=256, hidden_size=64, intermediate_size=128,
@@ -37,7 +38,18 @@ TINY_D = dict(
 )  # fmt: skip
 BLOCK_SIZE_D = 16
 
+# Head size 128 with five query heads per kv head (a group that does not divide the attention
+# kernels' 128-row tile, as Qwen3-14B has it) and a window of 40 on layers 1 and 2: the window's
+# edges and the released pages through the tensor-core attention kernels.
+TINY_E = dict(
+    architectures=["Qwen3ForCausalLM"], vocab_size=777, hidden_size=320, intermediate_size=528,
+    num_hidden_layers=3, num_attention_heads=10, num_key_value_heads=2, head_dim=128,
+    rms_norm_eps=2e-6, rope_theta=500000.0, tie_word_embeddings=True,
+    max_position_embeddings=4096, hidden_act="silu",
+    use_sliding_window=True, sliding_window=40, max_window_layers=1,
+)  # fmt: skip
+BLOCK_SIZE_E = 8
 TINY = {
     "a": (TINY_A, BLOCK_SIZE_A), "b": (TINY_B, BLOCK_SIZE_B), "c": (TINY_C, BLOCK_SIZE_C),
-    "d": (TINY_D, BLOCK_SIZE_D),
+    "d": (TINY_D, BLOCK_SIZE_D), "e": (TINY_E, BLOCK_SIZE_E),
 }  # fmt: skip
