@@ -18,6 +18,7 @@ class EngineConfig:
     max_model_len: int = 16384  # longest sequence (prompt + output) accepted
     enable_prefix_caching: bool = True  # share pages of identical prompt prefixes
     cuda_graphs: bool = True  # replay captured graphs for decode-only steps
+    decode_lookahead: bool = True  # launch a decode-only step before the one before it has been read
 
     def __post_init__(self) -> None:
         if self.block_size < 1 or self.num_blocks < 1 or self.max_num_seqs < 1:

@@ -348,17 +348,24 @@ class ModelRunner:
     # ---- running --------------------------------------------------------------------------------
 
     @torch.inference_mode()
-    def step(self, rows: list[Row]) -> torch.Tensor:
-        """Run one step; float32 logits [sum(len(row.want)), vocab]."""
+    def step(self, rows: list[Row], device_tokens: torch.Tensor | None = None) -> torch.Tensor:
+        """Run one step; float32 logits [sum(len(row.want)), vocab]. `device_tokens` (int32, one
+        per row, on the device) stands in for the rows' token ids where the host does not know
+        them yet: a step of single tokens launched before its predecessor's sampled ids were read;
+        the rows then carry placeholders."""
         if not rows:
             return torch.empty(0, self.model.spec.vocab_size, device=self.device, dtype=torch.float32)
+        if device_tokens is not None and (device_tokens.shape[0] != len(rows) or any(len(r.tokens) != 1 for r in rows)):
+            raise ValueError("tokens from the device are one per row of a step of single tokens")
         if self.use_graphs and all(len(r.tokens) == 1 for r in rows):
-            return self._step_graph(rows)
+            return self._step_graph(rows, device_tokens)
         ctx, groups, _ = self.prepare(rows)
+        if device_tokens is not None:
+            ctx.token_ids[: len(rows)].copy_(device_tokens)
         self._bind(groups)
         return self.model.forward(ctx, self.views)
 
-    def _step_graph(self, rows: list[Row]) -> torch.Tensor:
+    def _step_graph(self, rows: list[Row], device_tokens: torch.Tensor | None = None) -> torch.Tensor:
         """Decode-only step through a captured graph. The graph is keyed by everything that
         fixes kernel shapes and buffer offsets: requests (rounded up to a bucket and padded with
         dummy requests when every row wants its logits, as in generation), table width (rounded
@@ -372,6 +379,8 @@ class ModelRunner:
         wanted = sum(len(r.want) for r in rows)
         pad_r = batch_bucket(len(rows)) if wanted == len(rows) else None
         ctx, groups, key = self.prepare(rows, pad_requests=pad_r, pad_width=pad_w)
+        if device_tokens is not None:  # behind the upload, before anything reads the ids
+            ctx.token_ids[: len(rows)].copy_(device_tokens)
         ctx.max_context = context_bucket(ctx.max_context)
         key = (*key, ctx.max_context)
         self._bind(groups)

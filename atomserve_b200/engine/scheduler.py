@@ -164,6 +164,8 @@ class Scheduler:
         gained: list[tuple[Sequence, list[int]]] = []
         limit = self.config.max_model_len
         for seq, result in zip(out.seqs, results, strict=True):
+            if seq.status is SequenceStatus.FINISHED:
+                continue  # retired while its step was on the device (a step launched ahead, an abort): the row is dropped
             taken = 0
             reason = None
             for token in result.tokens:

@@ -189,6 +189,76 @@ def test_concurrent_clients_abort_and_validation(setup):
     assert eng.stats()["kv_blocks_used"] == 0 and eng.stats()["running"] == 0
 
 
+def ahead_engine_for(model, bs, eos=frozenset(), **kw):
+    config = EngineConfig(**{"block_size": bs, "num_blocks": 64, "max_model_len": 64 * bs, "max_num_seqs": 8,
+                             "max_num_batched_tokens": 256, **kw})  # fmt: skip
+    cache = CacheManager(model.cache_requirements(), bs, config.num_blocks, config.max_num_seqs, torch.float32, "cpu")
+    return Engine(ModelRunner(model, cache), Scheduler(config, cache, frozenset(eos)), toy_parts.TwoPhaseArgmaxSampler())
+
+
+def test_steps_launched_ahead_change_no_token(setup):
+    """With a sampler that can start a step's sampling and be read later, the engine launches a
+    decode-only step before it has read the step before it. The tokens must be those of the plain
+    implementation: batched with different lengths (sequences ending by length at different
+    steps), with end-of-sequence tokens that end sequences while the step ahead is on its way
+    (its row is dropped), with so few pages that sequences are preempted, with a prefix shared."""
+    cfg, bs, w, model = setup
+    ps = prompts(cfg, [5, 17, 33, 2], seed=3)
+    lengths = [9, 3, 14, 6]
+    expect = [plain.greedy_generate(w, cfg, p, n) for p, n in zip(ps, lengths)]
+    eng = ahead_engine_for(model, bs)
+    handles = [eng.submit(p, SamplingParams(max_tokens=n, **GREEDY)) for p, n in zip(ps, lengths)]
+    while eng.step():
+        pass
+    assert [list(h) for h in handles] == expect and [h.finish_reason for h in handles] == ["length"] * 4
+    assert eng.stats()["steps_ahead"] >= 5 and eng.stats()["kv_blocks_used"] == 0
+    # end-of-sequence tokens: whatever the third and the fifth token of the first reply are
+    long = [plain.greedy_generate(w, cfg, p, 12) for p in ps]
+    eos = {long[0][2], long[0][4]}
+    def cut(out):
+        for i, t in enumerate(out):
+            if t in eos:
+                return out[: i + 1]
+        return out
+    eng = ahead_engine_for(model, bs, eos=eos)
+    got = eng.generate(ps, SamplingParams(max_tokens=12, temperature=0.0))
+    assert got == [cut(o) for o in long] and len(got[0]) <= 3
+    assert eng.stats()["steps_ahead"] > 0 and eng.stats()["kv_blocks_used"] == 0
+    # few pages: preemption between steps launched ahead
+    ps3 = prompts(cfg, [bs + 3, bs + 5, 2 * bs - 1], seed=5)
+    n = bs + 8
+    eng = ahead_engine_for(model, bs, num_blocks=7, max_model_len=7 * bs, enable_prefix_caching=False)
+    assert eng.generate(ps3, SamplingParams(max_tokens=n, **GREEDY)) == [plain.greedy_generate(w, cfg, p, n) for p in ps3]
+    assert eng.stats()["preemptions"] > 0 and eng.stats()["steps_ahead"] > 0 and eng.stats()["kv_blocks_used"] == 0
+    # a shared prefix, one request after the other on one engine
+    shared = prompts(cfg, [3 * bs + 2], seed=6)[0]
+    eng = ahead_engine_for(model, bs)
+    for p in (shared + [1, 2, 3], shared + [4]):
+        assert eng.generate([p], SamplingParams(max_tokens=6, **GREEDY)) == [plain.greedy_generate(w, cfg, p, 6)]
+
+
+def test_abort_and_arrival_while_a_step_is_ahead(setup):
+    """A request aborted while a step launched ahead still carries its row, and a request that
+    arrives meanwhile: the others' tokens stay those of the plain implementation."""
+    cfg, bs, w, model = setup
+    ps = prompts(cfg, [7, 12, 20], seed=9)
+    expect = [plain.greedy_generate(w, cfg, p, 10) for p in ps]
+    eng = ahead_engine_for(model, bs)
+    params = SamplingParams(max_tokens=10, **GREEDY)
+    a, b = eng.submit(ps[0], params), eng.submit(ps[1], params)
+    for _ in range(4):
+        assert eng.step()
+    assert eng._ahead is not None  # a step is on its way with rows of both
+    b.abort()
+    c = eng.submit(ps[2], params)
+    while eng.step():
+        pass
+    assert list(a) == expect[0] and list(c) == expect[2]
+    got_b = list(b)
+    assert b.finish_reason == "abort" and 0 < len(got_b) < 10 and got_b == expect[1][: len(got_b)]
+    assert eng.stats()["kv_blocks_used"] == 0 and eng.stats()["running"] == 0
+
+
 def test_engine_survives_a_failing_step(setup):
     cfg, bs, w, model = setup
     eng = engine_for(model, bs)

@@ -163,6 +163,44 @@ def test_sampled_generation_is_seeded_and_in_support(folders):
     assert len(set(out)) == len(out)  # a large penalty never repeats a generated token
 
 
+def test_steps_launched_ahead_give_the_same_tokens(folders):
+    """Decode-only steps launched before the step before them has been read (their input the
+    sampled ids as they lie on the device) against the engine that reads every step first:
+    the same tokens for seeded sampling (the draw counters run one ahead), for greedy requests of
+    different lengths, and with end-of-sequence ids that end requests while a step is ahead."""
+    from atomserve_b200.engine.sequence import SamplingParams
+
+    cfg, bs, w, folder = folders["b"]
+    ps = prompts(cfg, [12, 5, 30, 2], seed=4)
+    for dtype in ("float32", "bfloat16"):
+        outs = {}
+        for ahead in (False, True):
+            eng = engine_for(folder, dtype, bs, decode_lookahead=ahead)
+            hs = [eng.submit(p, SamplingParams(temperature=0.9, top_k=8, top_p=0.95, max_tokens=n, seed=3 + i, ignore_eos=True))
+                  for i, (p, n) in enumerate(zip(ps, [14, 3, 9, 20]))]  # fmt: skip
+            hs += [eng.submit(p, SamplingParams(temperature=0.0, max_tokens=n, ignore_eos=True)) for p, n in zip(ps, [6, 17, 2, 11])]
+            while eng.step():
+                pass
+            outs[ahead] = [list(h) for h in hs]
+            assert (eng.stats()["steps_ahead"] > 5) == ahead and eng.stats()["kv_blocks_used"] == 0
+        assert outs[True] == outs[False], dtype
+    greedy = plain.greedy_generate(w, cfg, ps[0], 12)
+    eos = frozenset({greedy[3]})
+    from atomserve_b200.config import EngineConfig
+    from atomserve_b200.engine.engine import create_engine
+    from atomserve_b200.weights import load_model
+
+    _, _, model = load_model(folder, "float32", "cuda")
+    config = EngineConfig(block_size=bs, num_blocks=64, max_model_len=64 * bs, max_num_seqs=8, max_num_batched_tokens=256)
+    eng = create_engine(model, config, eos_token_ids=eos, sampler_seed=0)
+    got = eng.generate(ps[:3], SamplingParams(temperature=0.0, max_tokens=12))
+    for p, g in zip(ps[:3], got):
+        full = plain.greedy_generate(w, cfg, p, 12)
+        cut = next((i + 1 for i, t in enumerate(full) if t in eos), 12)
+        assert g == full[:cut]
+    assert len(got[0]) <= 4 and eng.stats()["steps_ahead"] > 0 and eng.stats()["kv_blocks_used"] == 0
+
+
 def test_first_token_sees_only_itself(folders):
     from atomserve_b200.engine.replay import TraceReplayer
 

@@ -390,3 +390,19 @@ class ArgmaxSampler:
 
     def release(self, seq_id):
         pass
+
+
+class LaunchedArgmax:
+    def __init__(self, ids):
+        self.device_ids = ids
+
+
+class TwoPhaseArgmaxSampler(ArgmaxSampler):
+    """The same in the two phases of the package's sampler (start a step's sampling, read it
+    later), which is what lets the engine launch a step ahead of the one it is reading."""
+
+    def launch(self, logits, seqs, ahead=0):
+        return LaunchedArgmax(logits.argmax(-1).to(torch.int32))
+
+    def collect(self, picked):
+        return picked.device_ids.tolist()
