@@ -231,6 +231,13 @@ class Engine:
 
     def step(self) -> bool:
         """Plan, run and book one step. False when no request is left to work on."""
+        try:
+            return self._step()
+        except BaseException:
+            self._ahead = None  # a step that raised leaves nothing on its way to be read later
+            raise
+
+    def _step(self) -> bool:
         self._read_mail(wait=False)
         launched, self._ahead = self._ahead, None
         if launched is None:
