@@ -143,8 +143,8 @@ def linear_partial(x: torch.Tensor, w: torch.Tensor) -> PartialSums | None:
         return None
     (M, K), N = x.shape, w.shape[0]
     cuts_k, swapped, max_slots, tile_tokens, k_blocks, tiles, blocks, _pair = _plan(M, N, K)
-    if not (cuts_k and swapped) or tiles * 128 < N or M > tile_tokens:
-        return None
+    if not (cuts_k and swapped) or tiles * 128 < N or M > tile_tokens or tile_tokens & (tile_tokens - 1):
+        return None  # (the consumers read slots of 16 to 256 token columns, a power of two)
     workspace = gemm_workspace(x.device, tiles * max_slots * 128 * tile_tokens)
     check(lib().asb_gemm_tcgen05(None, ptr(x), ptr(w), None, M, N, K, 3, ptr(workspace), ptr(gemm_status(x.device)), stream()))
     return PartialSums(workspace, M, N, max_slots, tile_tokens, k_blocks, tiles, blocks)
